@@ -1,0 +1,82 @@
+// Shared device helpers for the sm_100a kernels of this package.
+//
+// Every kernel file is compiled on its own into a small shared library with
+// plain C entry points (no framework headers), so that a model compiles only the
+// kernels it needs and a fresh checkout builds in seconds.  Entry points return
+// 0 on success or a negative code for a refused size / a positive cudaError_t.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Refusal codes (negative so that they never collide with cudaError_t values).
+#define TB_ERR_BAD_DTYPE (-2)
+#define TB_ERR_BAD_SIZE (-3)
+#define TB_ERR_BAD_ALIGN (-4)
+
+enum TbDtype : int { TB_F32 = 0, TB_BF16 = 1 };
+
+static inline int tb_launch_status() {
+    cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? 0 : (int)err;
+}
+
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+    // Value an element takes when written and read back (identity in 32-bit).
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+
+template <>
+struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum with a fixed reduction tree (depends only on blockDim), so that
+// a row's statistic does not depend on what else is in the batch.
+// `scratch` must hold 32 floats.  Every thread receives the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < warps) ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < warps) ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}

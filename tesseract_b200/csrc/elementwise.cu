@@ -1,0 +1,92 @@
+// Row gathers and the SwiGLU activation.
+//
+//   tb_embedding     out[t, :] = table[token[t], :]           (src/cuda/kernels.rs:10-24)
+//   tb_gather_rows   out[s, :] = in[rows[s], :]               (src/cuda/kernels.rs:774-801)
+//   tb_silu_mul      out[t, j] = silu(gu[t, j]) * gu[t, I+j]  (src/cuda/kernels.rs:191-208)
+//
+// The activation is computed in 32-bit: g * (1 / (1 + exp(-g))) * u, rounded once.
+#include "common.cuh"
+
+namespace {
+
+// Copies `row_bytes` bytes per row; 16-byte vectors when the row allows it.
+template <int VEC_BYTES>
+__global__ void gather_rows_kernel(const int* __restrict__ index, const char* __restrict__ src,
+                                   char* __restrict__ dst, int64_t row_bytes, int num_src_rows) {
+    const int row = blockIdx.x;
+    int from = index[row];
+    if (from < 0 || from >= num_src_rows) from = 0;  // host validates; never read out of bounds
+    const char* s = src + (int64_t)from * row_bytes;
+    char* d = dst + (int64_t)row * row_bytes;
+    if (VEC_BYTES == 16) {
+        const int n = (int)(row_bytes / 16);
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+        const int n = (int)(row_bytes / VEC_BYTES);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            if (VEC_BYTES == 4) reinterpret_cast<uint32_t*>(d)[i] = reinterpret_cast<const uint32_t*>(s)[i];
+            else reinterpret_cast<uint16_t*>(d)[i] = reinterpret_cast<const uint16_t*>(s)[i];
+        }
+    }
+}
+
+int gather_rows(const int* index, const void* src, void* dst, int rows, int64_t width, int num_src_rows,
+                int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (dtype != TB_F32 && dtype != TB_BF16) return TB_ERR_BAD_DTYPE;
+    const int64_t elem = dtype == TB_F32 ? 4 : 2;
+    const int64_t row_bytes = width * elem;
+    const bool aligned = (row_bytes % 16 == 0) && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0);
+    const int threads = 128;
+    if (aligned)
+        gather_rows_kernel<16><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
+    else if (elem == 4)
+        gather_rows_kernel<4><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
+    else
+        gather_rows_kernel<2><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
+    return tb_launch_status();
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride) {
+    const int row = blockIdx.x;
+    const T* g = gu + (int64_t)row * gu_stride;
+    const T* u = g + inter;
+    T* o = out + (int64_t)row * inter;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < inter; j += gridDim.y * blockDim.x) {
+        const float gv = Elem<T>::load(g + j);
+        const float uv = Elem<T>::load(u + j);
+        const float act = gv * (1.0f / (1.0f + expf(-gv))) * uv;
+        Elem<T>::store(o + j, act);
+    }
+}
+
+}  // namespace
+
+TB_EXPORT int tb_embedding(const int* tokens, const void* table, void* out, int rows, int hidden, int vocab,
+                           int dtype, cudaStream_t stream) {
+    return gather_rows(tokens, table, out, rows, hidden, vocab, dtype, stream);
+}
+
+TB_EXPORT int tb_gather_rows(const int* rows_index, const void* in, void* out, int rows, int width,
+                             int num_in_rows, int dtype, cudaStream_t stream) {
+    return gather_rows(rows_index, in, out, rows, width, num_in_rows, dtype, stream);
+}
+
+// gu: [rows, 2*inter] with the gate in columns [0, inter) and the up projection in [inter, 2*inter).
+TB_EXPORT int tb_silu_mul(const void* gu, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+    if (rows == 0 || inter == 0) return 0;
+    const int threads = 256;
+    int bx = (inter + threads - 1) / threads;
+    if (bx > 64) bx = 64;
+    dim3 grid(rows, bx);
+    if (dtype == TB_F32)
+        silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter);
+    else if (dtype == TB_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                                                                    inter, 2 * (int64_t)inter);
+    else
+        return TB_ERR_BAD_DTYPE;
+    return tb_launch_status();
+}

@@ -1,0 +1,220 @@
+"""Python face of the hand-written CUDA kernels.
+
+Each function checks what the kernel assumes (device, dtype, contiguity, sizes), then
+calls the C entry point of the lazily built library on the current CUDA stream.  There
+is no other implementation behind these functions: if a library cannot be built or
+loaded, or a kernel refuses a size, the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_library
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+_REFUSALS = {
+    -2: "unsupported dtype",
+    -3: "unsupported size",
+    -4: "misaligned pointer",
+    -5: "scratch capacity exceeded",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: kernel refused the call ({_REFUSALS.get(status, status)})")
+    raise KernelError(f"{what}: CUDA error {status} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, got {dtype}") from None
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(cond: bool, message: str) -> None:
+    if not cond:
+        raise KernelError(message)
+
+
+def _cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must live on a CUDA device")
+
+
+_i32 = ctypes.c_int
+_i64 = ctypes.c_int64
+_f32 = ctypes.c_float
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = table[tokens[t]]``; tokens int32 ``[T]``, table ``[V, H]``, out ``[T, H]``."""
+    _cuda(tokens, table, out)
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "tokens must be contiguous int32")
+    _need(table.is_contiguous() and out.is_contiguous() and table.dtype == out.dtype, "table/out mismatch")
+    rows, hidden = out.shape
+    _need(tokens.numel() == rows and table.shape[1] == hidden, "embedding shapes disagree")
+    lib = load_library("elementwise")
+    _check(lib.tb_embedding(_ptr(tokens), _ptr(table), _ptr(out), _i32(rows), _i32(hidden), _i32(table.shape[0]),
+                            _i32(_code(out.dtype)), _stream()), "embedding")
+    return out
+
+
+def gather_rows(rows_index: torch.Tensor, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[s] = src[rows_index[s]]``."""
+    _cuda(rows_index, src, out)
+    _need(rows_index.dtype == torch.int32 and rows_index.is_contiguous(), "row index must be contiguous int32")
+    _need(src.is_contiguous() and out.is_contiguous() and src.dtype == out.dtype, "src/out mismatch")
+    rows, width = out.shape
+    _need(rows_index.numel() == rows and src.shape[1] == width, "gather shapes disagree")
+    lib = load_library("elementwise")
+    _check(lib.tb_gather_rows(_ptr(rows_index), _ptr(src), _ptr(out), _i32(rows), _i32(width), _i32(src.shape[0]),
+                              _i32(_code(out.dtype)), _stream()), "gather_rows")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]`` with ``I = out.shape[1]``."""
+    _cuda(gate_up, out)
+    rows, inter = out.shape
+    _need(gate_up.shape == (rows, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous(), "silu_mul shapes")
+    _need(gate_up.dtype == out.dtype, "silu_mul dtypes")
+    lib = load_library("elementwise")
+    _check(lib.tb_silu_mul(_ptr(gate_up), _ptr(out), _i32(rows), _i32(inter), _i32(_code(out.dtype)), _stream()),
+           "silu_mul")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    _cuda(x, weight, out)
+    rows, width = x.shape
+    _need(x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype, "rms_norm x/out")
+    _need(weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous(),
+          "rms_norm weight must be a contiguous float32 vector of the row width")
+    lib = load_library("norm")
+    _check(lib.tb_rms_norm(_ptr(x), _ptr(weight), _ptr(out), _i32(rows), _i32(width), _f32(eps),
+                           _i32(_code(x.dtype)), _stream()), "rms_norm")
+    return out
+
+
+def add_rms_norm(residual: torch.Tensor, update: torch.Tensor, weight: torch.Tensor, eps: float,
+                 out: torch.Tensor, residual_out: torch.Tensor) -> None:
+    """``c = residual + update``; ``residual_out = c``; ``out = norm(c) * weight``.  ``residual_out`` may be ``residual``."""
+    _cuda(residual, update, weight, out, residual_out)
+    rows, width = residual.shape
+    for t in (update, out, residual_out):
+        _need(t.shape == residual.shape and t.dtype == residual.dtype and t.is_contiguous(), "add_rms_norm operands")
+    _need(residual.is_contiguous(), "add_rms_norm residual must be contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous(),
+          "add_rms_norm weight must be a contiguous float32 vector of the row width")
+    lib = load_library("norm")
+    _check(lib.tb_add_rms_norm(_ptr(residual), _ptr(update), _ptr(weight), _ptr(out), _ptr(residual_out), _i32(rows),
+                               _i32(width), _f32(eps), _i32(_code(residual.dtype)), _stream()), "add_rms_norm")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor], cache: torch.Tensor, num_heads: int, num_kv_heads: int,
+                  head_dim: int, page_size: int, write_kv: bool = True) -> None:
+    """Rotate q (in place) and k, and store rotated k and v into the cache pages.
+
+    ``qkv``: ``[T, (num_heads + 2*num_kv_heads) * head_dim]`` (last dim contiguous).
+    ``cache``: one cache entry ``[pages, 2, num_kv_heads, page_size, head_dim]``.
+    ``inv_freq``: float32 ``[head_dim/2]`` or ``None`` for no rotation.
+    """
+    _cuda(qkv, positions, seq_of_row, block_table, cache)
+    rows = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qkv layout")
+    _need(positions.dtype == torch.int32 and seq_of_row.dtype == torch.int32 and block_table.dtype == torch.int32,
+          "positions, seq_of_row and block_table must be int32")
+    _need(positions.numel() >= rows and seq_of_row.numel() >= rows, "row metadata shorter than the batch")
+    _need(block_table.dim() == 2 and block_table.stride(1) == 1, "block table must be 2-D, rows contiguous")
+    _need(cache.is_contiguous() and cache.dtype == qkv.dtype and
+          tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache entry layout")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2 and inv_freq.is_cuda, "inv_freq")
+    lib = load_library("rope_cache")
+    _check(lib.tb_rope_kv_write(_ptr(qkv), _i64(qkv.stride(0)), _ptr(positions), _ptr(seq_of_row), _ptr(block_table),
+                                _i32(block_table.stride(0)), _ptr(inv_freq), _ptr(cache), _i32(rows), _i32(num_heads),
+                                _i32(num_kv_heads), _i32(head_dim), _i32(page_size), _i32(1 if write_kv else 0),
+                                _i32(_code(qkv.dtype)), _stream()), "rope_kv_write")
+
+
+def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                   seq_of_row: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
+                   head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+    """Plain paged attention, one warp per (row, head).  ``q``/``out``: ``[T, num_heads*head_dim]`` views."""
+    _cuda(q, out, cache, positions, seq_of_row, block_table)
+    rows = q.shape[0]
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim and out.shape == q.shape,
+          "q/out layout")
+    _need(q.dtype == out.dtype == cache.dtype, "attention dtypes disagree")
+    _need(positions.dtype == torch.int32 and seq_of_row.dtype == torch.int32 and block_table.dtype == torch.int32,
+          "positions, seq_of_row and block_table must be int32")
+    _need(block_table.dim() == 2 and block_table.stride(1) == 1, "block table must be 2-D, rows contiguous")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache layout")
+    lib = load_library("attention_rows")
+    _check(lib.tb_attention_rows(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                 _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
+                                 _i32(rows), _i32(num_heads), _i32(num_kv_heads), _i32(head_dim), _i32(page_size),
+                                 _i32(window), _f32(scale), _i32(_code(q.dtype)), _stream()), "attention_rows")
+    return out
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ w[N,K]^T`` in true 32-bit arithmetic."""
+    _cuda(a, w, out)
+    _need(a.dtype == w.dtype == out.dtype == torch.float32, "gemm_f32_nt takes float32")
+    m, k = a.shape
+    n = w.shape[0]
+    _need(w.shape[1] == k and out.shape == (m, n), "gemm shapes disagree")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm operands need contiguous rows")
+    lib = load_library("gemm_f32")
+    _check(lib.tb_gemm_f32_nt(_ptr(a), _i64(a.stride(0)), _ptr(w), _i64(w.stride(0)), _ptr(out), _i64(out.stride(0)),
+                              _i32(m), _i32(n), _i32(k), _stream()), "gemm_f32_nt")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Lowest index of each row's maximum; logits float32 ``[S, V]``, out int32 ``[S]``."""
+    _cuda(logits, out)
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 with contiguous rows")
+    _need(out.dtype == torch.int32 and out.numel() >= logits.shape[0] and out.is_contiguous(), "argmax out")
+    lib = load_library("sampling")
+    _check(lib.tb_argmax(_ptr(logits), _i64(logits.stride(0)), _ptr(out), _i32(logits.shape[0]),
+                         _i32(logits.shape[1]), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Per row: argmax if ``temperature <= 0`` else inverse-CDF sampling with the given uniform draw."""
+    _cuda(logits, temperature, uniform, out)
+    rows = logits.shape[0]
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 with contiguous rows")
+    _need(temperature.dtype == torch.float32 and temperature.numel() >= rows, "temperature must be float32 [S]")
+    _need(uniform.dtype == torch.float64 and uniform.numel() >= rows, "uniform must be float64 [S]")
+    _need(out.dtype == torch.int32 and out.numel() >= rows and out.is_contiguous(), "sample out")
+    lib = load_library("sampling")
+    _check(lib.tb_sample(_ptr(logits), _i64(logits.stride(0)), _ptr(temperature), _ptr(uniform), _ptr(out),
+                         _i32(rows), _i32(logits.shape[1]), _stream()), "sample")
+    return out

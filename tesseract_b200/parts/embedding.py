@@ -1,0 +1,65 @@
+"""Token embedding (a row gather, src/cuda/kernels.rs:10-24) and the output head.
+
+The head multiplies the normalised hidden rows by the ``[vocab, hidden]`` matrix
+(src/cuda/dense_decoder.rs:824-831) and returns 32-bit logits.  With tied embeddings the
+model builder hands both parts the same checkpoint tensor, and both keep one device copy.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import kernels
+from ..config.spec import PartSpec
+from ..weights.loader import ExpectedTensor
+from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime
+from .linear import Linear
+
+
+@EMBEDDINGS.register("token_embedding")
+class TokenEmbedding(Embedding):
+    """params: ``vocab_size, hidden_size``; weights: ``table``."""
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        self.vocab_size = int(spec.params["vocab_size"])
+        self.hidden_size = int(spec.params["hidden_size"])
+        self.table = runtime.matrix(tensors["table"])
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        p = spec.params
+        return {spec.weights["table"]: ExpectedTensor((int(p["vocab_size"]), int(p["hidden_size"])))}
+
+    def forward(self, token_ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((token_ids.numel(), self.hidden_size), dtype=self.table.dtype, device=self.table.device)
+        return kernels.embedding(token_ids, self.table, out)
+
+
+@HEADS.register("lm_head")
+class LMHead(Head):
+    """params: ``vocab_size, hidden_size``; weights: ``weight``.  Returns float32 logits."""
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime,
+                 shared: Optional[torch.Tensor] = None):
+        super().__init__(spec, tensors, runtime)
+        self.vocab_size = int(spec.params["vocab_size"])
+        self.hidden_size = int(spec.params["hidden_size"])
+        if shared is not None:
+            self.proj = Linear.__new__(Linear)
+            self.proj.runtime = runtime
+            self.proj.weight = shared
+            self.proj.out_features, self.proj.in_features = shared.shape
+        else:
+            self.proj = Linear(tensors["weight"], runtime)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        p = spec.params
+        return {spec.weights["weight"]: ExpectedTensor((int(p["vocab_size"]), int(p["hidden_size"])))}
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.proj.forward(x, out=out, float32_out=True)

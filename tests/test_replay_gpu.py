@@ -1,0 +1,153 @@
+"""The engine against the plain implementation under every way of cutting the work.
+
+Each case drives the engine's own step function (model, cache manager, kernels) through
+a trace and compares every wanted logits row with the plain whole-sequence model.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import (TINY, compare, max_live_tokens, plain_logits, random_tokens, replay, trace_mixed,
+                           trace_portions, trace_tail, trace_whole)
+
+pytestmark = pytest.mark.gpu
+
+# |diff| <= REL * max(1, max|logit|).  float32: summation-order noise only.  bfloat16: the
+# unit roundoff 2^-8 through a few dozen rounding points, on logits of order one.
+REL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+LENGTHS = {"a": [5, 17, 33, 100], "b": [1, 40, 63, 129, 200], "c": [3, 64, 65, 130]}
+
+
+def make_requests(name):
+    vocab = TINY[name]["vocab_size"]
+    return {f"{name}{i}": random_tokens(vocab, n, seed=100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def engines(model_folders):
+    from tesseract_b200.engine import load_model, make_stepper
+
+    cache = {}
+
+    def get(name, dtype, capacity_tokens=4096, store="bfloat16"):
+        key = (name, dtype, store)
+        if key not in cache:
+            cache[key] = load_model(model_folders(name, store), dtype=dtype)
+        return make_stepper(cache[key], capacity_tokens=capacity_tokens, max_requests=8)
+
+    return get
+
+
+@pytest.fixture(scope="module")
+def plains(model_folders):
+    cache = {}
+
+    def get(name, store="bfloat16"):
+        if (name, store) not in cache:
+            cache[(name, store)] = plain_logits(model_folders(name, store), make_requests(name))
+        return cache[(name, store)]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions"])
+def test_cuts_match_plain(engines, plains, name, dtype, cut):
+    requests = make_requests(name)
+    steps = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}[cut](requests)
+    stepper = engines(name, dtype)
+    got = replay(stepper, steps)
+    compare(got, plains(name), REL[dtype], f"{name}/{dtype}/{cut}")
+    stepper.cache.check()
+    assert stepper.cache.used_pages() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_mixed_with_page_reuse(engines, plains, name, dtype):
+    requests = make_requests(name)
+    requests.update({f"{name}x{i}": random_tokens(TINY[name]["vocab_size"], n, seed=7 + i)
+                     for i, n in enumerate([50, 21, 90, 34])})
+    steps = trace_mixed(requests, seed=3)
+    assert max(len(e) for e, _ in steps) >= 3, "the trace should batch several requests"
+    capacity = max_live_tokens(steps, 64)
+    stepper = engines(name, dtype, capacity_tokens=capacity)
+    got = replay(stepper, steps)
+    plain = dict(plains(name))
+    plain.update(_plain_extra(name, {rid: toks for rid, toks in requests.items() if rid not in plain}))
+    compare(got, plain, REL[dtype], f"{name}/{dtype}/mixed")
+    assert stepper.cache.pages_reused > 0, "the pool was meant to be small enough for pages to be used again"
+    stepper.cache.check()
+    assert stepper.cache.used_pages() == 0
+
+
+_extra_cache = {}
+
+
+def _plain_extra(name, extra):
+    key = (name, tuple(sorted(extra)))
+    if key not in _extra_cache:
+        _extra_cache[key] = plain_logits(_FOLDERS(name, "bfloat16"), extra)
+    return _extra_cache[key]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _bind_folders(model_folders):
+    global _FOLDERS
+    _FOLDERS = model_folders
+    yield
+
+
+def test_float32_cuts_agree_bitwise(engines):
+    """In 32-bit every reduction order depends only on the row itself: cuts agree bit for bit."""
+    name = "b"
+    requests = make_requests(name)
+    whole = replay(engines(name, "float32"), trace_whole(requests))
+    portions = replay(engines(name, "float32"), trace_portions(requests))
+    mixed = replay(engines(name, "float32", capacity_tokens=max_live_tokens(trace_mixed(requests, seed=5))),
+                   trace_mixed(requests, seed=5))
+    for key, row in portions.items():
+        assert np.array_equal(row, whole[key]), f"portions differ from whole at {key}"
+    for key, row in mixed.items():
+        assert np.array_equal(row, whole[key]), f"mixed differs from whole at {key}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_float32_stored_weights(engines, model_folders, dtype):
+    """A checkpoint stored in 32-bit: the float32 path keeps every bit of it."""
+    name = "a"
+    requests = make_requests(name)
+    got = replay(engines(name, dtype, store="float32"), trace_portions(requests))
+    plain = plain_logits(model_folders(name, "float32"), requests)
+    compare(got, plain, REL[dtype], f"{name}/{dtype}/float32-stored")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(engines, plains, dtype):
+    name = "b"
+    tokens = make_requests(name)["b4"]          # 200 tokens, decoded one by one from the third on
+    steps = [([("long", tokens[:3], [0, 1, 2])], [])]
+    steps += [([("long", tokens[i:i + 1], [0])], []) for i in range(3, len(tokens))]
+    steps[-1] = (steps[-1][0], ["long"])
+    got = replay(engines(name, dtype), steps)
+    plain = {"long": plains(name)["b4"]}
+    compare(got, plain, REL[dtype], f"{name}/{dtype}/long-decode")
+    assert len(got) == len(tokens)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens(engines, plains, dtype):
+    for name in ("a", "b"):
+        requests = make_requests(name)
+        steps = []
+        for rid, tokens in requests.items():
+            steps.append(([(rid, tokens[:1], [0])], []))
+            if len(tokens) > 1:
+                steps.append(([(rid, tokens[1:3], list(range(len(tokens[1:3]))))], [rid]))
+            else:
+                steps[-1] = (steps[-1][0], [rid])
+        got = replay(engines(name, dtype), steps)
+        compare(got, plains(name), REL[dtype], f"{name}/{dtype}/first-tokens")
