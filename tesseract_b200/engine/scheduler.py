@@ -1,0 +1,257 @@
+"""The scheduler above the step function: admit, cut prompts into portions, decode, finish, free.
+
+Behaviour follows the reference's engine thread (src/engine/scheduler.rs):
+
+* ``add_request`` (:531-603) bounds the number of known requests by
+  ``max_queue + max_running`` (overload is an error to the caller), validates the
+  options, rejects an empty prompt and a request whose ``prompt + max_tokens`` exceeds
+  the sequence limit, the model's positions or the whole cache.
+* ``admit_waiting`` (:605-633) scans the waiting queue once, first come first served;
+  a request is admitted only if the cache manager can give it a state slot **and**
+  reserve pages for ``prompt + max_tokens`` tokens in every group.  One that does not
+  fit goes to the back of the queue, so a smaller one may pass it.  This is what
+  happens when pages run out: nothing running is ever preempted, swapped or
+  recomputed, and a running request cannot run out, because its peak need was set
+  aside at admission.
+* ``build_batch`` (:635-722) spends ``max_batch_tokens`` on decode rows first (one token
+  each), then on prompt portions of at most ``prefill_chunk_tokens``; only a portion that
+  ends the known tokens samples; one uniform is drawn per sampled non-greedy row; the
+  running queue rotates by one after every batch.
+* ``apply`` (:724-833) appends sampled tokens and finishes on a stop token, an
+  end-of-sequence id or ``max_tokens``; a failed step fails the requests of its batch,
+  frees what they held and leaves the engine serving (:495-505).
+"""
+
+from __future__ import annotations
+
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.rng import SplitMix64
+from .step import StepEntry
+
+FINISH_STOP = "stop"
+FINISH_LENGTH = "length"
+FINISH_CANCELLED = "cancelled"
+FINISH_ERROR = "error"
+
+
+class EngineOverloaded(RuntimeError):
+    """More requests than ``max_queue + max_running`` are known to the engine."""
+
+
+class RequestRejected(ValueError):
+    """A request that can never be served (empty, too long, bad options)."""
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    rng: SplitMix64
+    generated: List[int] = field(default_factory=list)
+    computed_tokens: int = 0
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+
+    @property
+    def target_tokens(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    @property
+    def reservation_tokens(self) -> int:
+        return len(self.prompt) + self.params.max_tokens
+
+    def token_range(self, begin: int, end: int) -> List[int]:
+        n = len(self.prompt)
+        if end <= n:
+            return self.prompt[begin:end]
+        if begin >= n:
+            return self.generated[begin - n:end - n]
+        return self.prompt[begin:] + self.generated[:end - n]
+
+
+@dataclass
+class ScheduledSequence:
+    request: Request
+    begin: int
+    tokens: List[int]
+    samples: bool
+    draw: float = 0.0
+
+    @property
+    def is_decode(self) -> bool:
+        return self.begin >= len(self.request.prompt)
+
+
+@dataclass
+class StepResult:
+    """What one scheduler iteration did."""
+
+    batch: List[ScheduledSequence]
+    new_tokens: Dict[Hashable, int]
+    finished: List[Request]
+
+
+class Scheduler:
+    """``run_step(entries)`` runs the model and returns logits rows for the wanted places;
+    ``sample(logits, temperatures, top_ps, draws)`` returns one token per row.  Both are
+    injected, so the scheduler's decisions can be tested without a device."""
+
+    def __init__(self, config: EngineConfig, cache, run_step: Callable, sample: Callable, *, eos_token_ids=(),
+                 max_positions: Optional[int] = None, capacity_tokens: Optional[int] = None):
+        config.validate()
+        self.config = config
+        self.cache = cache
+        self.run_step = run_step
+        self.sample = sample
+        self.eos_token_ids = frozenset(int(t) for t in eos_token_ids)
+        self.max_positions = max_positions
+        self.capacity_tokens = capacity_tokens if capacity_tokens is not None else config.kv_capacity_tokens
+        self.requests: Dict[Hashable, Request] = {}
+        self.waiting: Deque[Hashable] = deque()
+        self.running: Deque[Hashable] = deque()
+        self._ids = itertools.count()
+        self.steps = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: SamplingParams, request_id: Hashable = None) -> Hashable:
+        if len(self.requests) >= self.config.max_pending + self.config.max_running:
+            raise EngineOverloaded("the inference engine is overloaded")
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise RequestRejected("the prompt is empty")
+        total = len(prompt) + params.max_tokens
+        limit = min(self.config.max_sequence_length, self.capacity_tokens)
+        if self.max_positions is not None:
+            limit = min(limit, self.max_positions)
+        if total > limit:
+            raise RequestRejected(f"prompt plus max_tokens ({total}) exceeds the configured capacity ({limit})")
+        if request_id is None:
+            request_id = next(self._ids)
+        if request_id in self.requests:
+            raise RequestRejected(f"request id {request_id!r} is already in use")
+        seed = params.seed if params.seed is not None else hash(request_id) & ((1 << 64) - 1)
+        self.requests[request_id] = Request(request_id, prompt, params, SplitMix64(seed))
+        self.waiting.append(request_id)
+        return request_id
+
+    def cancel(self, request_id: Hashable) -> None:
+        self._finish(request_id, FINISH_CANCELLED)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ one iteration
+    def admit_waiting(self) -> None:
+        for _ in range(len(self.waiting)):
+            if len(self.running) >= self.config.max_running:
+                break
+            request_id = self.waiting.popleft()
+            request = self.requests.get(request_id)
+            if request is None:
+                continue
+            if self.cache.admit(request_id, reserve_tokens=request.reservation_tokens):
+                self.running.append(request_id)
+            else:
+                self.waiting.append(request_id)
+
+    def build_batch(self) -> List[ScheduledSequence]:
+        budget = self.config.max_batch_tokens
+        batch: List[ScheduledSequence] = []
+        ids = list(self.running)
+        for decode_phase in (True, False):
+            for request_id in ids:
+                if budget == 0:
+                    break
+                request = self.requests.get(request_id)
+                if request is None:
+                    continue
+                is_decode = request.computed_tokens >= len(request.prompt)
+                if is_decode != decode_phase:
+                    continue
+                remaining = request.target_tokens - request.computed_tokens
+                if remaining <= 0:
+                    continue
+                limit = 1 if is_decode else self.config.prefill_chunk_tokens
+                count = min(remaining, limit, budget)
+                begin = request.computed_tokens
+                samples = begin + count == request.target_tokens
+                draw = 0.0
+                if samples and request.params.temperature != 0.0:
+                    draw = request.rng.unit_f64()
+                batch.append(ScheduledSequence(request, begin, request.token_range(begin, begin + count), samples, draw))
+                budget -= count
+        if len(self.running) > 1:
+            self.running.rotate(-1)
+        # prompt portions first, then decode rows (src/engine/batch.rs:355-428), order otherwise kept
+        batch.sort(key=lambda s: s.is_decode)
+        return batch
+
+    def step(self) -> StepResult:
+        """Admit, build one batch, run it, sample, apply.  Returns what happened."""
+        self.admit_waiting()
+        batch = self.build_batch()
+        if not batch:
+            return StepResult([], {}, [])
+        self.steps += 1
+        entries = [StepEntry(s.request.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
+        sampled = [s for s in batch if s.samples]
+        try:
+            logits = self.run_step(entries)
+            tokens = self.sample(logits, [s.request.params.temperature for s in sampled],
+                                 [s.request.params.top_p for s in sampled], [s.draw for s in sampled]) if sampled else []
+            if len(tokens) != len(sampled):
+                raise RuntimeError("the sampler returned a wrong number of tokens")
+        except Exception as exc:  # noqa: BLE001 - a failed step fails its batch, the engine keeps serving
+            finished = []
+            for s in batch:
+                s.request.error = f"{type(exc).__name__}: {exc}"
+                finished.append(self._finish(s.request.id, FINISH_ERROR))
+            return StepResult(batch, {}, [r for r in finished if r is not None])
+        return self._apply(batch, sampled, tokens)
+
+    def _apply(self, batch, sampled, tokens) -> StepResult:
+        new_tokens: Dict[Hashable, int] = {}
+        finished: List[Request] = []
+        for s in batch:
+            s.request.computed_tokens += len(s.tokens)
+        for s, token in zip(sampled, tokens):
+            request = s.request
+            token = int(token)
+            request.generated.append(token)
+            new_tokens[request.id] = token
+            reason = None
+            if token in request.params.stop_token_ids:
+                reason = FINISH_STOP
+            elif token in self.eos_token_ids and not request.params.ignore_eos:
+                reason = FINISH_STOP
+            elif len(request.generated) >= request.params.max_tokens:
+                reason = FINISH_LENGTH
+            if reason is not None:
+                done = self._finish(request.id, reason)
+                if done is not None:
+                    finished.append(done)
+        return StepResult(batch, new_tokens, finished)
+
+    def _finish(self, request_id: Hashable, reason: str) -> Optional[Request]:
+        request = self.requests.pop(request_id, None)
+        if request is None:
+            return None
+        request.finish_reason = reason
+        try:
+            self.waiting.remove(request_id)
+        except ValueError:
+            pass
+        try:
+            self.running.remove(request_id)
+        except ValueError:
+            pass
+        self.cache.release(request_id)
+        return request
