@@ -1,0 +1,121 @@
+"""Generation through the Python entry point and the command line, against the plain model."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests.helpers import TINY, random_tokens
+from tests.plain import llama
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_next(config, tensors, tokens):
+    return llama.forward(config, tensors, tokens)[-1].numpy()
+
+
+def check_greedy(config, tensors, prompt, generated, margin_rel):
+    tokens = list(prompt)
+    for k, got in enumerate(generated):
+        logits = plain_next(config, tensors, tokens)
+        best = int(np.argmax(logits))
+        if got != best:
+            margin = float(logits[best] - logits[got])
+            assert margin <= margin_rel * max(1.0, float(np.abs(logits).max())), \
+                f"generated token {k} is {got}, the plain model says {best} (margin {margin:.3e})"
+        tokens.append(got)
+
+
+@pytest.mark.parametrize("dtype, margin", [("float32", 1e-5), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("name, lengths, steps", [("a", [5, 17, 33], 8), ("b", [1, 40, 63, 129], 12)])
+def test_greedy_generation_matches_plain(model_folders, name, lengths, steps, dtype, margin):
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders(name)
+    config, tensors = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], n, seed=n) for n in lengths]
+    llm = LLM(folder, dtype=dtype, kv_capacity_tokens=1024, max_running=4, prefill_chunk_tokens=16,
+              max_batch_tokens=48)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=steps, temperature=0.0, ignore_eos=True))
+    for prompt, out in zip(prompts, outs):
+        assert len(out.token_ids) == steps and out.finish_reason == "length"
+        check_greedy(config, tensors, prompt, out.token_ids, margin)
+    assert llm.stepper.cache.used_pages() == 0
+    llm.stepper.cache.check()
+
+
+def test_temperature_sampling_is_reproducible_and_follows_the_draws(model_folders):
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("b")
+    config, tensors = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], n, seed=50 + n) for n in (1, 40, 63, 129)]
+    params = [SamplingParams(max_tokens=12, temperature=0.7, seed=1000 + i, ignore_eos=True) for i in range(4)]
+    runs = []
+    for chunk, running in ((16, 4), (512, 1)):           # mixed with others in portions of 16; then each alone
+        llm = LLM(folder, dtype="float32", kv_capacity_tokens=1024, max_running=running, prefill_chunk_tokens=chunk)
+        runs.append([o.token_ids for o in llm.generate(prompts, params)])
+    assert runs[0] == runs[1], "sampled tokens depend on the batching"
+    for prompt, p, generated in zip(prompts, params, runs[0]):
+        rng = llama.SplitMix64(p.seed)
+        tokens = list(prompt)
+        for got in generated:
+            draw = rng.unit_f64()
+            logits = plain_next(config, tensors, tokens)
+            want = llama.sample_in_token_order(logits, 0.7, draw)
+            if got != want:     # only a draw that lands within rounding of a boundary may differ, by one neighbour
+                scaled = logits.astype(np.float32) / np.float32(0.7)
+                cdf = np.cumsum(np.exp((scaled - scaled.max()).astype(np.float64)))
+                cdf /= cdf[-1]
+                assert abs(cdf[min(got, want)] - draw) < 1e-5, f"sampled {got}, the plain model says {want}"
+            tokens.append(got)
+
+
+def test_top_p_and_mixed_sampling_modes(model_folders):
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("a")
+    config, tensors = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], n, seed=n) for n in (9, 12, 20)]
+    params = [SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True),
+              SamplingParams(max_tokens=5, temperature=0.9, top_p=0.5, seed=3, ignore_eos=True),
+              SamplingParams(max_tokens=5, temperature=1.3, seed=4, ignore_eos=True)]
+    llm = LLM(folder, dtype="float32", kv_capacity_tokens=512, max_running=4)
+    outs = llm.generate(prompts, params)
+    check_greedy(config, tensors, prompts[0], outs[0].token_ids, 1e-5)
+    rng = llama.SplitMix64(3)
+    tokens = list(prompts[1])
+    for got in outs[1].token_ids:
+        want = llama.sample_host(plain_next(config, tensors, tokens), 0.9, 0.5, rng.unit_f64())
+        assert got == want
+        tokens.append(got)
+
+
+def test_eos_stops_generation(model_folders):
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("a")
+    config, tensors = llama.load_folder(folder)
+    prompt = random_tokens(config["vocab_size"], 7, seed=1)
+    llm = LLM(folder, dtype="float32", kv_capacity_tokens=256, max_running=2)
+    free = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))[0].token_ids
+    stopped = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.0, stop_token_ids=[free[2]]))[0]
+    assert stopped.token_ids == free[:3] and stopped.finish_reason == "stop"
+
+
+def test_command_line_generates(model_folders):
+    folder = model_folders("a")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "tesseract"), "--model-path", folder, "--prompt-ids", "5,6,7,8",
+           "--random-prompt", "11", "--max-tokens", "4", "--temperature", "0", "--ignore-eos", "--json",
+           "--kv-capacity-tokens", "256", "--max-running", "2", "--dtype", "float32"]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr
+    records = [json.loads(line) for line in done.stdout.strip().splitlines()]
+    assert len(records) == 2 and all(len(r["token_ids"]) == 4 and r["finish_reason"] == "length" for r in records)
+    config, tensors = llama.load_folder(folder)
+    check_greedy(config, tensors, [5, 6, 7, 8], records[0]["token_ids"], 1e-5)

@@ -1,0 +1,313 @@
+"""Each CUDA kernel alone against a plain PyTorch reference, at sizes other than the engine's."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import llama
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def dev(t):
+    return t.cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, width, vocab", [(1, 8, 3), (17, 100, 331), (129, 2048, 1000), (5, 7, 11)])
+def test_embedding_and_gather(dtype, rows, width, vocab):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(0)
+    table = torch.randn(vocab, width).to(dtype)
+    tokens = torch.randint(0, vocab, (rows,), dtype=torch.int32)
+    out = torch.empty(rows, width, dtype=dtype, device="cuda")
+    kernels.embedding(dev(tokens), dev(table), out)
+    assert torch.equal(out.cpu(), table[tokens.long()])
+    picked = torch.empty(rows, width, dtype=dtype, device="cuda")
+    index = torch.randint(0, rows, (rows,), dtype=torch.int32)
+    kernels.gather_rows(dev(index), out, picked)
+    assert torch.equal(picked.cpu(), table[tokens.long()][index.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, width, eps", [(1, 16, 1e-5), (3, 100, 1e-6), (64, 2048, 1e-5), (7, 4100, 1e-3)])
+def test_rms_norm_and_fused_add(dtype, rows, width, eps):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(1)
+    x = (torch.randn(rows, width) * 3).to(dtype)
+    u = torch.randn(rows, width).to(dtype)
+    w = 1 + 0.1 * torch.randn(width)
+    out = torch.empty(rows, width, dtype=dtype, device="cuda")
+    kernels.rms_norm(dev(x), dev(w), eps, out)
+    want = llama.rms_norm(x.double(), w.double(), eps)
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype))
+    res = dev(x.clone())
+    kernels.add_rms_norm(res, dev(u), dev(w), eps, out, res)
+    c = x.double() + u.double()
+    torch.testing.assert_close(out.cpu().double(), llama.rms_norm(c, w.double(), eps), **tol(dtype))
+    torch.testing.assert_close(res.cpu().double(), c, **tol(dtype))       # the residual holds the rounded sum
+    if dtype == torch.bfloat16:
+        assert torch.equal(res.cpu(), (x.float() + u.float()).to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, inter", [(1, 8), (5, 200), (33, 8192), (2, 333)])
+def test_silu_mul(dtype, rows, inter):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(2)
+    gu = (torch.randn(rows, 2 * inter) * 2).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device="cuda")
+    kernels.silu_mul(dev(gu), out)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    torch.testing.assert_close(out.cpu().double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 130, 33), (200, 96, 96), (17, 331, 72),
+                                     (2, 1000, 2048)])
+def test_gemm_f32(m, n, k):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(3)
+    a, w = torch.randn(m, k), torch.randn(n, k)
+    out = torch.empty(m, n, device="cuda")
+    kernels.gemm_f32_nt(dev(a), dev(w), out)
+    want = a.double() @ w.double().T
+    torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    # a row's result does not depend on the rows around it, nor a column's on the other columns
+    alone = torch.empty(1, n, device="cuda")
+    kernels.gemm_f32_nt(dev(a[m - 1:m].contiguous()), dev(w), alone)
+    assert torch.equal(alone[0], out[m - 1])
+    # strided operands (a column slice of a wider buffer)
+    wide = torch.randn(m, k + 5)
+    strided = torch.empty(m, n, device="cuda")
+    kernels.gemm_f32_nt(dev(wide)[:, 1:k + 1], dev(w), strided)
+    torch.testing.assert_close(strided.cpu().double(), wide[:, 1:k + 1].double() @ w.double().T, rtol=1e-5,
+                               atol=1e-5 * math.sqrt(k))
+
+
+def test_gemm_f32_is_true_32_bit():
+    """A product that a reduced-precision matrix mode (10-bit mantissa) would get visibly wrong."""
+    from tesseract_b200 import kernels
+
+    a = torch.full((4, 64), 1.0 + 2.0 ** -12)
+    w = torch.full((8, 64), 1.0 + 2.0 ** -13)
+    out = torch.empty(4, 8, device="cuda")
+    kernels.gemm_f32_nt(dev(a), dev(w), out)
+    want = 64 * (1.0 + 2.0 ** -12) * (1.0 + 2.0 ** -13)
+    assert abs(out[0, 0].item() - want) < 1e-5 and abs(64.0 - want) > 1e-2
+
+
+def paged_case(dtype, lengths, new, nh, nkv, d, page_size, seed, window=0):
+    """A batch of sequences with ``lengths[i]`` keys, the last ``new[i]`` of them being this step's rows."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-n // page_size) for n in lengths)
+    order = torch.randperm(total_pages + 3, generator=g)[:total_pages].tolist()     # scattered, non-identity pages
+    order = [p + 1 for p in order]
+    cache = torch.zeros(total_pages + 5, 2, nkv, page_size, d)
+    columns = max(-(-n // page_size) for n in lengths)
+    table = torch.zeros(len(lengths), columns, dtype=torch.int32)
+    ks, vs, at = [], [], 0
+    for s, n in enumerate(lengths):
+        k, v = torch.randn(n, nkv, d, generator=g), torch.randn(n, nkv, d, generator=g)
+        ks.append(k)
+        vs.append(v)
+        for logical in range(-(-n // page_size)):
+            page = order[at]
+            at += 1
+            table[s, logical] = page
+            span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+            cache[page, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+            cache[page, 1, :, :span.stop - span.start] = v[span].transpose(0, 1)
+    positions, seq_of_row = [], []
+    for s, (n, q) in enumerate(zip(lengths, new)):
+        positions += list(range(n - q, n))
+        seq_of_row += [s] * q
+    q = torch.randn(len(positions), nh, d, generator=g)
+    return dict(q=q.to(dtype), ks=[k.to(dtype) for k in ks], vs=[v.to(dtype) for v in vs], cache=cache.to(dtype),
+                table=table, positions=torch.tensor(positions, dtype=torch.int32),
+                seq_of_row=torch.tensor(seq_of_row, dtype=torch.int32), new=new, lengths=lengths)
+
+
+def plain_paged_attention(case, scale, window=None):
+    """Row by row with the plain whole-sequence attention: row at position p is row p of the full answer."""
+    outs = []
+    row = 0
+    for s, (n, new) in enumerate(zip(case["lengths"], case["new"])):
+        k, v = case["ks"][s].double(), case["vs"][s].double()
+        q_full = torch.zeros(n, case["q"].shape[1], case["q"].shape[2], dtype=torch.float64)
+        q_full[n - new:] = case["q"][row:row + new].double()
+        outs.append(llama.attention(q_full, k, v, scale, window)[n - new:])
+        row += new
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("lengths, new, nh, nkv, d, page_size, window", [
+    ([1], [1], 1, 1, 16, 16, 0),
+    ([17, 16, 15, 33], [1, 1, 1, 1], 6, 3, 48, 16, 0),            # decode rows, pages' edges
+    ([40, 129, 2, 64], [40, 5, 2, 17], 4, 2, 16, 16, 0),          # portions of prompts at any offset
+    ([300, 31], [1, 31], 3, 1, 32, 32, 0),                        # one kv head, larger pages
+    ([100, 70], [30, 1], 8, 8, 64, 16, 0),                        # no grouping
+    ([200, 90, 33], [16, 1, 33], 4, 2, 128, 64, 0),
+    ([150, 64, 10], [20, 1, 10], 4, 2, 32, 16, 24),               # sliding window
+    ([5], [5], 5, 5, 256, 16, 0),
+])
+def test_attention_rows(dtype, lengths, new, nh, nkv, d, page_size, window):
+    from tesseract_b200 import kernels
+
+    case = paged_case(dtype, lengths, new, nh, nkv, d, page_size, seed=len(lengths) + d)
+    scale = 1.0 / math.sqrt(d)
+    rows = case["q"].shape[0]
+    out = torch.empty(rows, nh * d, dtype=dtype, device="cuda")
+    kernels.attention_rows(dev(case["q"]).view(rows, nh * d), out, dev(case["cache"]), dev(case["positions"]),
+                           dev(case["seq_of_row"]), dev(case["table"]), nh, nkv, d, page_size, window, scale)
+    want = plain_paged_attention(case, scale, window or None).reshape(rows, nh * d)
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One query and one far key are scaled so that a single score stands out: the row must return that key's value,
+    wherever in the pages it lies (first key, a page's last slot, a page's first slot, the row's own position)."""
+    from tesseract_b200 import kernels
+
+    nh, nkv, d, page_size, n = 4, 2, 32, 16, 700
+    for target in (0, 15, 16, 351, 687, 699):
+        case = paged_case(dtype, [n], [1], nh, nkv, d, page_size, seed=target)
+        q = torch.zeros(1, nh, d)
+        q[0, :, 3] = 60.0
+        k = case["ks"][0].float()
+        k[:, :, 3] = 0.0
+        k[target, :, 3] = 8.0
+        page, slot = int(case["table"][0, target // page_size]), target % page_size
+        cache = case["cache"].float()
+        for logical in range(-(-n // page_size)):
+            p = int(case["table"][0, logical])
+            span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+            cache[p, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+        out = torch.empty(1, nh * d, dtype=dtype, device="cuda")
+        kernels.attention_rows(dev(q.to(dtype)).view(1, nh * d), out, dev(cache.to(dtype)), dev(case["positions"]),
+                               dev(case["seq_of_row"]), dev(case["table"]), nh, nkv, d, page_size, 0, 1.0)
+        want = case["vs"][0][target].float().repeat_interleave(nh // nkv, dim=0).reshape(1, nh * d)
+        torch.testing.assert_close(out.cpu().float(), want, rtol=1e-2, atol=1e-2)
+        assert cache[page, 0, 0, slot, 3] == 8.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, d, page_size, scaling", [
+    (4, 2, 16, 16, None), (3, 1, 32, 16, "llama3"), (6, 3, 48, 32, None), (2, 2, 128, 64, "llama3")])
+def test_rope_kv_write(dtype, nh, nkv, d, page_size, scaling):
+    from tesseract_b200 import kernels
+    from tesseract_b200.parts.rotary import rotary_inverse_frequencies
+
+    torch.manual_seed(5)
+    scaling = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                   original_max_position_embeddings=64) if scaling else None
+    inv_freq = rotary_inverse_frequencies(d, 500000.0 if scaling else 10000.0, scaling)
+    begins, news = [0, 37, 1000], [20, 1, 3]
+    positions = [p for b, n in zip(begins, news) for p in range(b, b + n)]
+    seq_of_row = [s for s, n in enumerate(news) for _ in range(n)]
+    rows = len(positions)
+    columns = max(-(-(b + n) // page_size) for b, n in zip(begins, news))
+    table = torch.zeros(3, columns, dtype=torch.int32)
+    page = 1
+    for s, (b, n) in enumerate(zip(begins, news)):
+        for logical in range(b // page_size, -(-(b + n) // page_size)):
+            table[s, logical] = page
+            page += 1
+    qkv = torch.randn(rows, (nh + 2 * nkv) * d).to(dtype)
+    cache = torch.zeros(page + 1, 2, nkv, page_size, d, dtype=dtype, device="cuda")
+    buf = dev(qkv.clone())
+    kernels.rope_kv_write(buf, dev(torch.tensor(positions, dtype=torch.int32)),
+                          dev(torch.tensor(seq_of_row, dtype=torch.int32)), dev(table),
+                          dev(torch.from_numpy(inv_freq)), cache, nh, nkv, d, page_size)
+    cos, sin = llama.rope_tables(positions, inv_freq)
+    q = qkv[:, :nh * d].double().view(rows, nh, d)
+    k = qkv[:, nh * d:(nh + nkv) * d].double().view(rows, nkv, d)
+    v = qkv[:, (nh + nkv) * d:].view(rows, nkv, d)
+    torch.testing.assert_close(buf.cpu()[:, :nh * d].double().view(rows, nh, d), llama.rotate_half(q, cos, sin),
+                               **tol(dtype))
+    k_rot = llama.rotate_half(k, cos, sin)
+    host = cache.cpu()
+    for r, (p, s) in enumerate(zip(positions, seq_of_row)):
+        pg, slot = int(table[s, p // page_size]), p % page_size
+        torch.testing.assert_close(host[pg, 0, :, slot].double(), k_rot[r], **tol(dtype))
+        assert torch.equal(host[pg, 1, :, slot], v[r])                  # values are stored as they are
+    assert torch.equal(buf.cpu()[:, nh * d:], qkv[:, nh * d:])          # k and v columns of the buffer are untouched
+    assert host[0].abs().sum() == 0                                      # nothing strayed into the scratch page
+
+
+@pytest.mark.parametrize("rows, vocab", [(1, 5), (4, 331), (3, 128256), (70, 1000)])
+def test_argmax_lowest_index_on_ties(rows, vocab):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(6)
+    logits = torch.randn(rows, vocab)
+    logits[0, vocab // 2] = 50.0
+    if vocab > 4:
+        logits[0, vocab - 1] = 50.0            # a tie: the lower index wins
+        logits[rows - 1, 1] = logits[rows - 1].max() + 1
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    kernels.argmax(dev(logits), out)
+    want = [int(np.flatnonzero(r == r.max())[0]) for r in logits.numpy()]
+    assert out.cpu().tolist() == want
+
+
+@pytest.mark.parametrize("vocab", [7, 384, 5000, 128256])
+def test_temperature_sampling_follows_the_inverse_cdf(vocab):
+    from tesseract_b200 import kernels
+
+    rng = np.random.default_rng(vocab)
+    rows = 24
+    logits = (rng.normal(size=(rows, vocab)) * 2).astype(np.float32)
+    temps = rng.uniform(0.3, 1.5, size=rows).astype(np.float32)
+    temps[3] = 0.0                              # a greedy row in the same call
+    draws = rng.uniform(size=rows)
+    draws[0], draws[1] = 0.0, 1.0 - 2.0 ** -53
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    kernels.sample(dev(torch.from_numpy(logits)), dev(torch.from_numpy(temps)), dev(torch.from_numpy(draws)), out)
+    got = out.cpu().tolist()
+    for r in range(rows):
+        want = llama.sample_in_token_order(logits[r], float(temps[r]), float(draws[r]))
+        if got[r] != want:
+            scaled = logits[r] * (np.float32(1.0) / temps[r])
+            cdf = np.cumsum(np.exp((scaled - scaled.max()).astype(np.float64)))
+            cdf /= cdf[-1]
+            assert abs(cdf[min(got[r], want)] - draws[r]) < 1e-9, f"row {r}: sampled {got[r]}, plain says {want}"
+    # the empirical distribution of one row follows softmax(l / T)
+    row = (rng.normal(size=(1, 16)) * 1.5).astype(np.float32)
+    n = 4000
+    many = torch.from_numpy(np.repeat(row, n, axis=0))
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    kernels.sample(dev(many), dev(torch.full((n,), 0.8)), dev(torch.from_numpy(rng.uniform(size=n))), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=16) / n
+    p = np.exp(row[0] / 0.8 - (row[0] / 0.8).max())
+    p /= p.sum()
+    assert np.abs(freq - p).max() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from tesseract_b200 import kernels
+
+    with pytest.raises(kernels.KernelError):
+        kernels.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))          # not on the device
+    with pytest.raises(kernels.KernelError):
+        kernels.rms_norm(torch.zeros(2, 8, device="cuda", dtype=torch.float16), torch.ones(8, device="cuda"), 1e-5,
+                         torch.zeros(2, 8, device="cuda", dtype=torch.float16))               # unsupported dtype
+    q = torch.zeros(1, 2 * 20, device="cuda")
+    with pytest.raises(kernels.KernelError):                                                   # head_dim 20
+        kernels.attention_rows(q, torch.empty_like(q), torch.zeros(2, 2, 1, 16, 20, device="cuda"),
+                               torch.zeros(1, dtype=torch.int32, device="cuda"),
+                               torch.zeros(1, dtype=torch.int32, device="cuda"),
+                               torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 2, 1, 20, 16, 0, 1.0)
