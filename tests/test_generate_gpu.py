@@ -104,8 +104,9 @@ def test_eos_stops_generation(model_folders):
     prompt = random_tokens(config["vocab_size"], 7, seed=1)
     llm = LLM(folder, dtype="float32", kv_capacity_tokens=256, max_running=2)
     free = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))[0].token_ids
-    stopped = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.0, stop_token_ids=[free[2]]))[0]
-    assert stopped.token_ids == free[:3] and stopped.finish_reason == "stop"
+    stop = free[-1]
+    stopped = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.0, stop_token_ids=[stop]))[0]
+    assert stopped.token_ids == free[:free.index(stop) + 1] and stopped.finish_reason == "stop"
 
 
 def test_command_line_generates(model_folders):
