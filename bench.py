@@ -1,0 +1,277 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200 (Llama 3.2 1B sizes, random weights).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 (device time, CUDA
+events around K decode steps through the engine's step function and device sampler);
+``e2e`` is the same through the scheduler that ``LLM.generate`` drives, with host token lists
+in and out; ``prefill`` is one 2,048-token prompt in one step; ``points`` holds decode at
+batch 1 and 64; ``roofline`` compares the bytes a decode step must read with the measured
+copy bandwidth.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Llama 3.2 1B)"
+
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "attention_bias": False, "mlp_bias": False, "num_hidden_layers": 16, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "max_position_embeddings": 131072, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "bos_token_id": 128000, "eos_token_id": [128001],
+}
+PROMPT_TOKENS = 2048
+CONTEXT = 4096
+PAGE_SIZE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, windows):
+        if self.proc is not None:
+            self.proc.terminate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for stamp, line in self.samples:
+            if windows and not any(a <= stamp <= b for a, b in windows):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "Leikoe/tesseract is a Rust crate (cargo/rustc are not in this image and cannot "
+                                     "be fetched offline) whose kernels are compiled at run time for sm_80 by cuTile; "
+                                     "it has no Python package to pip-install"}))
+    return 0
+
+
+def model_numbers(cfg, layers):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = h * (nh + 2 * nkv) * d + nh * d * h + 3 * h * i
+    matmul_params = layers * per_layer + v * h
+    weight_bytes = 2 * (matmul_params + (2 * layers + 1) * h)       # bfloat16; embedding shared with the head
+    kv_bytes_per_token = layers * 2 * nkv * d * 2
+    return {"layer_params": per_layer, "matmul_params": matmul_params, "weight_bytes": weight_bytes,
+            "kv_bytes_per_token": kv_bytes_per_token}
+
+
+def prefill_flops(cfg, layers, tokens, wanted_rows=1):
+    n = model_numbers(cfg, layers)
+    gemm = 2 * tokens * layers * n["layer_params"] + 2 * wanted_rows * cfg["vocab_size"] * cfg["hidden_size"]
+    attention = layers * 2 * tokens * tokens * cfg["head_dim"] * cfg["num_attention_heads"]    # causal: half of 4*T^2*d
+    return gemm + attention
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    from tesseract_b200 import LLM, SamplingParams, kernels
+    from tesseract_b200.engine import StepEntry
+    from tesseract_b200.weights.random_init import write_random_model
+
+    layers = args.layers or LLAMA_1B["num_hidden_layers"]
+    cfg = dict(LLAMA_1B, num_hidden_layers=layers)
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    windows = []
+    scratch = tempfile.TemporaryDirectory(prefix="tesseract_bench_")
+    write_random_model(scratch.name, cfg, seed=0)
+    max_batch = max(args.batch, 64)
+    llm = LLM(scratch.name, dtype="bfloat16", max_running=max_batch, max_batch_tokens=4096,
+              prefill_chunk_tokens=PROMPT_TOKENS, kv_capacity_tokens=max_batch * CONTEXT, page_size=PAGE_SIZE,
+              max_sequence_length=CONTEXT)
+    stepper, cache = llm.stepper, llm.stepper.cache
+    numbers = model_numbers(cfg, layers)
+    sampler.start()
+
+    def prompt():
+        return rng.integers(0, cfg["vocab_size"], PROMPT_TOKENS).tolist()
+
+    # ---------------------------------------------------------------- prefill: one 2,048-token prompt, one step
+    def prefill_once(rid):
+        assert cache.admit(rid)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tokens = prompt()
+        torch.cuda.synchronize()
+        start.record()
+        logits = stepper.step([StepEntry(rid, tokens, [PROMPT_TOKENS - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        cache.release(rid)
+        return start.elapsed_time(stop), logits
+
+    for k in range(3):
+        prefill_once(f"warm{k}")
+    t0 = time.time()
+    prefill_ms = sorted(prefill_once(f"pre{k}")[0] for k in range(5))[2]
+    windows.append((t0, time.time()))
+    flops = prefill_flops(cfg, layers, PROMPT_TOKENS)
+    prefill = {"value": PROMPT_TOKENS / (prefill_ms / 1e3), "tokens": PROMPT_TOKENS, "ms": prefill_ms,
+               "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "peak": f"{pk['source']} bf16"}
+
+    # ---------------------------------------------------------------- decode on the device clock
+    def decode_device(batch, steps, warmup):
+        ids = [f"d{batch}_{k}" for k in range(batch)]
+        last = []
+        for rid in ids:
+            assert cache.admit(rid)
+            stepper.step([StepEntry(rid, prompt(), [])])
+            last.append(int(rng.integers(0, cfg["vocab_size"])))
+        out = torch.empty(batch, dtype=torch.int32, device="cuda")
+
+        def one_step(tokens):
+            logits = stepper.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)])
+            kernels.argmax(logits, out)
+            return out.cpu().tolist()
+
+        for _ in range(warmup):
+            last = one_step(last)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        launches = kernels.launch_count
+        t0 = time.time()
+        start.record()
+        for _ in range(steps):
+            last = one_step(last)
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.time()))
+        launches = kernels.launch_count - launches
+        ms = start.elapsed_time(stop) / steps
+        context = cache.length(ids[0])
+        for rid in ids:
+            cache.release(rid)
+        return ms, launches, context
+
+    ms_step, launches, context = decode_device(args.batch, args.steps, args.warmup)
+    point_steps = max(8, min(args.steps, 64))
+    ms_b1, _, _ = decode_device(1, point_steps, args.warmup)
+    ms_b64, _, _ = decode_device(64, point_steps, args.warmup)
+    step_bytes = numbers["weight_bytes"] + args.batch * context * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+
+    # ---------------------------------------------------------------- end to end through the scheduler
+    params = SamplingParams(max_tokens=args.steps + args.warmup + 4, temperature=0.0, ignore_eos=True)
+    for _ in range(args.batch):
+        llm.scheduler.add_request(prompt(), params)
+    while any(r.computed_tokens < len(r.prompt) for r in llm.scheduler.requests.values()) or llm.scheduler.waiting:
+        llm.scheduler.step()
+    for _ in range(args.warmup):
+        llm.scheduler.step()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    produced = 0
+    for _ in range(args.steps):
+        produced += len(llm.scheduler.step().new_tokens)
+    torch.cuda.synchronize()
+    e2e_seconds = time.time() - t0
+    windows.append((t0, time.time()))
+    for rid in list(llm.scheduler.requests):
+        llm.scheduler.cancel(rid)
+    pages = -(-context // PAGE_SIZE)
+    h2d = 4 * (args.batch * 6 + 1 + args.batch * pages)
+    e2e = {"value": produced / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * args.batch}
+
+    clocks = sampler.stop(windows)
+    value = args.batch / (ms_step / 1e3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
+        "config": {"model": "Llama-3.2-1B sizes", "layers": layers, "layers_of_model": LLAMA_1B["num_hidden_layers"],
+                   "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
+                   "decode_context": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (2.47 GB of weights read every step)"},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "of": pk["source"]},
+        "points": {"decode_b1": 1 / (ms_b1 / 1e3), "decode_b64": 64 / (ms_b64 / 1e3)},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "impl": "ours",
+    }
+    print(json.dumps(line))
+    scratch.cleanup()
+    return 0
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
+        return 2
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

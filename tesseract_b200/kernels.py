@@ -29,7 +29,12 @@ class KernelError(RuntimeError):
     pass
 
 
+launch_count = 0     # kernels of this package launched so far (the benchmark reports the difference)
+
+
 def _check(status: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if status == 0:
         return
     if status < 0:
