@@ -1,0 +1,533 @@
+// Tensor-core paged attention for bfloat16: prompt portions (tiles of query rows) and decode
+// (split over the keys), over the same block tables and cache pages.
+//
+// Math per query row, as in the plain kernel and the reference (src/cuda/kernels.rs:447-562):
+//   s_j = (q . k_j) * scale for keys j in [max(0, p - window + 1), p], streaming softmax in
+//   32-bit, probabilities rounded to bfloat16 for P.V, 32-bit accumulator, out = acc / max(l, 1e-8).
+//
+// Layout of the work.  The G = num_heads / num_kv_heads query heads that share a kv head are
+// folded into the row dimension of a tile: row r of a sequence's tile space is query position
+// r / G, head (kv_head * G + r % G), so one pass over a kv head's keys serves the whole group.
+//   tb_attention_tiles   : one CTA per (64-row tile, kv head, sequence); its 4 warps own 16 rows
+//                          each and share every K/V tile.  For sequences with more than 16 rows.
+//   tb_attention_decode  : sequences with at most 16 rows (decode, and tiny portions); one CTA per
+//                          (key split, kv head, sequence); its 4 warps share the 16 rows and own 16
+//                          keys of every 64-key tile, are merged in shared memory, and the splits are
+//                          merged by tb_attention_combine from 32-bit partials in scratch memory.
+// K/V tiles come in through cp.async (16-byte chunks, XOR-swizzled in shared memory, double
+// buffered); the products are mma.sync.m16n8k16 bf16 with fragments from ldmatrix.
+// head_dim may be any multiple of 16 up to 256: tiles are zero-padded to 32/64/128/256 columns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMasked = -1.0e30f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bf16 tile, XOR-swizzled so that the
+// eight rows an ldmatrix reads fall into distinct bank groups.
+template <int D>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+    constexpr int CH = D / 8;
+    const int key = (CH >= 8) ? (row & 7) : ((row >> 1) & (CH - 1));
+    return (uint32_t)(row * (D * 2) + ((chunk ^ key) << 4));
+}
+
+struct AttnParams {
+    const __nv_bfloat16* q;      // [rows, num_heads*head_dim], row stride q_stride
+    __nv_bfloat16* out;          // [rows, num_heads*head_dim], row stride out_stride
+    const __nv_bfloat16* cache;  // [page][K|V][kv_head][page_size][head_dim]
+    const int* row_start;        // [R+1]
+    const int* seq_begin;        // [R] position of the sequence's first new row
+    const int* block_table;      // [R, bt_stride]
+    float* part_o;               // [splits][rows][num_heads][D]   (decode only)
+    float* part_ml;              // [splits][rows][num_heads][2]
+    int64_t q_stride, out_stride;
+    int bt_stride, total_rows;
+    int num_heads, num_kv_heads, group, head_dim, page_shift, page_size, window, splits;
+    float scale_log2;            // scale * log2(e): scores are kept in the base-2 domain
+};
+
+// Copies rows [key0, key0 + ROWS) of one kv head's K (which = 0) or V (which = 1) into a swizzled tile.
+template <int D, int ROWS>
+__device__ __forceinline__ void load_kv_tile(uint32_t tile, const AttnParams& p, const int* table, int kv_head,
+                                             int which, int key0, int key_lo, int key_hi) {
+    constexpr int CH = D / 8;
+    const int64_t head_block = (int64_t)p.page_size * p.head_dim;
+    const int64_t page_block = 2 * (int64_t)p.num_kv_heads * head_block;
+    const __nv_bfloat16* base = p.cache + ((int64_t)which * p.num_kv_heads + kv_head) * head_block;
+    for (int idx = threadIdx.x; idx < ROWS * CH; idx += kThreads) {
+        const int r = idx / CH, c = idx % CH;
+        const int key = key0 + r;
+        const bool ok = key >= key_lo && key <= key_hi && c * 8 < p.head_dim;
+        const __nv_bfloat16* src = base;
+        if (ok) {
+            const int page = table[key >> p.page_shift];
+            src = base + (int64_t)page * page_block + (int64_t)(key & (p.page_size - 1)) * p.head_dim + c * 8;
+        }
+        cp_async16(tile + tile_offset<D>(r, c), src, ok);
+    }
+}
+
+// Copies ROWS folded query rows starting at tile-space row r0 of a sequence into a swizzled tile.
+template <int D, int ROWS>
+__device__ __forceinline__ void load_q_tile(uint32_t tile, const AttnParams& p, int first_row, int kv_head, int r0,
+                                            int n_rows) {
+    constexpr int CH = D / 8;
+    for (int idx = threadIdx.x; idx < ROWS * CH; idx += kThreads) {
+        const int r = idx / CH, c = idx % CH;
+        const int fr = r0 + r;
+        const bool ok = fr < n_rows && c * 8 < p.head_dim;
+        const __nv_bfloat16* src = p.q;
+        if (ok) {
+            const int qpos = fr / p.group, g = fr - qpos * p.group;
+            src = p.q + (int64_t)(first_row + qpos) * p.q_stride + (int64_t)(kv_head * p.group + g) * p.head_dim + c * 8;
+        }
+        cp_async16(tile + tile_offset<D>(r, c), src, ok);
+    }
+}
+
+// One warp: 16 query rows (tile rows qrow0..qrow0+15) against NK keys (tile rows krow0..krow0+NK-1, absolute
+// keys key_base..).  Updates the running maximum m, the per-thread partial sum l and the accumulator o of the
+// thread's two rows (lane/4 and lane/4 + 8).  pos[i] is the absolute position of row i (-1: no such row) and
+// lo[i] its first visible key.
+template <int D, int NK>
+__device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t k_tile, uint32_t v_tile, int krow0,
+                                            int key_base, const int (&pos)[2], const int (&lo)[2], float scale_log2,
+                                            float (&o)[D / 8][4], float (&m)[2], float (&l)[2]) {
+    const int lane = threadIdx.x & 31;
+    float s[NK / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < NK / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_tile + tile_offset<D>(qrow0 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+        for (int np = 0; np < NK / 16; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_tile + tile_offset<D>(krow0 + np * 16 + (lane & 7) + ((lane >> 4) << 3),
+                                                   ks * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s[2 * np], a, b[0], b[1]);
+            mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+        }
+    }
+
+    // scale, mask, running maximum
+    float block_max[2] = {kMasked, kMasked};
+#pragma unroll
+    for (int nt = 0; nt < NK / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1;
+            const int key = key_base + nt * 8 + 2 * (lane & 3) + (e & 1);
+            const bool valid = key >= lo[i] && key <= pos[i];
+            s[nt][e] = valid ? s[nt][e] * scale_log2 : kMasked;
+            block_max[i] = fmaxf(block_max[i], s[nt][e]);
+        }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        block_max[i] = fmaxf(block_max[i], __shfl_xor_sync(0xffffffffu, block_max[i], 1));
+        block_max[i] = fmaxf(block_max[i], __shfl_xor_sync(0xffffffffu, block_max[i], 2));
+        const float m_new = fmaxf(m[i], block_max[i]);
+        corr[i] = exp2f(m[i] - m_new);
+        m[i] = m_new;
+        l[i] *= corr[i];
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        o[dt][0] *= corr[0];
+        o[dt][1] *= corr[0];
+        o[dt][2] *= corr[1];
+        o[dt][3] *= corr[1];
+    }
+    // probabilities (masked lanes are exactly zero), 32-bit row sums, bfloat16 P fragments
+    uint32_t pa[NK / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < NK / 8; ++nt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1;
+            pv[e] = (s[nt][e] > 0.5f * kMasked) ? exp2f(s[nt][e] - m[i]) : 0.0f;
+            l[i] += pv[e];
+        }
+        pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+    }
+    // O += P . V
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_tile + tile_offset<D>(krow0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3),
+                                                         dp * 2 + (lane >> 4)));
+            mma_bf16(o[2 * dp], pa[kk], b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], pa[kk], b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prompt portions: one CTA per (64-row tile, kv head, sequence).
+template <int D, int BN>
+__global__ void __launch_bounds__(kThreads) attention_tiles_kernel(const AttnParams p) {
+    constexpr int BM = 64;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int seq = blockIdx.z, kv_head = blockIdx.y, r0 = blockIdx.x * BM;
+    const int first_row = p.row_start[seq];
+    const int q_len = p.row_start[seq + 1] - first_row;
+    const int n_rows = q_len * p.group;
+    if (n_rows <= 16 || r0 >= n_rows) return;  // short sequences belong to the decode kernel
+    const int begin = p.seq_begin[seq];
+    const int* table = p.block_table + (int64_t)seq * p.bt_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t q_tile = smem_u32(smem);
+    const uint32_t kv_tiles = q_tile + BM * D * 2;  // [stage][K|V][BN][D]
+    constexpr uint32_t kTileBytes = BN * D * 2;
+
+    const int last_row = min(n_rows, r0 + BM) - 1;
+    const int key_hi = begin + last_row / p.group;
+    const int key_lo = p.window > 0 ? max(0, begin + r0 / p.group - p.window + 1) : 0;
+    const int kb_first = key_lo / BN, kb_last = key_hi / BN;
+
+    load_q_tile<D, BM>(q_tile, p, first_row, kv_head, r0, n_rows);
+    load_kv_tile<D, BN>(kv_tiles, p, table, kv_head, 0, kb_first * BN, key_lo, key_hi);
+    load_kv_tile<D, BN>(kv_tiles + kTileBytes, p, table, kv_head, 1, kb_first * BN, key_lo, key_hi);
+    cp_async_commit();
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int fr = r0 + warp * 16 + (lane >> 2) + i * 8;
+        pos[i] = fr < n_rows ? begin + fr / p.group : -1;
+        lo[i] = p.window > 0 ? max(0, pos[i] - p.window + 1) : 0;
+    }
+    float o[D / 8][4], m[2] = {kMasked, kMasked}, l[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+    // rows of this warp span positions [warp_lo_pos, warp_hi_pos]; key blocks wholly outside need no math
+    const int warp_first = r0 + warp * 16;
+    const bool warp_active = warp_first < n_rows;
+    const int warp_hi_key = begin + (min(n_rows, warp_first + 16) - 1) / p.group;
+
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int stage = (kb - kb_first) & 1;
+        if (kb < kb_last) {
+            const uint32_t next = kv_tiles + (stage ^ 1) * 2 * kTileBytes;
+            load_kv_tile<D, BN>(next, p, table, kv_head, 0, (kb + 1) * BN, key_lo, key_hi);
+            load_kv_tile<D, BN>(next + kTileBytes, p, table, kv_head, 1, (kb + 1) * BN, key_lo, key_hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (warp_active && kb * BN <= warp_hi_key) {
+            const uint32_t cur = kv_tiles + stage * 2 * kTileBytes;
+            warp_attend<D, BN>(q_tile, warp * 16, cur, cur + kTileBytes, 0, kb * BN, pos, lo, p.scale_log2, o, m, l);
+        }
+        __syncthreads();  // everyone is done with this stage before the next prefetch overwrites it
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        if (pos[i] < 0) continue;
+        const int fr = r0 + warp * 16 + (lane >> 2) + i * 8;
+        const int qpos = fr / p.group, g = fr - qpos * p.group;
+        const float inv = 1.0f / fmaxf(l[i], 1.0e-8f);
+        __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride +
+                             (int64_t)(kv_head * p.group + g) * p.head_dim;
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            const int col = dt * 8 + 2 * (lane & 3);
+            if (col < p.head_dim)
+                *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[dt][2 * i] * inv, o[dt][2 * i + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode and tiny portions (at most 16 folded rows): one CTA per (key split, kv head, sequence).
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
+    constexpr int BN = 64;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int split = blockIdx.x, kv_head = blockIdx.y, seq = blockIdx.z;
+    const int first_row = p.row_start[seq];
+    const int q_len = p.row_start[seq + 1] - first_row;
+    const int n_rows = q_len * p.group;
+    if (n_rows > 16 || n_rows == 0) return;
+    const int begin = p.seq_begin[seq];
+    const int* table = p.block_table + (int64_t)seq * p.bt_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t q_tile = smem_u32(smem);
+    const uint32_t kv_tiles = q_tile + 16 * D * 2;
+    constexpr uint32_t kTileBytes = BN * D * 2;
+
+    const int key_hi = begin + q_len - 1;
+    const int key_lo = p.window > 0 ? max(0, begin - p.window + 1) : 0;
+    const int kb_first = key_lo / BN, kb_end = key_hi / BN + 1;
+    const int per_split = (kb_end - kb_first + p.splits - 1) / p.splits;
+    const int b0 = kb_first + split * per_split;
+    const int b1 = min(kb_end, b0 + per_split);
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int fr = (lane >> 2) + i * 8;
+        pos[i] = fr < n_rows ? begin + fr / p.group : -1;
+        lo[i] = p.window > 0 ? max(0, pos[i] - p.window + 1) : 0;
+    }
+    float o[D / 8][4], m[2] = {kMasked, kMasked}, l[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+
+    if (b0 < b1) {
+        load_q_tile<D, 16>(q_tile, p, first_row, kv_head, 0, n_rows);
+        load_kv_tile<D, BN>(kv_tiles, p, table, kv_head, 0, b0 * BN, key_lo, key_hi);
+        load_kv_tile<D, BN>(kv_tiles + kTileBytes, p, table, kv_head, 1, b0 * BN, key_lo, key_hi);
+        cp_async_commit();
+        for (int kb = b0; kb < b1; ++kb) {
+            const int stage = (kb - b0) & 1;
+            if (kb + 1 < b1) {
+                const uint32_t next = kv_tiles + (stage ^ 1) * 2 * kTileBytes;
+                load_kv_tile<D, BN>(next, p, table, kv_head, 0, (kb + 1) * BN, key_lo, key_hi);
+                load_kv_tile<D, BN>(next + kTileBytes, p, table, kv_head, 1, (kb + 1) * BN, key_lo, key_hi);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (kb * BN + warp * 16 <= key_hi) {
+                const uint32_t cur = kv_tiles + stage * 2 * kTileBytes;
+                warp_attend<D, 16>(q_tile, 0, cur, cur + kTileBytes, warp * 16, kb * BN + warp * 16, pos, lo,
+                                   p.scale_log2, o, m, l);
+            }
+            __syncthreads();
+        }
+    }
+    // merge the four warps (each saw a quarter of the keys) through shared memory
+    float* sm_m = reinterpret_cast<float*>(smem);             // [warps][16]
+    float* sm_l = sm_m + kWarps * 16;                         // [warps][16]
+    float* sm_o = sm_l + kWarps * 16;                         // [warps][16][D]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        const int r = (lane >> 2) + i * 8;
+        if ((lane & 3) == 0) {
+            sm_m[warp * 16 + r] = m[i];
+            sm_l[warp * 16 + r] = l[i];
+        }
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            const int col = dt * 8 + 2 * (lane & 3);
+            sm_o[(warp * 16 + r) * D + col] = o[dt][2 * i];
+            sm_o[(warp * 16 + r) * D + col + 1] = o[dt][2 * i + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rows * D; idx += kThreads) {
+        const int r = idx / D, col = idx - r * D;
+        float big = kMasked;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) big = fmaxf(big, sm_m[w * 16 + r]);
+        float acc = 0.0f, sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float wgt = exp2f(sm_m[w * 16 + r] - big);
+            acc += wgt * sm_o[(w * 16 + r) * D + col];
+            sum += wgt * sm_l[w * 16 + r];
+        }
+        const int qpos = r / p.group, g = r - qpos * p.group;
+        const int head = kv_head * p.group + g;
+        const int row = first_row + qpos;
+        if (p.splits == 1) {
+            if (col < p.head_dim)
+                p.out[(int64_t)row * p.out_stride + (int64_t)head * p.head_dim + col] =
+                    __float2bfloat16_rn(acc / fmaxf(sum, 1.0e-8f));
+        } else {
+            const int64_t slot = ((int64_t)split * p.total_rows + row) * p.num_heads + head;
+            p.part_o[slot * D + col] = acc;
+            if (col == 0) {
+                p.part_ml[slot * 2] = big;
+                p.part_ml[slot * 2 + 1] = sum;
+            }
+        }
+    }
+}
+
+// Merges the splits of the decode kernel: one block per (sequence, head).
+template <int D>
+__global__ void attention_combine_kernel(const AttnParams p) {
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int first_row = p.row_start[seq];
+    const int q_len = p.row_start[seq + 1] - first_row;
+    if (q_len * p.group > 16) return;
+    for (int qpos = 0; qpos < q_len; ++qpos) {
+        const int row = first_row + qpos;
+        float big = kMasked;
+        for (int s = 0; s < p.splits; ++s) {
+            const int64_t slot = ((int64_t)s * p.total_rows + row) * p.num_heads + head;
+            if (p.part_ml[slot * 2 + 1] > 0.0f) big = fmaxf(big, p.part_ml[slot * 2]);
+        }
+        for (int col = threadIdx.x; col < p.head_dim; col += blockDim.x) {
+            float acc = 0.0f, sum = 0.0f;
+            for (int s = 0; s < p.splits; ++s) {
+                const int64_t slot = ((int64_t)s * p.total_rows + row) * p.num_heads + head;
+                const float ls = p.part_ml[slot * 2 + 1];
+                if (ls > 0.0f) {  // an empty split left nothing behind
+                    const float wgt = exp2f(p.part_ml[slot * 2] - big);
+                    acc += wgt * p.part_o[slot * D + col];
+                    sum += wgt * ls;
+                }
+            }
+            p.out[(int64_t)row * p.out_stride + (int64_t)head * p.head_dim + col] =
+                __float2bfloat16_rn(acc / fmaxf(sum, 1.0e-8f));
+        }
+    }
+}
+
+template <int D>
+int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_tiles, int run_decode,
+               cudaStream_t stream) {
+    constexpr int BN = D <= 128 ? 64 : 32;
+    if (run_tiles) {
+        const size_t smem = (size_t)64 * D * 2 + (size_t)2 * 2 * BN * D * 2;
+        auto kernel = attention_tiles_kernel<D, BN>;
+        if (smem > 48 * 1024) {
+            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (err != cudaSuccess) return (int)err;
+        }
+        dim3 grid((max_rows_per_seq + 63) / 64, p.num_kv_heads, num_seqs);
+        kernel<<<grid, kThreads, smem, stream>>>(p);
+        if (int status = tb_launch_status()) return status;
+    }
+    if (run_decode) {
+        const size_t tiles = (size_t)16 * D * 2 + (size_t)2 * 2 * 64 * D * 2;
+        const size_t merge = (size_t)(2 * kWarps * 16 + kWarps * 16 * D) * sizeof(float);
+        const size_t smem = tiles > merge ? tiles : merge;
+        auto kernel = attention_decode_kernel<D>;
+        if (smem > 48 * 1024) {
+            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (err != cudaSuccess) return (int)err;
+        }
+        dim3 grid(p.splits, p.num_kv_heads, num_seqs);
+        kernel<<<grid, kThreads, smem, stream>>>(p);
+        if (int status = tb_launch_status()) return status;
+        if (p.splits > 1) {
+            dim3 cgrid(num_seqs, p.num_heads);
+            attention_combine_kernel<D><<<cgrid, 64, 0, stream>>>(p);
+            if (int status = tb_launch_status()) return status;
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+
+// Column count of the zero-padded tiles (and of the partial accumulators) for a head size.
+TB_EXPORT int tb_attention_mma_padded_dim(int head_dim) {
+    if (head_dim <= 0 || head_dim > 256 || head_dim % 16 != 0) return TB_ERR_BAD_SIZE;
+    return head_dim <= 32 ? 32 : head_dim <= 64 ? 64 : head_dim <= 128 ? 128 : 256;
+}
+
+// Attention of every row of a packed batch over its sequence's cached keys (bfloat16).
+//   run_tiles  : launch the tile kernel (sequences with more than 16 folded rows)
+//   run_decode : launch the split kernel (sequences with at most 16 folded rows) with `splits` key splits;
+//                splits > 1 needs scratch: part_o float[splits * total_rows * num_heads * padded_dim],
+//                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o.
+TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
+                               const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
+                               int num_seqs, int total_rows, int max_rows_per_seq, int num_heads, int num_kv_heads,
+                               int head_dim, int page_size, int window, float scale, int run_tiles, int run_decode,
+                               int splits, float* part_o, float* part_ml, int64_t scratch_floats,
+                               cudaStream_t stream) {
+    if (num_seqs == 0 || total_rows == 0) return 0;
+    const int padded = tb_attention_mma_padded_dim(head_dim);
+    if (padded < 0) return padded;
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return TB_ERR_BAD_SIZE;
+    if (page_size < 8 || (page_size & (page_size - 1)) != 0) return TB_ERR_BAD_SIZE;
+    if (num_seqs > 65535 || num_kv_heads > 65535 || num_heads > 65535) return TB_ERR_BAD_SIZE;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || (q_stride % 8) != 0) return TB_ERR_BAD_ALIGN;
+    if (splits < 1) splits = 1;
+    if (run_decode && splits > 1) {
+        const int64_t need = (int64_t)splits * total_rows * num_heads * padded;
+        if (part_o == nullptr || part_ml == nullptr || need > scratch_floats) return -5;
+    }
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.out = (__nv_bfloat16*)out;
+    p.cache = (const __nv_bfloat16*)cache;
+    p.row_start = row_start;
+    p.seq_begin = seq_begin;
+    p.block_table = block_table;
+    p.part_o = part_o;
+    p.part_ml = part_ml;
+    p.q_stride = q_stride;
+    p.out_stride = out_stride;
+    p.bt_stride = bt_stride;
+    p.total_rows = total_rows;
+    p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads;
+    p.group = num_heads / num_kv_heads;
+    p.head_dim = head_dim;
+    p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window;
+    p.splits = splits;
+    p.scale_log2 = scale * kLog2e;
+    const int max_folded = max_rows_per_seq * p.group;
+    switch (padded) {
+        case 32: return launch_all<32>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
+        case 64: return launch_all<64>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
+        case 128: return launch_all<128>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
+        default: return launch_all<256>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
+    }
+}

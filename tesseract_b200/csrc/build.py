@@ -34,6 +34,7 @@ SOURCES: Dict[str, List[str]] = {
     "norm": [],
     "rope_cache": [],
     "attention_rows": [],
+    "attention_mma": [],
     "gemm_f32": [],
     "sampling": [],
 }

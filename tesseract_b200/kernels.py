@@ -223,3 +223,61 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     _check(lib.tb_sample(_ptr(logits), _i64(logits.stride(0)), _ptr(temperature), _ptr(uniform), _ptr(out),
                          _i32(rows), _i32(logits.shape[1]), _stream()), "sample")
     return out
+
+
+_SM_COUNT = 148
+_attention_scratch = {}
+
+
+def _scratch(device, name: str, floats: int) -> torch.Tensor:
+    """A float32 work buffer that only ever grows (shared by all layers; they run one after another)."""
+    key = (device, name)
+    buf = _attention_scratch.get(key)
+    if buf is None or buf.numel() < floats:
+        buf = torch.empty(max(floats, 1024), dtype=torch.float32, device=device)
+        _attention_scratch[key] = buf
+    return buf
+
+
+def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
+    """How many key splits the decode kernel uses: enough CTAs for every SM, at least two 64-key tiles each."""
+    ctas = max(1, num_seqs * num_kv_heads)
+    want = -(-2 * _SM_COUNT // ctas)
+    blocks = -(-max_context // 64)
+    return max(1, min(want, -(-blocks // 2), 64))
+
+
+def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,
+                  seq_begin: torch.Tensor, block_table: torch.Tensor, num_seqs: int, max_new: int, num_heads: int,
+                  num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, run_tiles: bool,
+                  run_decode: bool, splits: int) -> torch.Tensor:
+    """Tensor-core paged attention (bfloat16).  Sequences with more than 16 folded rows
+    (``new tokens * num_heads / num_kv_heads``) go through the tile kernel, the others through the split kernel."""
+    _cuda(q, out, cache, row_start, seq_begin, block_table)
+    rows = q.shape[0]
+    _need(q.dtype == out.dtype == cache.dtype == torch.bfloat16, "attention_mma takes bfloat16")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim and out.shape == q.shape,
+          "q/out layout")
+    _need(row_start.dtype == torch.int32 and seq_begin.dtype == torch.int32 and block_table.dtype == torch.int32,
+          "row_start, seq_begin and block_table must be int32")
+    _need(row_start.numel() >= num_seqs + 1 and seq_begin.numel() >= num_seqs, "sequence metadata too short")
+    _need(block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[0] >= num_seqs, "block table")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache layout")
+    lib = load_library("attention_mma")
+    padded = lib.tb_attention_mma_padded_dim(_i32(head_dim))
+    if padded < 0:
+        raise KernelError(f"attention_mma: head_dim {head_dim} is not a multiple of 16 up to 256")
+    part_o = part_ml = None
+    capacity = 0
+    if run_decode and splits > 1:
+        capacity = splits * rows * num_heads * padded
+        part_o = _scratch(q.device, "part_o", capacity)
+        part_ml = _scratch(q.device, "part_ml", splits * rows * num_heads * 2)
+        capacity = part_o.numel()
+    _check(lib.tb_attention_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                _ptr(row_start), _ptr(seq_begin), _ptr(block_table), _i32(block_table.stride(0)),
+                                _i32(num_seqs), _i32(rows), _i32(max_new), _i32(num_heads), _i32(num_kv_heads),
+                                _i32(head_dim), _i32(page_size), _i32(window), _f32(scale),
+                                _i32(1 if run_tiles else 0), _i32(1 if run_decode else 0), _i32(splits),
+                                _ptr(part_o), _ptr(part_ml), _i64(capacity), _stream()), "attention_mma")
+    return out

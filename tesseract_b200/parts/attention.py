@@ -87,6 +87,16 @@ class Attention(Mixer):
         return self.o_proj.forward(attended)
 
     def _attend(self, q, out, cache: CacheBinding, ctx: StepContext, group) -> None:
-        kernels.attention_rows(q, out, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
-                               self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
-                               self.scale)
+        if self.runtime.is_float32:
+            # the 32-bit path: one warp per (row, head), a fixed order of every reduction
+            kernels.attention_rows(q, out, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                   self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
+                                   self.scale)
+            return
+        fold = self.num_heads // self.num_kv_heads
+        long_seqs = any(n * fold > 16 for n in ctx.host_new)
+        short_seqs = any(n * fold <= 16 for n in ctx.host_new)
+        splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context) if short_seqs else 1
+        kernels.attention_mma(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table, ctx.num_seqs,
+                              ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
+                              self.window, self.scale, long_seqs, short_seqs, splits)

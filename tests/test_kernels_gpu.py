@@ -311,3 +311,70 @@ def test_kernels_refuse_what_they_cannot_do():
                                torch.zeros(1, dtype=torch.int32, device="cuda"),
                                torch.zeros(1, dtype=torch.int32, device="cuda"),
                                torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 2, 1, 20, 16, 0, 1.0)
+
+
+def run_attention_mma(case, nh, nkv, d, page_size, window, scale, splits):
+    from tesseract_b200 import kernels
+
+    rows = case["q"].shape[0]
+    new, lengths = case["new"], case["lengths"]
+    row_start = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32)
+    seq_begin = torch.tensor([n - q for n, q in zip(lengths, new)], dtype=torch.int32)
+    fold = nh // nkv
+    out = torch.full((rows, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.attention_mma(dev(case["q"]).view(rows, nh * d), out, dev(case["cache"]), dev(row_start), dev(seq_begin),
+                          dev(case["table"]), len(lengths), max(new), nh, nkv, d, page_size, window, scale,
+                          any(n * fold > 16 for n in new), any(n * fold <= 16 for n in new), splits)
+    return out
+
+
+@pytest.mark.parametrize("lengths, new, nh, nkv, d, page_size, window, splits", [
+    ([1], [1], 1, 1, 16, 16, 0, 1),
+    ([17, 16, 15, 33], [1, 1, 1, 1], 6, 3, 48, 16, 0, 1),             # decode rows at pages' edges
+    ([17, 16, 15, 333], [1, 1, 1, 1], 6, 3, 48, 16, 0, 3),            # the same, keys split three ways
+    ([700, 64, 65, 1], [1, 1, 1, 1], 32, 8, 64, 16, 0, 8),            # more splits than some sequences have tiles
+    ([40, 129, 2, 64], [40, 5, 2, 17], 4, 2, 16, 16, 0, 2),           # long and short sequences in one batch
+    ([300, 31], [1, 31], 3, 1, 32, 32, 0, 4),                          # one kv head, larger pages
+    ([100, 70], [30, 1], 8, 8, 64, 16, 0, 1),                          # no grouping
+    ([200, 90, 33], [16, 1, 33], 4, 2, 128, 64, 0, 2),
+    ([150, 64, 10, 200], [20, 1, 10, 1], 4, 2, 32, 16, 24, 2),        # sliding window
+    ([5, 300], [5, 2], 5, 5, 256, 16, 0, 2),
+    ([260, 70], [200, 3], 2, 1, 80, 16, 0, 1),                         # a head size between the padded widths
+    ([513], [513], 32, 8, 64, 16, 0, 1),                               # many tiles of one long prompt
+    ([90, 5], [2, 1], 32, 2, 96, 16, 0, 2),                            # a group of 16 heads: one token fills a tile
+    ([90, 50], [2, 1], 40, 2, 16, 16, 0, 1),                           # a group of 20: decode goes to the tile kernel
+])
+def test_attention_mma(lengths, new, nh, nkv, d, page_size, window, splits):
+    case = paged_case(torch.bfloat16, lengths, new, nh, nkv, d, page_size, seed=sum(lengths) + d)
+    scale = 1.0 / math.sqrt(d)
+    out = run_attention_mma(case, nh, nkv, d, page_size, window, scale, splits)
+    rows = case["q"].shape[0]
+    want = plain_paged_attention(case, scale, window or None).reshape(rows, nh * d)
+    torch.testing.assert_close(out.cpu().double(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_mma_finds_one_far_key_among_hundreds():
+    nh, nkv, d, page_size, n = 8, 2, 64, 16, 1500
+    for target in (0, 15, 16, 63, 64, 777, 1487, 1499):
+        for new, splits in ((1, 1), (1, 7), (40, 1)):
+            case = paged_case(torch.bfloat16, [n], [new], nh, nkv, d, page_size, seed=target + new)
+            q = torch.zeros(new, nh, d)
+            q[:, :, 3] = 60.0
+            case["q"] = q.to(torch.bfloat16)
+            k = case["ks"][0].float()
+            k[:, :, 3] = 0.0
+            k[target, :, 3] = 8.0
+            case["ks"][0] = k.to(torch.bfloat16)
+            cache = case["cache"].float()
+            for logical in range(-(-n // page_size)):
+                pg = int(case["table"][0, logical])
+                span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+                cache[pg, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+            case["cache"] = cache.to(torch.bfloat16)
+            out = run_attention_mma(case, nh, nkv, d, page_size, 0, 1.0, splits)
+            # every row at or after the target returns the target's value; earlier rows do not see it
+            v = case["vs"][0][target].float().repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+            first_pos = n - new
+            for r in range(new):
+                if first_pos + r >= target:
+                    torch.testing.assert_close(out[r].cpu().float(), v, rtol=1e-2, atol=1e-2)
