@@ -28,6 +28,11 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "-Xcudafe", "--diag_suppress=177"]
 
+# Files a source includes besides common.cuh and its own header (they count for its hash).
+INCLUDES: Dict[str, List[str]] = {
+    "attention_noalloc": ["attention_mma.cu", "attention_noalloc.h"],
+}
+
 # Every source file, with the extra flags it needs.
 SOURCES: Dict[str, List[str]] = {
     "elementwise": [],
@@ -35,6 +40,7 @@ SOURCES: Dict[str, List[str]] = {
     "rope_cache": [],
     "attention_rows": [],
     "attention_mma": [],
+    "attention_noalloc": [],
     "gemm_f32": [],
     "sampling": [],
 }
@@ -86,10 +92,11 @@ def _digest(name: str, flags: Sequence[str]) -> str:
     for path in (os.path.join(CSRC_DIR, name + ".cu"), os.path.join(CSRC_DIR, "common.cuh")):
         with open(path, "rb") as handle:
             h.update(handle.read())
-    extra = os.path.join(CSRC_DIR, name + ".cuh")
-    if os.path.exists(extra):
-        with open(extra, "rb") as handle:
-            h.update(handle.read())
+    for extra in [name + ".cuh"] + INCLUDES.get(name, []):
+        extra = os.path.join(CSRC_DIR, extra)
+        if os.path.exists(extra):
+            with open(extra, "rb") as handle:
+                h.update(handle.read())
     h.update(" ".join(list(ARCH_FLAGS) + list(BASE_FLAGS) + list(flags)).encode())
     return h.hexdigest()[:16]
 
