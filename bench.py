@@ -140,7 +140,7 @@ def run_ours(args):
     max_batch = max(args.batch, 64)
     llm = LLM(scratch.name, dtype="bfloat16", max_running=max_batch, max_batch_tokens=4096,
               prefill_chunk_tokens=PROMPT_TOKENS, kv_capacity_tokens=max_batch * CONTEXT, page_size=PAGE_SIZE,
-              max_sequence_length=CONTEXT)
+              max_sequence_length=CONTEXT, cuda_graphs=not args.no_graphs)
     stepper, cache = llm.stepper, llm.stepper.cache
     numbers = model_numbers(cfg, layers)
     sampler.start()
@@ -161,11 +161,17 @@ def run_ours(args):
         cache.release(rid)
         return start.elapsed_time(stop), logits
 
-    for k in range(3):
-        prefill_once(f"warm{k}")
-    t0 = time.time()
-    prefill_ms = sorted(prefill_once(f"pre{k}")[0] for k in range(5))[2]
-    windows.append((t0, time.time()))
+    if args.only == "decode":
+        prefill_ms = float("nan")
+    else:
+        for k in range(3):
+            prefill_once(f"warm{k}")
+        t0 = time.time()
+        prefill_ms = sorted(prefill_once(f"pre{k}")[0] for k in range(5))[2]
+        windows.append((t0, time.time()))
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens_per_s": PROMPT_TOKENS / (prefill_ms / 1e3)}))
+        return 0
     flops = prefill_flops(cfg, layers, PROMPT_TOKENS)
     prefill = {"value": PROMPT_TOKENS / (prefill_ms / 1e3), "tokens": PROMPT_TOKENS, "ms": prefill_ms,
                "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "peak": f"{pk['source']} bf16"}
@@ -178,18 +184,20 @@ def run_ours(args):
             assert cache.admit(rid)
             stepper.step([StepEntry(rid, prompt(), [])])
             last.append(int(rng.integers(0, cfg["vocab_size"])))
-        out = torch.empty(batch, dtype=torch.int32, device="cuda")
+        greedy, ones = [0.0] * batch, [1.0] * batch
 
         def one_step(tokens):
-            logits = stepper.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)])
-            kernels.argmax(logits, out)
-            return out.cpu().tolist()
+            return stepper.step_and_sample([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)],
+                                           greedy, ones, greedy)
+
+        def launched():
+            return kernels.launch_count + (stepper.graphs.kernels_replayed if stepper.graphs else 0)
 
         for _ in range(warmup):
             last = one_step(last)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
-        launches = kernels.launch_count
+        launches = launched()
         t0 = time.time()
         start.record()
         for _ in range(steps):
@@ -197,7 +205,7 @@ def run_ours(args):
         stop.record()
         torch.cuda.synchronize()
         windows.append((t0, time.time()))
-        launches = kernels.launch_count - launches
+        launches = launched() - launches
         ms = start.elapsed_time(stop) / steps
         context = cache.length(ids[0])
         for rid in ids:
@@ -205,6 +213,10 @@ def run_ours(args):
         return ms, launches, context
 
     ms_step, launches, context = decode_device(args.batch, args.steps, args.warmup)
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms_step,
+                          "tokens_per_s": args.batch / (ms_step / 1e3), "context": context}))
+        return 0
     point_steps = max(8, min(args.steps, 64))
     ms_b1, _, _ = decode_device(1, point_steps, args.warmup)
     ms_b64, _, _ = decode_device(64, point_steps, args.warmup)
@@ -264,6 +276,9 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                        help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
+    parser.add_argument("--no-graphs", action="store_true", help="decode without CUDA-graph replay")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()

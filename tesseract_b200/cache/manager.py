@@ -5,7 +5,7 @@ fixed-size state) form a *group*.  A paged group has its own page pool and one b
 table per live request, shared by the group's entries (each entry has its own storage
 ``[pages + 1, 2, kv_heads, page_size, head_dim]`` addressed by the same page ids; page 0
 is a scratch page that no request owns, for padded rows).  A state group has storage
-``[entries, slots, *shape]`` addressed by the request's state slot.  Every live request
+``[entries, slots + 1, *shape]`` addressed by the request's state slot (the last slot is scratch).  Every live request
 holds one state slot whether or not the model has state groups
 (src/engine/recurrent.rs:6-38; groups after src/engine/state.rs:31-132).
 
@@ -59,6 +59,7 @@ class CacheManager:
         self.dtype = dtype
         self.device = device
         self.slots = StateSlots(max_requests)
+        self.scratch_slot = max_requests       # one state slot more than requests: padded rows point here
         self.groups: List[_Group] = []
         self._group_of_entry: List[Optional[int]] = [None] * len(needs)
         self._index_in_group: List[Optional[int]] = [None] * len(needs)
@@ -84,7 +85,7 @@ class CacheManager:
                         dtype=dtype, device=device)
             elif isinstance(need, StateNeed):
                 if allocate_storage:
-                    group.storage = torch.zeros((len(group.entries), max_requests, *need.shape),
+                    group.storage = torch.zeros((len(group.entries), max_requests + 1, *need.shape),
                                                 dtype=need.dtype, device=device)
             else:
                 raise TypeError(f"unknown cache need {need!r}")

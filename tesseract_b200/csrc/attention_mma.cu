@@ -8,7 +8,7 @@
 // Layout of the work.  The G = num_heads / num_kv_heads query heads that share a kv head are
 // folded into the row dimension of a tile: row r of a sequence's tile space is query position
 // r / G, head (kv_head * G + r % G), so one pass over a kv head's keys serves the whole group.
-//   tb_attention_tiles   : one CTA per (64-row tile, kv head, sequence); its 4 warps own 16 rows
+//   tb_attention_tiles   : one CTA per (128-row tile, kv head, sequence); its 8 warps own 16 rows
 //                          each and share every K/V tile.  For sequences with more than 16 rows.
 //   tb_attention_decode  : sequences with at most 16 rows (decode, and tiny portions); one CTA per
 //                          (key split, kv head, sequence); its 4 warps share the 16 rows and own 16
@@ -50,6 +50,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (relative error about 2^-22, far below bfloat16's rounding of P).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -80,14 +86,14 @@ struct AttnParams {
 };
 
 // Copies rows [key0, key0 + ROWS) of one kv head's K (which = 0) or V (which = 1) into a swizzled tile.
-template <int D, int ROWS>
+template <int D, int ROWS, int NT = kThreads>
 __device__ __forceinline__ void load_kv_tile(uint32_t tile, const AttnParams& p, const int* table, int kv_head,
                                              int which, int key0, int key_lo, int key_hi) {
     constexpr int CH = D / 8;
     const int64_t head_block = (int64_t)p.page_size * p.head_dim;
     const int64_t page_block = 2 * (int64_t)p.num_kv_heads * head_block;
     const __nv_bfloat16* base = p.cache + ((int64_t)which * p.num_kv_heads + kv_head) * head_block;
-    for (int idx = threadIdx.x; idx < ROWS * CH; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < ROWS * CH; idx += NT) {
         const int r = idx / CH, c = idx % CH;
         const int key = key0 + r;
         const bool ok = key >= key_lo && key <= key_hi && c * 8 < p.head_dim;
@@ -101,11 +107,11 @@ __device__ __forceinline__ void load_kv_tile(uint32_t tile, const AttnParams& p,
 }
 
 // Copies ROWS folded query rows starting at tile-space row r0 of a sequence into a swizzled tile.
-template <int D, int ROWS>
+template <int D, int ROWS, int NT = kThreads>
 __device__ __forceinline__ void load_q_tile(uint32_t tile, const AttnParams& p, int first_row, int kv_head, int r0,
                                             int n_rows) {
     constexpr int CH = D / 8;
-    for (int idx = threadIdx.x; idx < ROWS * CH; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < ROWS * CH; idx += NT) {
         const int r = idx / CH, c = idx % CH;
         const int fr = r0 + r;
         const bool ok = fr < n_rows && c * 8 < p.head_dim;
@@ -122,10 +128,12 @@ __device__ __forceinline__ void load_q_tile(uint32_t tile, const AttnParams& p, 
 // keys key_base..).  Updates the running maximum m, the per-thread partial sum l and the accumulator o of the
 // thread's two rows (lane/4 and lane/4 + 8).  pos[i] is the absolute position of row i (-1: no such row) and
 // lo[i] its first visible key.
-template <int D, int NK>
+// QREG: the Q fragments are already in registers (qf); MASK: some (row, key) pairs of this block are invisible.
+template <int D, int NK, bool QREG = false, bool MASK = true>
 __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t k_tile, uint32_t v_tile, int krow0,
                                             int key_base, const int (&pos)[2], const int (&lo)[2], float scale_log2,
-                                            float (&o)[D / 8][4], float (&m)[2], float (&l)[2]) {
+                                            float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
+                                            const uint32_t (*qf)[4] = nullptr) {
     const int lane = threadIdx.x & 31;
     float s[NK / 8][4];
 #pragma unroll
@@ -136,7 +144,12 @@ __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
         uint32_t a[4];
-        ldmatrix_x4(a, q_tile + tile_offset<D>(qrow0 + (lane & 15), ks * 2 + (lane >> 4)));
+        if (QREG) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) a[e] = qf[ks][e];
+        } else {
+            ldmatrix_x4(a, q_tile + tile_offset<D>(qrow0 + (lane & 15), ks * 2 + (lane >> 4)));
+        }
 #pragma unroll
         for (int np = 0; np < NK / 16; ++np) {
             uint32_t b[4];
@@ -155,7 +168,7 @@ __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t
         for (int e = 0; e < 4; ++e) {
             const int i = e >> 1;
             const int key = key_base + nt * 8 + 2 * (lane & 3) + (e & 1);
-            const bool valid = key >= lo[i] && key <= pos[i];
+            const bool valid = !MASK || (key >= lo[i] && key <= pos[i]);
             s[nt][e] = valid ? s[nt][e] * scale_log2 : kMasked;
             block_max[i] = fmaxf(block_max[i], s[nt][e]);
         }
@@ -165,7 +178,7 @@ __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t
         block_max[i] = fmaxf(block_max[i], __shfl_xor_sync(0xffffffffu, block_max[i], 1));
         block_max[i] = fmaxf(block_max[i], __shfl_xor_sync(0xffffffffu, block_max[i], 2));
         const float m_new = fmaxf(m[i], block_max[i]);
-        corr[i] = exp2f(m[i] - m_new);
+        corr[i] = fast_exp2(m[i] - m_new);
         m[i] = m_new;
         l[i] *= corr[i];
     }
@@ -184,7 +197,7 @@ __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int i = e >> 1;
-            pv[e] = (s[nt][e] > 0.5f * kMasked) ? exp2f(s[nt][e] - m[i]) : 0.0f;
+            pv[e] = (!MASK || s[nt][e] > 0.5f * kMasked) ? fast_exp2(s[nt][e] - m[i]) : 0.0f;
             l[i] += pv[e];
         }
         pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
@@ -205,16 +218,22 @@ __device__ __forceinline__ void warp_attend(uint32_t q_tile, int qrow0, uint32_t
 }
 
 // ------------------------------------------------------------------------------------------------
-// Prompt portions: one CTA per (64-row tile, kv head, sequence).
-template <int D, int BN>
-__global__ void __launch_bounds__(kThreads) attention_tiles_kernel(const AttnParams p) {
-    constexpr int BM = 64;
+// Prompt portions: one CTA per (BM-row tile, kv head, sequence); WARPS warps of 16 rows each share every K/V
+// tile, which arrive through a STAGES-deep cp.async pipeline.
+template <int D, int BN, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, (D <= 64 ? 2 : 1)) attention_tiles_kernel(const AttnParams p) {
+    constexpr int BM = WARPS * 16;
+    constexpr int NT = WARPS * 32;
+    constexpr bool QREG = D <= 128;  // Q fragments live in registers unless the head is very wide
     extern __shared__ __align__(128) unsigned char smem[];
-    const int seq = blockIdx.z, kv_head = blockIdx.y, r0 = blockIdx.x * BM;
+    const int seq = blockIdx.z, kv_head = blockIdx.y;
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
-    if (n_rows <= 16 || r0 >= n_rows) return;  // short sequences belong to the decode kernel
+    // heavy tiles (late rows see the most keys) are scheduled first
+    const int n_tiles = (n_rows + BM - 1) / BM;
+    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) return;  // short sequences belong to the decode kernel
+    const int r0 = (n_tiles - 1 - blockIdx.x) * BM;
     const int begin = p.seq_begin[seq];
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -227,11 +246,18 @@ __global__ void __launch_bounds__(kThreads) attention_tiles_kernel(const AttnPar
     const int key_hi = begin + last_row / p.group;
     const int key_lo = p.window > 0 ? max(0, begin + r0 / p.group - p.window + 1) : 0;
     const int kb_first = key_lo / BN, kb_last = key_hi / BN;
+    const int n_blocks = kb_last - kb_first + 1;
 
-    load_q_tile<D, BM>(q_tile, p, first_row, kv_head, r0, n_rows);
-    load_kv_tile<D, BN>(kv_tiles, p, table, kv_head, 0, kb_first * BN, key_lo, key_hi);
-    load_kv_tile<D, BN>(kv_tiles + kTileBytes, p, table, kv_head, 1, kb_first * BN, key_lo, key_hi);
-    cp_async_commit();
+    load_q_tile<D, BM, NT>(q_tile, p, first_row, kv_head, r0, n_rows);
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < n_blocks) {
+            const uint32_t dst = kv_tiles + st * 2 * kTileBytes;
+            load_kv_tile<D, BN, NT>(dst, p, table, kv_head, 0, (kb_first + st) * BN, key_lo, key_hi);
+            load_kv_tile<D, BN, NT>(dst + kTileBytes, p, table, kv_head, 1, (kb_first + st) * BN, key_lo, key_hi);
+        }
+        cp_async_commit();  // one group per stage, empty or not, keeps the wait count fixed
+    }
 
     int pos[2], lo[2];
 #pragma unroll
@@ -245,26 +271,40 @@ __global__ void __launch_bounds__(kThreads) attention_tiles_kernel(const AttnPar
     for (int dt = 0; dt < D / 8; ++dt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
-    // rows of this warp span positions [warp_lo_pos, warp_hi_pos]; key blocks wholly outside need no math
     const int warp_first = r0 + warp * 16;
     const bool warp_active = warp_first < n_rows;
-    const int warp_hi_key = begin + (min(n_rows, warp_first + 16) - 1) / p.group;
+    const int warp_rows_end = min(n_rows, warp_first + 16);
+    const int warp_hi_key = begin + (warp_rows_end - 1) / p.group;   // last key any row of this warp sees
+    const int warp_lo_pos = begin + warp_first / p.group;            // every row of this warp sees keys up to here
+    const bool all_rows = warp_first + 16 <= n_rows;
 
-    for (int kb = kb_first; kb <= kb_last; ++kb) {
-        const int stage = (kb - kb_first) & 1;
-        if (kb < kb_last) {
-            const uint32_t next = kv_tiles + (stage ^ 1) * 2 * kTileBytes;
-            load_kv_tile<D, BN>(next, p, table, kv_head, 0, (kb + 1) * BN, key_lo, key_hi);
-            load_kv_tile<D, BN>(next + kTileBytes, p, table, kv_head, 1, (kb + 1) * BN, key_lo, key_hi);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+    uint32_t qf[QREG ? D / 16 : 1][4];
+    for (int it = 0; it < n_blocks; ++it) {
+        const int kb = kb_first + it;
+        // prefetch block it + STAGES - 1 into the stage that was consumed in the previous iteration
+        if (it + STAGES - 1 < n_blocks) {
+            const uint32_t dst = kv_tiles + ((it + STAGES - 1) % STAGES) * 2 * kTileBytes;
+            load_kv_tile<D, BN, NT>(dst, p, table, kv_head, 0, (kb + STAGES - 1) * BN, key_lo, key_hi);
+            load_kv_tile<D, BN, NT>(dst + kTileBytes, p, table, kv_head, 1, (kb + STAGES - 1) * BN, key_lo, key_hi);
         }
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
+        if (QREG && it == 0) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                ldmatrix_x4(qf[ks], q_tile + tile_offset<D>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+        }
         if (warp_active && kb * BN <= warp_hi_key) {
-            const uint32_t cur = kv_tiles + stage * 2 * kTileBytes;
-            warp_attend<D, BN>(q_tile, warp * 16, cur, cur + kTileBytes, 0, kb * BN, pos, lo, p.scale_log2, o, m, l);
+            const uint32_t cur = kv_tiles + (it % STAGES) * 2 * kTileBytes;
+            // no mask when every key of the block is visible to every row of the warp
+            const bool full = all_rows && p.window <= 0 && kb * BN + BN - 1 <= warp_lo_pos;
+            if (full)
+                warp_attend<D, BN, QREG, false>(q_tile, warp * 16, cur, cur + kTileBytes, 0, kb * BN, pos, lo,
+                                                p.scale_log2, o, m, l, qf);
+            else
+                warp_attend<D, BN, QREG, true>(q_tile, warp * 16, cur, cur + kTileBytes, 0, kb * BN, pos, lo,
+                                               p.scale_log2, o, m, l, qf);
         }
         __syncthreads();  // everyone is done with this stage before the next prefetch overwrites it
     }
@@ -437,15 +477,18 @@ template <int D>
 int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_tiles, int run_decode,
                cudaStream_t stream) {
     constexpr int BN = D <= 128 ? 64 : 32;
+    constexpr int WARPS = D <= 128 ? 8 : 4;
+    constexpr int STAGES = D <= 64 ? 3 : 2;
     if (run_tiles) {
-        const size_t smem = (size_t)64 * D * 2 + (size_t)2 * 2 * BN * D * 2;
-        auto kernel = attention_tiles_kernel<D, BN>;
+        constexpr int BM = WARPS * 16;
+        const size_t smem = (size_t)BM * D * 2 + (size_t)STAGES * 2 * BN * D * 2;
+        auto kernel = attention_tiles_kernel<D, BN, WARPS, STAGES>;
         if (smem > 48 * 1024) {
             cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess) return (int)err;
         }
-        dim3 grid((max_rows_per_seq + 63) / 64, p.num_kv_heads, num_seqs);
-        kernel<<<grid, kThreads, smem, stream>>>(p);
+        dim3 grid((max_rows_per_seq + BM - 1) / BM, p.num_kv_heads, num_seqs);
+        kernel<<<grid, WARPS * 32, smem, stream>>>(p);
         if (int status = tb_launch_status()) return status;
     }
     if (run_decode) {

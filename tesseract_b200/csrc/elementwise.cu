@@ -62,6 +62,31 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     }
 }
 
+// bfloat16, eight elements (16 bytes) per thread and iteration.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                       int inter, int64_t gu_stride) {
+    const int row = blockIdx.x;
+    const uint4* g = reinterpret_cast<const uint4*>(gu + (int64_t)row * gu_stride);
+    const uint4* u = reinterpret_cast<const uint4*>(gu + (int64_t)row * gu_stride + inter);
+    uint4* o = reinterpret_cast<uint4*>(out + (int64_t)row * inter);
+    const int packets = inter / 8;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < packets; j += gridDim.y * blockDim.x) {
+        const uint4 gp = g[j], up = u[j];
+        const uint32_t gw[4] = {gp.x, gp.y, gp.z, gp.w}, uw[4] = {up.x, up.y, up.z, up.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xffff0000u);
+            const float a0 = g0 * (1.0f / (1.0f + expf(-g0))) * u0;
+            const float a1 = g1 * (1.0f / (1.0f + expf(-g1))) * u1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
+            ow[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        o[j] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 }  // namespace
 
 TB_EXPORT int tb_embedding(const int* tokens, const void* table, void* out, int rows, int hidden, int vocab,
@@ -83,7 +108,12 @@ TB_EXPORT int tb_silu_mul(const void* gu, void* out, int rows, int inter, int dt
     dim3 grid(rows, bx);
     if (dtype == TB_F32)
         silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter);
-    else if (dtype == TB_BF16)
+    else if (dtype == TB_BF16 && inter % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
+        int by = (inter / 8 + threads - 1) / threads;
+        if (by > 64) by = 64;
+        silu_mul_bf16x8_kernel<<<dim3(rows, by), threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                                                                      inter, 2 * (int64_t)inter);
+    } else if (dtype == TB_BF16)
         silu_mul_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
                                                                     inter, 2 * (int64_t)inter);
     else

@@ -12,43 +12,85 @@
 
 namespace {
 
-template <typename T, bool ADD>
+// VEC: 16-byte packets (width a multiple of the packet, pointers aligned) or one element at a time.
+// Which of the two runs depends on the width and the buffers' alignment only, never on the batch.
+template <typename T, bool ADD, bool VEC>
 __global__ void rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ upd, const float* __restrict__ w,
                                 T* __restrict__ y, T* __restrict__ res_out, int width, float eps) {
-    extern __shared__ float row_cache[];  // width floats: the (summed) row, kept between the two passes
+    extern __shared__ __align__(16) float row_cache[];  // width floats: the (summed) row, kept between the passes
     __shared__ float scratch[32];
     const int64_t base = (int64_t)blockIdx.x * width;
     float ss = 0.0f;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) {
-        float v = Elem<T>::load(x + base + j);
-        if (ADD) {
-            v += Elem<T>::load(upd + base + j);
-            Elem<T>::store(res_out + base + j, v);
+    if (VEC) {
+        constexpr int N = Packet<T>::N;
+        for (int j = threadIdx.x * N; j < width; j += blockDim.x * N) {
+            float v[N];
+            Packet<T>::load(x + base + j, v);
+            if (ADD) {
+                float u[N];
+                Packet<T>::load(upd + base + j, u);
+#pragma unroll
+                for (int e = 0; e < N; ++e) v[e] += u[e];
+                Packet<T>::store(res_out + base + j, v);
+            }
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                row_cache[j + e] = v[e];
+                ss += v[e] * v[e];
+            }
         }
-        row_cache[j] = v;
-        ss += v * v;
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) {
+            float v = Elem<T>::load(x + base + j);
+            if (ADD) {
+                v += Elem<T>::load(upd + base + j);
+                Elem<T>::store(res_out + base + j, v);
+            }
+            row_cache[j] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int j = threadIdx.x; j < width; j += blockDim.x)
-        Elem<T>::store(y + base + j, row_cache[j] * inv * w[j]);
+    if (VEC) {
+        constexpr int N = Packet<T>::N;
+        for (int j = threadIdx.x * N; j < width; j += blockDim.x * N) {
+            float v[N];
+#pragma unroll
+            for (int e = 0; e < N; ++e) v[e] = row_cache[j + e] * inv * w[j + e];
+            Packet<T>::store(y + base + j, v);
+        }
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x)
+            Elem<T>::store(y + base + j, row_cache[j] * inv * w[j]);
+    }
 }
 
-template <typename T, bool ADD>
-int launch(const void* x, const void* upd, const float* w, void* y, void* res_out, int rows, int width, float eps,
-           cudaStream_t stream) {
-    if (rows == 0) return 0;
+template <typename T, bool ADD, bool VEC>
+int launch_kernel(const void* x, const void* upd, const float* w, void* y, void* res_out, int rows, int width,
+                  float eps, cudaStream_t stream) {
     const size_t smem = (size_t)width * sizeof(float);
-    if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
+    const int per_thread = VEC ? Packet<T>::N : 4;
     int threads = 32;
-    while (threads < 512 && threads * 4 < width) threads <<= 1;
-    auto kernel = rms_norm_kernel<T, ADD>;
+    while (threads < 512 && threads * per_thread < width) threads <<= 1;
+    auto kernel = rms_norm_kernel<T, ADD, VEC>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
     kernel<<<rows, threads, smem, stream>>>((const T*)x, (const T*)upd, w, (T*)y, (T*)res_out, width, eps);
     return tb_launch_status();
+}
+
+template <typename T, bool ADD>
+int launch(const void* x, const void* upd, const float* w, void* y, void* res_out, int rows, int width, float eps,
+           cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if ((size_t)width * sizeof(float) > 200 * 1024) return TB_ERR_BAD_SIZE;
+    const uintptr_t bits = (uintptr_t)x | (uintptr_t)upd | (uintptr_t)y | (uintptr_t)res_out | (uintptr_t)w;
+    const bool vec = (width % Packet<T>::N == 0) && (bits % 16 == 0);
+    if (vec) return launch_kernel<T, ADD, true>(x, upd, w, y, res_out, rows, width, eps, stream);
+    return launch_kernel<T, ADD, false>(x, upd, w, y, res_out, rows, width, eps, stream);
 }
 
 }  // namespace

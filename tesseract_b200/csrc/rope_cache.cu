@@ -14,15 +14,27 @@
 
 namespace {
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int64_t qkv_stride, const int* __restrict__ positions,
                                      const int* __restrict__ seq_of_row, const int* __restrict__ block_table,
                                      int bt_stride, const float* __restrict__ inv_freq, T* __restrict__ cache,
                                      int num_heads, int num_kv_heads, int head_dim, int page_size, int write_kv) {
+    extern __shared__ float trig[];  // cos[half] then sin[half] of this row's angles, shared by all heads
     const int row = blockIdx.x;
     const int pos = positions[row];
     const int half = head_dim >> 1;
     T* base = qkv + (int64_t)row * qkv_stride;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float c = 1.0f, s = 0.0f;
+        if (inv_freq != nullptr) {
+            const float angle = (float)pos * inv_freq[i];
+            c = cosf(angle);
+            s = sinf(angle);
+        }
+        trig[i] = c;
+        trig[half + i] = s;
+    }
+    __syncthreads();
 
     int64_t page = 0;
     int offset = 0;
@@ -36,40 +48,82 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int64_t qkv_stride, co
     T* kpage = cache + page * page_block + (int64_t)offset * head_dim;
     T* vpage = kpage + (int64_t)num_kv_heads * head_block;
 
+    constexpr int N = VEC ? Packet<T>::N : 1;
     const int rot_heads = num_heads + num_kv_heads;
-    const int rot_items = rot_heads * half;
+    const int per_head = half / N;
+    const int rot_items = rot_heads * per_head;
     for (int item = threadIdx.x; item < rot_items; item += blockDim.x) {
-        const int head = item / half;
-        const int i = item - head * half;
+        const int head = item / per_head;
+        const int i = (item - head * per_head) * N;
         T* x = base + (int64_t)head * head_dim;
-        const float lo = Elem<T>::load(x + i);
-        const float hi = Elem<T>::load(x + half + i);
-        float c = 1.0f, s = 0.0f;
-        if (inv_freq != nullptr) {
-            const float angle = (float)pos * inv_freq[i];
-            c = cosf(angle);
-            s = sinf(angle);
+        float lo[N], hi[N], out_lo[N], out_hi[N];
+        if (VEC) {
+            Packet<T>::load(x + i, lo);
+            Packet<T>::load(x + half + i, hi);
+        } else {
+            lo[0] = Elem<T>::load(x + i);
+            hi[0] = Elem<T>::load(x + half + i);
         }
-        const float out_lo = lo * c - hi * s;
-        const float out_hi = hi * c + lo * s;
-        if (head < num_heads) {
-            Elem<T>::store(x + i, out_lo);
-            Elem<T>::store(x + half + i, out_hi);
-        } else if (write_kv) {
-            T* dst = kpage + (int64_t)(head - num_heads) * head_block;
-            Elem<T>::store(dst + i, out_lo);
-            Elem<T>::store(dst + half + i, out_hi);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            const float c = trig[i + e], s = trig[half + i + e];
+            out_lo[e] = lo[e] * c - hi[e] * s;
+            out_hi[e] = hi[e] * c + lo[e] * s;
+        }
+        T* dst = nullptr;
+        if (head < num_heads) dst = x;
+        else if (write_kv) dst = kpage + (int64_t)(head - num_heads) * head_block;
+        if (dst != nullptr) {
+            if (VEC) {
+                Packet<T>::store(dst + i, out_lo);
+                Packet<T>::store(dst + half + i, out_hi);
+            } else {
+                Elem<T>::store(dst + i, out_lo[0]);
+                Elem<T>::store(dst + half + i, out_hi[0]);
+            }
         }
     }
     if (write_kv) {
         const T* v = base + (int64_t)(num_heads + num_kv_heads) * head_dim;
-        const int v_items = num_kv_heads * head_dim;
-        for (int item = threadIdx.x; item < v_items; item += blockDim.x) {
-            const int head = item / head_dim;
-            const int i = item - head * head_dim;
-            vpage[(int64_t)head * head_block + i] = v[item];
+        if (VEC) {
+            const int per = head_dim / N;
+            for (int item = threadIdx.x; item < num_kv_heads * per; item += blockDim.x) {
+                const int head = item / per;
+                const int i = (item - head * per) * N;
+                *reinterpret_cast<uint4*>(vpage + (int64_t)head * head_block + i) =
+                    *reinterpret_cast<const uint4*>(v + (int64_t)head * head_dim + i);
+            }
+        } else {
+            const int v_items = num_kv_heads * head_dim;
+            for (int item = threadIdx.x; item < v_items; item += blockDim.x) {
+                const int head = item / head_dim;
+                const int i = item - head * head_dim;
+                vpage[(int64_t)head * head_block + i] = v[item];
+            }
         }
     }
+}
+
+template <typename T>
+int launch(void* qkv, int64_t qkv_stride, const int* positions, const int* seq_of_row, const int* block_table,
+           int bt_stride, const float* inv_freq, void* cache, int rows, int num_heads, int num_kv_heads, int head_dim,
+           int page_size, int write_kv, cudaStream_t stream) {
+    const int half = head_dim / 2;
+    const bool vec = (half % Packet<T>::N == 0) && (qkv_stride % Packet<T>::N == 0) &&
+                     (((uintptr_t)qkv | (uintptr_t)cache) % 16 == 0);
+    const int work = (num_heads + num_kv_heads) * (vec ? half / Packet<T>::N : half);
+    int threads = 32;
+    while (threads < 512 && threads < work) threads <<= 1;
+    const size_t smem = (size_t)head_dim * sizeof(float);
+    if (vec)
+        rope_kv_write_kernel<T, true><<<rows, threads, smem, stream>>>(
+            (T*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
+            num_kv_heads, head_dim, page_size, write_kv);
+    else
+        rope_kv_write_kernel<T, false><<<rows, threads, smem, stream>>>(
+            (T*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
+            num_kv_heads, head_dim, page_size, write_kv);
+    return tb_launch_status();
 }
 
 }  // namespace
@@ -82,18 +136,11 @@ TB_EXPORT int tb_rope_kv_write(void* qkv, int64_t qkv_stride, const int* positio
                                int write_kv, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (head_dim <= 0 || (head_dim & 1)) return TB_ERR_BAD_SIZE;
-    const int work = (num_heads + num_kv_heads) * (head_dim / 2);
-    int threads = 64;
-    while (threads < 512 && threads * 4 < work) threads <<= 1;
     if (dtype == TB_F32)
-        rope_kv_write_kernel<float><<<rows, threads, 0, stream>>>(
-            (float*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (float*)cache,
-            num_heads, num_kv_heads, head_dim, page_size, write_kv);
-    else if (dtype == TB_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq,
-            (__nv_bfloat16*)cache, num_heads, num_kv_heads, head_dim, page_size, write_kv);
-    else
-        return TB_ERR_BAD_DTYPE;
-    return tb_launch_status();
+        return launch<float>(qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, cache, rows,
+                             num_heads, num_kv_heads, head_dim, page_size, write_kv, stream);
+    if (dtype == TB_BF16)
+        return launch<__nv_bfloat16>(qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, cache,
+                                     rows, num_heads, num_kv_heads, head_dim, page_size, write_kv, stream);
+    return TB_ERR_BAD_DTYPE;
 }

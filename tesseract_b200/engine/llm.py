@@ -54,10 +54,13 @@ class LLM:
         self.stepper = make_stepper(self.model, capacity_tokens=kv_capacity_tokens, page_size=page_size,
                                     max_requests=max_running, max_step_tokens=prefill_chunk_tokens)
         self.sampler = Sampler(self.model.runtime.device)
+        if cuda_graphs:
+            self.stepper.enable_graphs(max_running)
         self.scheduler = Scheduler(self.config, self.stepper.cache, self.stepper.step, self.sampler.sample,
                                    eos_token_ids=self.model.spec.eos_token_ids,
                                    max_positions=self.model.spec.max_positions,
-                                   capacity_tokens=self.stepper.cache.num_pages * page_size)
+                                   capacity_tokens=self.stepper.cache.num_pages * page_size,
+                                   run_and_sample=self.stepper.step_and_sample)
         self.tokenizer = self._load_tokenizer(model_path)
 
     @staticmethod

@@ -104,12 +104,14 @@ class Scheduler:
     injected, so the scheduler's decisions can be tested without a device."""
 
     def __init__(self, config: EngineConfig, cache, run_step: Callable, sample: Callable, *, eos_token_ids=(),
-                 max_positions: Optional[int] = None, capacity_tokens: Optional[int] = None):
+                 max_positions: Optional[int] = None, capacity_tokens: Optional[int] = None,
+                 run_and_sample: Optional[Callable] = None):
         config.validate()
         self.config = config
         self.cache = cache
         self.run_step = run_step
         self.sample = sample
+        self.run_and_sample = run_and_sample    # (entries, temperatures, top_ps, draws) -> tokens, in one call
         self.eos_token_ids = frozenset(int(t) for t in eos_token_ids)
         self.max_positions = max_positions
         self.capacity_tokens = capacity_tokens if capacity_tokens is not None else config.kv_capacity_tokens
@@ -204,9 +206,14 @@ class Scheduler:
         entries = [StepEntry(s.request.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
         sampled = [s for s in batch if s.samples]
         try:
-            logits = self.run_step(entries)
-            tokens = self.sample(logits, [s.request.params.temperature for s in sampled],
-                                 [s.request.params.top_p for s in sampled], [s.draw for s in sampled]) if sampled else []
+            temperatures = [s.request.params.temperature for s in sampled]
+            top_ps = [s.request.params.top_p for s in sampled]
+            draws = [s.draw for s in sampled]
+            if self.run_and_sample is not None:
+                tokens = self.run_and_sample(entries, temperatures, top_ps, draws)
+            else:
+                logits = self.run_step(entries)
+                tokens = self.sample(logits, temperatures, top_ps, draws) if sampled else []
             if len(tokens) != len(sampled):
                 raise RuntimeError("the sampler returned a wrong number of tokens")
         except Exception as exc:  # noqa: BLE001 - a failed step fails its batch, the engine keeps serving

@@ -81,6 +81,8 @@ class Stepper:
         self.max_positions = model.spec.max_positions
         self._staging = _Staging(self.runtime.device)
         self.steps_run = 0
+        self.graphs = None          # set by enable_graphs()
+        self._sampler = None
 
     # ------------------------------------------------------------------ validation
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -152,3 +154,34 @@ class Stepper:
             self.cache.commit(entry.request, len(entry.tokens))
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------------ step + sampling
+    def enable_graphs(self, max_batch: int) -> None:
+        """Replay pure decode steps as CUDA graphs from now on (if every mixer allows it)."""
+        from .graph import DecodeGraphs
+
+        self.graphs = DecodeGraphs(self, max_batch)
+
+    def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float], top_ps: Sequence[float],
+                        draws: Sequence[float]) -> List[int]:
+        """One step, then one token per wanted row (entries want at most their last place).
+
+        ``temperatures``, ``top_ps`` and ``draws`` hold one value per wanted row, in order.
+        """
+        from ..sampling.sampler import Sampler, sample_top_p_host
+
+        if self._sampler is None:
+            self._sampler = Sampler(self.runtime.device)
+        wanted = sum(len(e.want) for e in entries)
+        if wanted == 0:
+            self.step(entries)
+            return []
+        if self.graphs is not None and wanted == len(entries) and self.graphs.eligible(entries):
+            tokens, logits = self.graphs.step(entries, temperatures, draws)
+            out = tokens.cpu().tolist()
+            for i, (t, p) in enumerate(zip(temperatures, top_ps)):
+                if t > 0.0 and p < 1.0:
+                    out[i] = sample_top_p_host(logits[i].cpu().numpy(), t, p, draws[i])
+            return out
+        logits = self.step(entries)
+        return self._sampler.sample(logits, temperatures, top_ps, draws)

@@ -29,6 +29,8 @@ class Attention(Mixer):
     """params: ``hidden_size, num_heads, num_kv_heads, head_dim``, optional ``window``, ``scale``.
     weights: ``q, k, v, o``.  children: ``position`` (a position encoding spec)."""
 
+    graph_safe = True      # reads only device-side metadata of the step, so a decode step can be captured
+
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         super().__init__(spec, tensors, runtime)
         p = spec.params

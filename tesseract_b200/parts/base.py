@@ -215,6 +215,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if ``forward`` takes everything that varies from step to step from device tensors of the
+    # context (never from its host lists), so that a decode step may be captured in a CUDA graph.
+    graph_safe = False
+
     def cache_need(self):
         return None
 

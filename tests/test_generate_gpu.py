@@ -120,3 +120,29 @@ def test_command_line_generates(model_folders):
     assert len(records) == 2 and all(len(r["token_ids"]) == 4 and r["finish_reason"] == "length" for r in records)
     config, tensors = llama.load_folder(folder)
     check_greedy(config, tensors, [5, 6, 7, 8], records[0]["token_ids"], 1e-5)
+
+
+@pytest.mark.parametrize("dtype, margin", [("float32", 1e-5), ("bfloat16", 3e-2)])
+def test_graph_replay_decodes_like_the_eager_path(model_folders, dtype, margin):
+    """Pure decode steps replayed as CUDA graphs (batch padded to a bucket) give the eager path's tokens."""
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("b")
+    config, tensors = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], n, seed=70 + n) for n in (3, 40, 66)]      # three rows: bucket of 4
+    params = [SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True),
+              SamplingParams(max_tokens=25, temperature=0.8, seed=5, ignore_eos=True),
+              SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True)]
+    outs = {}
+    for graphs in (True, False):
+        llm = LLM(folder, dtype=dtype, kv_capacity_tokens=1024, max_running=4, cuda_graphs=graphs)
+        outs[graphs] = [o.token_ids for o in llm.generate(prompts, params)]
+        if graphs:
+            assert llm.stepper.graphs.replays >= 30 and llm.stepper.graphs.captures >= 1
+            # the table width grows past its first bucket while decoding (8 pages = 128 tokens)
+            assert len(llm.stepper.graphs.graphs) >= 2
+        assert llm.stepper.cache.used_pages() == 0
+    if dtype == "float32":
+        assert outs[True] == outs[False]
+    for k in (0, 2):
+        check_greedy(config, tensors, prompts[k], outs[True][k], margin)

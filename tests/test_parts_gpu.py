@@ -242,7 +242,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     # entry 2 keeps no cache (it reads entry 0's); the toy layer's two runs each keep their own state
     assert needs[2] is None and type(needs[1]).__name__ == "StateNeed" and needs[3] == needs[1]
     stepper = make_stepper(model, capacity_tokens=256, max_requests=3)
-    assert len(stepper.cache.groups) == 2 and stepper.cache.groups[1].storage.shape[:2] == (2, 3)
+    assert len(stepper.cache.groups) == 2 and stepper.cache.groups[1].storage.shape[:2] == (2, 3 + 1)
     rng = np.random.default_rng(0)
     seqs = {"p": rng.integers(0, 50, 37).tolist(), "q": rng.integers(0, 50, 20).tolist()}
     plain = {r: toy_plain(tensors, t) for r, t in seqs.items()}
