@@ -42,6 +42,7 @@ SOURCES: Dict[str, List[str]] = {
     "attention_mma": [],
     "attention_noalloc": [],
     "gemm_f32": [],
+    "decode_linear": [],
     "sampling": [],
 }
 
@@ -143,6 +144,13 @@ def _compile(name: str, out_path: str, verbose: bool) -> None:
             pass
         raise KernelBuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{output}")
     os.replace(tmp_path, out_path)
+    prefix = f"libtb_{name}-"
+    for stale in os.listdir(os.path.dirname(out_path)):       # older builds of this source are of no use
+        if stale.startswith(prefix) and stale.endswith(".so") and stale != os.path.basename(out_path):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out_path), stale))
+            except OSError:
+                pass
     if verbose and output:
         print(output, file=sys.stderr)
 

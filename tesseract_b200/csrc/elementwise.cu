@@ -2,7 +2,8 @@
 //
 //   tb_embedding     out[t, :] = table[token[t], :]           (src/cuda/kernels.rs:10-24)
 //   tb_gather_rows   out[s, :] = in[rows[s], :]               (src/cuda/kernels.rs:774-801)
-//   tb_silu_mul      out[t, j] = silu(gu[t, j]) * gu[t, I+j]  (src/cuda/kernels.rs:191-208)
+//   tb_silu_mul      out[t, j] = silu(gate[t, j]) * up[t, j]  (src/cuda/kernels.rs:191-208); gate and up lie
+//                    either in the two halves of a row or interleaved in blocks of eight columns
 //
 // The activation is computed in 32-bit: g * (1 / (1 + exp(-g))) * u, rounded once.
 #include "common.cuh"
@@ -49,14 +50,16 @@ int gather_rows(const int* index, const void* src, void* dst, int rows, int64_t 
 }
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride,
+                                int interleaved) {
     const int row = blockIdx.x;
     const T* g = gu + (int64_t)row * gu_stride;
-    const T* u = g + inter;
     T* o = out + (int64_t)row * inter;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < inter; j += gridDim.y * blockDim.x) {
-        const float gv = Elem<T>::load(g + j);
-        const float uv = Elem<T>::load(u + j);
+        const int gi = interleaved ? (j >> 3) * 16 + (j & 7) : j;
+        const int ui = interleaved ? gi + 8 : inter + j;
+        const float gv = Elem<T>::load(g + gi);
+        const float uv = Elem<T>::load(g + ui);
         const float act = gv * (1.0f / (1.0f + expf(-gv))) * uv;
         Elem<T>::store(o + j, act);
     }
@@ -64,14 +67,13 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 // bfloat16, eight elements (16 bytes) per thread and iteration.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                                       int inter, int64_t gu_stride) {
+                                       int inter, int64_t gu_stride, int interleaved) {
     const int row = blockIdx.x;
     const uint4* g = reinterpret_cast<const uint4*>(gu + (int64_t)row * gu_stride);
-    const uint4* u = reinterpret_cast<const uint4*>(gu + (int64_t)row * gu_stride + inter);
     uint4* o = reinterpret_cast<uint4*>(out + (int64_t)row * inter);
     const int packets = inter / 8;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < packets; j += gridDim.y * blockDim.x) {
-        const uint4 gp = g[j], up = u[j];
+        const uint4 gp = g[interleaved ? 2 * j : j], up = g[interleaved ? 2 * j + 1 : packets + j];
         const uint32_t gw[4] = {gp.x, gp.y, gp.z, gp.w}, uw[4] = {up.x, up.y, up.z, up.w};
         uint32_t ow[4];
 #pragma unroll
@@ -99,23 +101,27 @@ TB_EXPORT int tb_gather_rows(const int* rows_index, const void* in, void* out, i
     return gather_rows(rows_index, in, out, rows, width, num_in_rows, dtype, stream);
 }
 
-// gu: [rows, 2*inter] with the gate in columns [0, inter) and the up projection in [inter, 2*inter).
-TB_EXPORT int tb_silu_mul(const void* gu, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+// gu: [rows, 2*inter].  interleaved = 0: the gate in columns [0, inter), the up projection in [inter, 2*inter);
+// interleaved = 1: blocks of 16 columns hold eight gates then the eight matching up projections.
+TB_EXPORT int tb_silu_mul(const void* gu, void* out, int rows, int inter, int interleaved, int dtype,
+                          cudaStream_t stream) {
     if (rows == 0 || inter == 0) return 0;
+    if (interleaved && inter % 8 != 0) return TB_ERR_BAD_SIZE;
     const int threads = 256;
     int bx = (inter + threads - 1) / threads;
     if (bx > 64) bx = 64;
     dim3 grid(rows, bx);
     if (dtype == TB_F32)
-        silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter);
+        silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter,
+                                                              interleaved);
     else if (dtype == TB_BF16 && inter % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
         int by = (inter / 8 + threads - 1) / threads;
         if (by > 64) by = 64;
         silu_mul_bf16x8_kernel<<<dim3(rows, by), threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
-                                                                      inter, 2 * (int64_t)inter);
+                                                                      inter, 2 * (int64_t)inter, interleaved);
     } else if (dtype == TB_BF16)
         silu_mul_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
-                                                                    inter, 2 * (int64_t)inter);
+                                                                    inter, 2 * (int64_t)inter, interleaved);
     else
         return TB_ERR_BAD_DTYPE;
     return tb_launch_status();

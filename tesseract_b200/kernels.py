@@ -99,15 +99,16 @@ def gather_rows(rows_index: torch.Tensor, src: torch.Tensor, out: torch.Tensor) 
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]`` with ``I = out.shape[1]``."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """``out = silu(gate) * up`` with ``I = out.shape[1]``; gate and up are the two halves of ``gate_up``'s rows,
+    or (``interleaved``) alternate in blocks of eight columns: eight gates, their eight up projections, ..."""
     _cuda(gate_up, out)
     rows, inter = out.shape
     _need(gate_up.shape == (rows, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous(), "silu_mul shapes")
     _need(gate_up.dtype == out.dtype, "silu_mul dtypes")
     lib = load_library("elementwise")
-    _check(lib.tb_silu_mul(_ptr(gate_up), _ptr(out), _i32(rows), _i32(inter), _i32(_code(out.dtype)), _stream()),
-           "silu_mul")
+    _check(lib.tb_silu_mul(_ptr(gate_up), _ptr(out), _i32(rows), _i32(inter), _i32(1 if interleaved else 0),
+                           _i32(_code(out.dtype)), _stream()), "silu_mul")
     return out
 
 
@@ -280,4 +281,54 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_s
                                 _i32(head_dim), _i32(page_size), _i32(window), _f32(scale),
                                 _i32(1 if run_tiles else 0), _i32(1 if run_decode else 0), _i32(splits),
                                 _ptr(part_o), _ptr(part_ml), _i64(capacity), _stream()), "attention_mma")
+    return out
+
+
+PRO_NONE, PRO_NORM, PRO_ADD_NORM = 0, 1, 2
+EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
+
+
+def decode_linear_supported(rows: int, out_features: int, in_features: int, prologue: int = PRO_NONE) -> bool:
+    """Whether the skinny decode product takes these sizes (else the caller uses the general path)."""
+    return bool(load_library("decode_linear").tb_decode_linear_supported(_i32(rows), _i32(out_features),
+                                                                        _i32(in_features), _i32(prologue)))
+
+
+def decode_linear(weight: torch.Tensor, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None, update: Optional[torch.Tensor] = None,
+                  norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                  residual_out: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16) -> torch.Tensor:
+    """``out = X @ weight^T`` for at most 16 rows (bfloat16 weights, 32-bit accumulation).
+
+    ``X`` is ``x``, or ``rms_norm(residual)`` (``norm_weight`` given), or ``rms_norm(residual + update)``
+    with the rounded sum stored in ``residual_out`` (which must not be ``residual``).  ``epilogue``:
+    ``EPI_BF16`` / ``EPI_F32`` store ``[M, N]``; ``EPI_SWIGLU`` treats the weight's rows as blocks of eight gates
+    and eight up projections and stores ``silu(gate) * up`` as ``[M, N / 2]``.
+    """
+    _cuda(weight, out, x, residual, update, norm_weight, residual_out)
+    n, k = weight.shape
+    _need(weight.dtype == torch.bfloat16 and weight.is_contiguous(), "decode_linear weight must be contiguous bfloat16")
+    if norm_weight is None:
+        prologue, source = PRO_NONE, x
+        _need(x is not None and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == k, "decode_linear x")
+    else:
+        prologue, source = (PRO_ADD_NORM if update is not None else PRO_NORM), residual
+        _need(residual is not None and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+              and residual.shape[1] == k, "decode_linear residual")
+        _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == k, "decode_linear norm weight")
+        if update is not None:
+            _need(update.shape == residual.shape and update.dtype == torch.bfloat16 and update.is_contiguous(),
+                  "decode_linear update")
+            _need(residual_out is not None and residual_out.shape == residual.shape and residual_out.is_contiguous()
+                  and residual_out.dtype == torch.bfloat16 and residual_out.data_ptr() != residual.data_ptr(),
+                  "decode_linear residual_out must be a separate bfloat16 buffer")
+    m = source.shape[0]
+    width = n // 2 if epilogue == EPI_SWIGLU else n
+    _need(out.shape == (m, width) and out.stride(1) == 1, "decode_linear out shape")
+    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "decode_linear out dtype")
+    lib = load_library("decode_linear")
+    _check(lib.tb_decode_linear(_ptr(x), _i64(x.stride(0) if x is not None else 0), _ptr(residual), _ptr(update),
+                                _ptr(norm_weight), _f32(eps), _ptr(residual_out), _ptr(weight), _ptr(out),
+                                _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(prologue), _i32(epilogue),
+                                _stream()), "decode_linear")
     return out

@@ -16,8 +16,8 @@ import torch
 
 from .. import kernels
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheBinding, ResidualStream,
-                     Runtime, StepContext)
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheBinding, DeferredNorm,
+                     ResidualStream, Runtime, StepContext)
 from ..weights.loader import ExpectedTensor
 
 
@@ -123,10 +123,9 @@ class DecoderModel:
         width = stream.residual.shape[1]
         residual = torch.empty((count, width), dtype=stream.residual.dtype, device=stream.residual.device)
         kernels.gather_rows(want_rows, stream.residual, residual)
-        if stream.update is None:
-            normed = self.final_norm.forward(residual)
-        else:
+        update = None
+        if stream.update is not None:
             update = torch.empty_like(residual)
             kernels.gather_rows(want_rows, stream.update, update)
-            normed = self.final_norm.forward_add(residual, update)
-        return self.head.forward(normed)
+        final = DeferredNorm(self.final_norm, residual, update)
+        return self.head.forward(final if self.head.accepts_deferred_norm else final.materialize())

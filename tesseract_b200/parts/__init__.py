@@ -1,6 +1,6 @@
 """Parts of a decoder and their registries; importing this package registers the built-in kinds."""
 
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block,
+from .base import (BLOCKS, DeferredNorm, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block,
                    CacheBinding, Embedding, FeedForward, GroupView, Head, Mixer, Norm, PagedKVNeed, Part,
                    PositionEncoding, Registry, ResidualStream, Runtime, StateNeed, StepContext)
 from . import attention, block, embedding, mlp, norm, rotary  # noqa: F401  (registration)

@@ -20,7 +20,8 @@ import torch
 from .. import kernels
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
-from .base import (MIXERS, POSITION_ENCODINGS, CacheBinding, Mixer, PagedKVNeed, Runtime, StepContext)
+from .base import (MIXERS, POSITION_ENCODINGS, CacheBinding, DeferredNorm, Mixer, PagedKVNeed, Runtime,
+                   StepContext)
 from .linear import Linear
 
 
@@ -29,6 +30,7 @@ class Attention(Mixer):
     """params: ``hidden_size, num_heads, num_kv_heads, head_dim``, optional ``window``, ``scale``.
     weights: ``q, k, v, o``.  children: ``position`` (a position encoding spec)."""
 
+    accepts_deferred_norm = True
     graph_safe = True      # reads only device-side metadata of the step, so a decode step can be captured
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
@@ -69,11 +71,17 @@ class Attention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window or None)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[CacheBinding]) -> torch.Tensor:
+    def forward(self, x, ctx: StepContext, cache: Optional[CacheBinding]) -> torch.Tensor:
         if cache is None or cache.storage is None:
             raise RuntimeError("attention needs a paged key/value cache binding")
         group = ctx.groups[cache.group]
-        qkv = self.qkv_proj.forward(x)
+        qkv = None
+        if isinstance(x, DeferredNorm):
+            qkv = self.qkv_proj.forward_normed(x)       # the norm folded into the projection, if possible
+            if qkv is None:
+                x = x.materialize()
+        if qkv is None:
+            qkv = self.qkv_proj.forward(x)
         inv_freq = self.position.rotary_inv_freq
         if inv_freq is None and self.position.kind != "none":
             rows = qkv.shape[0]

@@ -178,6 +178,42 @@ class ResidualStream:
     update: Optional[torch.Tensor] = None
 
 
+class DeferredNorm:
+    """``norm(residual [+ update])`` that has not been computed yet.
+
+    A block hands this to a mixer or feed-forward that sets ``accepts_deferred_norm``; such a part may
+    fold the addition and the normalisation into its first kernel and then calls :meth:`fused` with the
+    new residual.  Any other consumer calls :meth:`materialize`, which runs the norm's own kernel.
+    Either way ``residual`` afterwards is the updated residual stream.
+    """
+
+    def __init__(self, norm: "Norm", residual: torch.Tensor, update: Optional[torch.Tensor]):
+        self.norm = norm
+        self.residual = residual
+        self.update = update
+        self._value: Optional[torch.Tensor] = None
+        self.done = False
+
+    @property
+    def rows(self) -> int:
+        return self.residual.shape[0]
+
+    def materialize(self) -> torch.Tensor:
+        if self._value is None:
+            if self.update is None:
+                self._value = self.norm.forward(self.residual)
+            else:
+                self._value = self.norm.forward_add(self.residual, self.update)   # residual += update, in place
+            self.done = True
+        return self._value
+
+    def fused(self, new_residual: Optional[torch.Tensor]) -> None:
+        """A consumer computed the norm inside its own kernel; ``new_residual`` holds ``residual + update``."""
+        if new_residual is not None:
+            self.residual = new_residual
+        self.done = True
+
+
 # ----------------------------------------------------------------------------- part bases
 
 
@@ -215,6 +251,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if ``forward`` also takes a :class:`DeferredNorm` in place of ``x``.
+    accepts_deferred_norm = False
     # True if ``forward`` takes everything that varies from step to step from device tensors of the
     # context (never from its host lists), so that a decode step may be captured in a CUDA graph.
     graph_safe = False
@@ -227,6 +265,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_norm = False     # True if ``forward`` also takes a :class:`DeferredNorm` in place of ``x``
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -237,6 +277,8 @@ class Embedding(Part):
 
 
 class Head(Part):
+    accepts_deferred_norm = False
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
-from .base import BLOCKS, Block, CacheBinding, ResidualStream, StepContext
+from .base import BLOCKS, Block, CacheBinding, DeferredNorm, ResidualStream, StepContext
 
 
 @BLOCKS.register("pre_norm")
@@ -24,12 +24,11 @@ class PreNormBlock(Block):
         return ("input", "post_mixer")
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: Optional[CacheBinding]) -> ResidualStream:
-        residual = stream.residual
-        if stream.update is None:
-            x = self.norms["input"].forward(residual)
-        else:
-            x = self.norms["input"].forward_add(residual, stream.update)
+        # each norm is handed on unevaluated: a part that can fold it into its first kernel does so
+        first = DeferredNorm(self.norms["input"], stream.residual, stream.update)
+        x = first if self.mixer.accepts_deferred_norm else first.materialize()
         mixed = self.mixer.forward(x, ctx, cache)
-        m = self.norms["post_mixer"].forward_add(residual, mixed)
+        second = DeferredNorm(self.norms["post_mixer"], first.residual, mixed)
+        m = second if self.feed_forward.accepts_deferred_norm else second.materialize()
         update = self.feed_forward.forward(m, ctx)
-        return ResidualStream(residual, update)
+        return ResidualStream(second.residual, update)

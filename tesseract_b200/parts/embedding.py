@@ -61,5 +61,14 @@ class LMHead(Head):
         p = spec.params
         return {spec.weights["weight"]: ExpectedTensor((int(p["vocab_size"]), int(p["hidden_size"])))}
 
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    accepts_deferred_norm = True
+
+    def forward(self, x, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .base import DeferredNorm
+
+        if isinstance(x, DeferredNorm):
+            logits = self.proj.forward_normed(x, float32_out=True)
+            if logits is not None:
+                return logits
+            x = x.materialize()
         return self.proj.forward(x, out=out, float32_out=True)

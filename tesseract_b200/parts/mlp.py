@@ -1,8 +1,11 @@
 """Gated feed-forward with the SiLU activation (SwiGLU).
 
 ``down( silu(x Wg^T) * (x Wu^T) )`` (src/cuda/dense_decoder.rs:737-774,
-src/cuda/kernels.rs:191-208).  Gate and up weights are concatenated at load so that one
-product feeds the activation kernel; each output column equals the separate product's.
+src/cuda/kernels.rs:191-208).  Gate and up weights are merged at load so that one product
+feeds the activation; each output column equals the separate product's.  When the
+intermediate size is a multiple of eight the merged rows alternate in blocks of eight
+(eight gate rows, the eight matching up rows, ...), which lets the decode kernel apply
+the activation to its own accumulators; otherwise the gate rows come first.
 """
 
 from __future__ import annotations
@@ -14,7 +17,7 @@ import torch
 from .. import kernels
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
-from .base import FEED_FORWARDS, FeedForward, Runtime, StepContext
+from .base import FEED_FORWARDS, DeferredNorm, FeedForward, Runtime, StepContext
 from .linear import Linear
 
 
@@ -27,7 +30,15 @@ class SwiGLU(FeedForward):
         p = spec.params
         self.hidden_size = int(p["hidden_size"])
         self.intermediate_size = int(p["intermediate_size"])
-        self.gate_up_proj = Linear(torch.cat([tensors["gate"], tensors["up"]], dim=0), runtime)
+        self.interleaved = self.intermediate_size % 8 == 0
+        if self.interleaved:
+            blocks = self.intermediate_size // 8
+            merged = torch.stack([tensors["gate"].view(blocks, 8, self.hidden_size),
+                                  tensors["up"].view(blocks, 8, self.hidden_size)], dim=1)
+            merged = merged.reshape(2 * self.intermediate_size, self.hidden_size)
+        else:
+            merged = torch.cat([tensors["gate"], tensors["up"]], dim=0)
+        self.gate_up_proj = Linear(merged, runtime)
         self.down_proj = Linear(tensors["down"], runtime)
 
     @classmethod
@@ -40,8 +51,25 @@ class SwiGLU(FeedForward):
             w["down"]: ExpectedTensor((hidden, inter)),
         }
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = self.gate_up_proj.forward(x)
-        activated = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gate_up, activated)
+    accepts_deferred_norm = True
+
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        activated = None
+        if isinstance(x, DeferredNorm):
+            if self.interleaved:      # norm, both projections and the activation in one kernel, if the sizes allow
+                activated = self.gate_up_proj.forward_normed(x, epilogue=kernels.EPI_SWIGLU)
+            if activated is None:
+                x = x.materialize()
+        if activated is None:
+            activated = self._activate(x)
         return self.down_proj.forward(activated)
+
+    def _activate(self, x: torch.Tensor) -> torch.Tensor:
+        rows = x.shape[0]
+        activated = torch.empty((rows, self.intermediate_size), dtype=x.dtype, device=x.device)
+        proj = self.gate_up_proj
+        if (self.interleaved and not self.runtime.is_float32 and rows <= 16
+                and kernels.decode_linear_supported(rows, proj.out_features, proj.in_features)):
+            return kernels.decode_linear(proj.weight, activated, x=x, epilogue=kernels.EPI_SWIGLU)
+        gate_up = proj.forward(x)
+        return kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)

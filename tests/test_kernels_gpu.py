@@ -378,3 +378,100 @@ def test_attention_mma_finds_one_far_key_among_hundreds():
             for r in range(new):
                 if first_pos + r >= target:
                     torch.testing.assert_close(out[r].cpu().float(), v, rtol=1e-2, atol=1e-2)
+
+
+def test_silu_mul_interleaved_layout():
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(7)
+    for dtype in DTYPES:
+        for rows, inter in ((3, 8), (5, 200), (17, 8192)):
+            gate, up = (torch.randn(rows, inter) * 2).to(dtype), torch.randn(rows, inter).to(dtype)
+            merged = torch.stack([gate.view(rows, inter // 8, 8), up.view(rows, inter // 8, 8)], dim=2)
+            merged = merged.reshape(rows, 2 * inter).contiguous()
+            out = torch.empty(rows, inter, dtype=dtype, device="cuda")
+            kernels.silu_mul(dev(merged), out, interleaved=True)
+            g, u = gate.double(), up.double()
+            torch.testing.assert_close(out.cpu().double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n, k", [(16, 32), (48, 96), (160, 64), (2048, 2048), (384, 320), (1008, 4096)])
+def test_decode_linear_plain_and_f32(m, n, k):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m * 1000 + n + k)
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    kernels.decode_linear(dev(w), out, x=dev(x))
+    torch.testing.assert_close(out.cpu().double(), want, rtol=1e-2, atol=1e-2)
+    out32 = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    kernels.decode_linear(dev(w), out32, x=dev(x), epilogue=kernels.EPI_F32)
+    torch.testing.assert_close(out32.cpu().double(), want, rtol=1e-4, atol=1e-4)
+    # a strided view of a wider buffer as input (a column slice)
+    wide = torch.randn(m, k + 16).to(torch.bfloat16)
+    kernels.decode_linear(dev(w), out32, x=dev(wide)[:, 8:k + 8], epilogue=kernels.EPI_F32)
+    torch.testing.assert_close(out32.cpu().double(), wide[:, 8:k + 8].double() @ w.double().T, rtol=1e-4, atol=1e-4)
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, n, dtype=torch.float32, device="cuda")
+    kernels.decode_linear(dev(w), alone, x=dev(x[m - 1:m].contiguous()), epilogue=kernels.EPI_F32)
+    kernels.decode_linear(dev(w), out32, x=dev(x), epilogue=kernels.EPI_F32)
+    assert torch.equal(alone[0], out32[m - 1])
+
+
+@pytest.mark.parametrize("m, n, k, eps", [(1, 64, 64, 1e-5), (7, 160, 96, 1e-6), (8, 3072, 2048, 1e-5),
+                                          (13, 512, 1024, 1e-3), (16, 256, 4096, 1e-5)])
+def test_decode_linear_fused_norm_and_swiglu(m, n, k, eps):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m + n + k)
+    res = (torch.randn(m, k) * 2).to(torch.bfloat16)
+    upd = torch.randn(m, k).to(torch.bfloat16)
+    nw = 1 + 0.1 * torch.randn(k)
+    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
+
+    def rounded(t):
+        return t.to(torch.bfloat16).double()
+
+    # norm only
+    x = rounded(llama.rms_norm(res.double(), nw.double(), eps))
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    kernels.decode_linear(dev(w), out, residual=dev(res), norm_weight=dev(nw), eps=eps, epilogue=kernels.EPI_F32)
+    torch.testing.assert_close(out.cpu().double(), x @ w.double().T, rtol=2e-2, atol=2e-2)
+    # add + norm, new residual written apart
+    c = res.double() + upd.double()
+    x = rounded(llama.rms_norm(c, nw.double(), eps))
+    new_res = torch.zeros(m, k, dtype=torch.bfloat16, device="cuda")
+    res_dev = dev(res)
+    kernels.decode_linear(dev(w), out, residual=res_dev, update=dev(upd), norm_weight=dev(nw), eps=eps,
+                          residual_out=new_res, epilogue=kernels.EPI_F32)
+    torch.testing.assert_close(out.cpu().double(), x @ w.double().T, rtol=2e-2, atol=2e-2)
+    assert torch.equal(new_res.cpu(), (res.float() + upd.float()).to(torch.bfloat16))
+    assert torch.equal(res_dev.cpu(), res)                                   # the old residual is left alone
+    with pytest.raises(kernels.KernelError):
+        kernels.decode_linear(dev(w), out, residual=res_dev, update=dev(upd), norm_weight=dev(nw), eps=eps,
+                              residual_out=res_dev, epilogue=kernels.EPI_F32)
+    # add + norm + gate/up + activation
+    gate, up = w[: n // 2], w[n // 2:]
+    merged = torch.stack([gate.view(n // 16, 8, k), up.view(n // 16, 8, k)], dim=1).reshape(n, k).contiguous()
+    act = torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda")
+    kernels.decode_linear(dev(merged), act, residual=res_dev, update=dev(upd), norm_weight=dev(nw), eps=eps,
+                          residual_out=new_res, epilogue=kernels.EPI_SWIGLU)
+    g, u = x @ gate.double().T, x @ up.double().T
+    torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+
+
+def test_decode_linear_refuses_other_sizes():
+    from tesseract_b200 import kernels
+
+    assert not kernels.decode_linear_supported(17, 64, 64)
+    assert not kernels.decode_linear_supported(4, 72, 64)
+    assert not kernels.decode_linear_supported(4, 64, 72)
+    assert kernels.decode_linear_supported(16, 128256, 2048, kernels.PRO_ADD_NORM)
+    assert not kernels.decode_linear_supported(16, 64, 8192, kernels.PRO_ADD_NORM)      # rows would not fit shared memory
+    with pytest.raises(kernels.KernelError):
+        kernels.decode_linear(torch.zeros(64, 72, dtype=torch.bfloat16, device="cuda"),
+                              torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda"),
+                              x=torch.zeros(2, 72, dtype=torch.bfloat16, device="cuda"))
