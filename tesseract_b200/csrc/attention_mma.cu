@@ -12,8 +12,8 @@
 //                          each and share every K/V tile.  For sequences with more than 16 rows.
 //   tb_attention_decode  : sequences with at most 16 rows (decode, and tiny portions); one CTA per
 //                          (key split, kv head, sequence); its 4 warps share the 16 rows and own 16
-//                          keys of every 64-key tile, are merged in shared memory, and the splits are
-//                          merged by tb_attention_combine from 32-bit partials in scratch memory.
+//                          keys of every 64-key tile, are merged in shared memory, and the split that finishes
+//                          last merges all splits from 32-bit partials in scratch memory.
 // K/V tiles come in through cp.async (16-byte chunks, XOR-swizzled in shared memory, double
 // buffered); the products are mma.sync.m16n8k16 bf16 with fragments from ldmatrix.
 // head_dim may be any multiple of 16 up to 256: tiles are zero-padded to 32/64/128/256 columns.
@@ -79,6 +79,7 @@ struct AttnParams {
     const int* block_table;      // [R, bt_stride]
     float* part_o;               // [splits][rows][num_heads][D]   (decode only)
     float* part_ml;              // [splits][rows][num_heads][2]
+    int* counters;               // [num_seqs][num_kv_heads] arrival counts of the splits; zero between launches
     int64_t q_stride, out_stride;
     int bt_stride, total_rows;
     int num_heads, num_kv_heads, group, head_dim, page_shift, page_size, window, splits;
@@ -333,6 +334,8 @@ template <int D>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
     constexpr int BN = 64;
     extern __shared__ __align__(128) unsigned char smem[];
+    pdl_trigger();
+    pdl_wait();
     const int split = blockIdx.x, kv_head = blockIdx.y, seq = blockIdx.z;
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
@@ -440,36 +443,62 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
             }
         }
     }
-}
+    if (p.splits == 1) return;
 
-// Merges the splits of the decode kernel: one block per (sequence, head).
-template <int D>
-__global__ void attention_combine_kernel(const AttnParams p) {
-    const int seq = blockIdx.x, head = blockIdx.y;
-    const int first_row = p.row_start[seq];
-    const int q_len = p.row_start[seq + 1] - first_row;
-    if (q_len * p.group > 16) return;
-    for (int qpos = 0; qpos < q_len; ++qpos) {
-        const int row = first_row + qpos;
+    // The split that arrives last merges all of them (a fixed order over the splits, so the result does not
+    // depend on which one that is) and leaves the counter at zero for the next launch.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = p.counters + seq * p.num_kv_heads + kv_head;
+        const int ticket = atomicAdd(counter, 1);
+        is_last = ticket == p.splits - 1;
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // weights of the splits per row, computed side by side: wgt[s][r] = 2^(m_s - max m) (0 for an empty split)
+    float* wgt = reinterpret_cast<float*>(smem);              // [splits][16]
+    float* row_big = wgt + p.splits * 16;                     // [16]
+    float* row_sum = row_big + 16;                            // [16]
+    for (int idx = threadIdx.x; idx < p.splits * n_rows; idx += kThreads) {
+        const int s = idx / n_rows, r = idx - s * n_rows;
+        const int qpos = r / p.group, g = r - qpos * p.group;
+        const int64_t slot = ((int64_t)s * p.total_rows + first_row + qpos) * p.num_heads + kv_head * p.group + g;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2));
+        wgt[s * 16 + r] = ml.y > 0.0f ? ml.x : kMasked;        // the maximum for now
+        wgt[(p.splits + 2 + s) * 16 + r] = ml.y;               // the sums, parked behind row_big / row_sum
+    }
+    __syncthreads();
+    if (threadIdx.x < n_rows) {
+        const int r = threadIdx.x;
         float big = kMasked;
+        for (int s = 0; s < p.splits; ++s) big = fmaxf(big, wgt[s * 16 + r]);
+        float sum = 0.0f;
         for (int s = 0; s < p.splits; ++s) {
-            const int64_t slot = ((int64_t)s * p.total_rows + row) * p.num_heads + head;
-            if (p.part_ml[slot * 2 + 1] > 0.0f) big = fmaxf(big, p.part_ml[slot * 2]);
+            const float l_s = wgt[(p.splits + 2 + s) * 16 + r];
+            const float w = l_s > 0.0f ? exp2f(wgt[s * 16 + r] - big) : 0.0f;
+            wgt[s * 16 + r] = w;
+            sum += w * l_s;
         }
-        for (int col = threadIdx.x; col < p.head_dim; col += blockDim.x) {
-            float acc = 0.0f, sum = 0.0f;
-            for (int s = 0; s < p.splits; ++s) {
-                const int64_t slot = ((int64_t)s * p.total_rows + row) * p.num_heads + head;
-                const float ls = p.part_ml[slot * 2 + 1];
-                if (ls > 0.0f) {  // an empty split left nothing behind
-                    const float wgt = exp2f(p.part_ml[slot * 2] - big);
-                    acc += wgt * p.part_o[slot * D + col];
-                    sum += wgt * ls;
-                }
-            }
-            p.out[(int64_t)row * p.out_stride + (int64_t)head * p.head_dim + col] =
-                __float2bfloat16_rn(acc / fmaxf(sum, 1.0e-8f));
-        }
+        row_sum[r] = sum;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rows * D; idx += kThreads) {
+        const int r = idx / D, col = idx - r * D;
+        if (col >= p.head_dim) continue;
+        const int qpos = r / p.group, g = r - qpos * p.group;
+        const int head = kv_head * p.group + g;
+        const int row = first_row + qpos;
+        const float* src = p.part_o + ((int64_t)row * p.num_heads + head) * D + col;
+        const int64_t split_stride = (int64_t)p.total_rows * p.num_heads * D;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < p.splits; ++s) acc += wgt[s * 16 + r] * __ldcg(src + s * split_stride);
+        p.out[(int64_t)row * p.out_stride + (int64_t)head * p.head_dim + col] =
+            __float2bfloat16_rn(acc / fmaxf(row_sum[r], 1.0e-8f));
     }
 }
 
@@ -493,7 +522,9 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
     }
     if (run_decode) {
         const size_t tiles = (size_t)16 * D * 2 + (size_t)2 * 2 * 64 * D * 2;
-        const size_t merge = (size_t)(2 * kWarps * 16 + kWarps * 16 * D) * sizeof(float);
+        const size_t merge_a = (size_t)(2 * kWarps * 16 + kWarps * 16 * D) * sizeof(float);
+        const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
+        const size_t merge = merge_a > merge_b ? merge_a : merge_b;
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = attention_decode_kernel<D>;
         if (smem > 48 * 1024) {
@@ -501,13 +532,8 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
             if (err != cudaSuccess) return (int)err;
         }
         dim3 grid(p.splits, p.num_kv_heads, num_seqs);
-        kernel<<<grid, kThreads, smem, stream>>>(p);
+        if (cudaError_t err = tb_launch_pdl(kernel, grid, dim3(kThreads), smem, stream, p)) return (int)err;
         if (int status = tb_launch_status()) return status;
-        if (p.splits > 1) {
-            dim3 cgrid(num_seqs, p.num_heads);
-            attention_combine_kernel<D><<<cgrid, 64, 0, stream>>>(p);
-            if (int status = tb_launch_status()) return status;
-        }
     }
     return 0;
 }
@@ -524,13 +550,15 @@ TB_EXPORT int tb_attention_mma_padded_dim(int head_dim) {
 //   run_tiles  : launch the tile kernel (sequences with more than 16 folded rows)
 //   run_decode : launch the split kernel (sequences with at most 16 folded rows) with `splits` key splits;
 //                splits > 1 needs scratch: part_o float[splits * total_rows * num_heads * padded_dim],
-//                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o.
+//                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o;
+//                counters int[num_seqs * num_kv_heads], all zero before the first launch (each launch leaves
+//                them zero again).
 TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
                                int num_seqs, int total_rows, int max_rows_per_seq, int num_heads, int num_kv_heads,
                                int head_dim, int page_size, int window, float scale, int run_tiles, int run_decode,
                                int splits, float* part_o, float* part_ml, int64_t scratch_floats,
-                               cudaStream_t stream) {
+                               int* counters, cudaStream_t stream) {
     if (num_seqs == 0 || total_rows == 0) return 0;
     const int padded = tb_attention_mma_padded_dim(head_dim);
     if (padded < 0) return padded;
@@ -541,7 +569,7 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
     if (splits < 1) splits = 1;
     if (run_decode && splits > 1) {
         const int64_t need = (int64_t)splits * total_rows * num_heads * padded;
-        if (part_o == nullptr || part_ml == nullptr || need > scratch_floats) return -5;
+        if (part_o == nullptr || part_ml == nullptr || counters == nullptr || need > scratch_floats) return -5;
     }
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
@@ -552,6 +580,7 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
     p.block_table = block_table;
     p.part_o = part_o;
     p.part_ml = part_ml;
+    p.counters = counters;
     p.q_stride = q_stride;
     p.out_stride = out_stride;
     p.bt_stride = bt_stride;

@@ -8,13 +8,16 @@ namespace {
 
 // Part of the library image: present on every GPU that loads this library, until the process exits.
 static __device__ __align__(256) float g_noalloc_scratch[TB_NOALLOC_SCRATCH_FLOATS];
+// Arrival counters of the splits, one per (sequence, kv head).  Zero at load; every call leaves them zero.
+static __device__ __align__(256) int g_noalloc_counters[TB_NOALLOC_COUNTERS];
 
 constexpr int kMaxDevices = 64;
 // Device address of the array, per device.  In host code the name g_noalloc_scratch is only a handle
 // for the runtime, not an address a kernel may use, so the address is asked for once per device.
 float* g_scratch_address[kMaxDevices] = {};
+int* g_counter_address[kMaxDevices] = {};
 
-int scratch_for_current_device(float** ptr) {
+int scratch_for_current_device(float** ptr, int** counters) {
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) return (int)err;
@@ -23,9 +26,14 @@ int scratch_for_current_device(float** ptr) {
         void* address = nullptr;
         err = cudaGetSymbolAddress(&address, g_noalloc_scratch);
         if (err != cudaSuccess) return (int)err;
+        void* counter_address = nullptr;
+        err = cudaGetSymbolAddress(&counter_address, g_noalloc_counters);
+        if (err != cudaSuccess) return (int)err;
+        g_counter_address[device] = static_cast<int*>(counter_address);
         g_scratch_address[device] = static_cast<float*>(address);
     }
     *ptr = g_scratch_address[device];
+    *counters = g_counter_address[device];
     return 0;
 }
 
@@ -50,7 +58,8 @@ TB_EXPORT const char* tb_attention_noalloc_strerror(int code) {
                                      "power of two, num_heads a multiple of num_kv_heads)";
         case TB_ERR_BAD_ALIGN: return "q, out and cache must be 16-byte aligned and q_stride a multiple of 8";
         case TB_NOALLOC_TOO_LARGE: return "the call needs more than the 16 MiB static scratch array "
-                                          "(splits * total_rows * num_heads * (padded_head_dim + 2) floats); "
+                                          "(splits * total_rows * num_heads * (padded_head_dim + 2) floats) or "
+                                          "more than 16384 (sequence, kv head) pairs; "
                                           "use fewer splits or rows, or the entry point that takes scratch buffers";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown refusal code";
     }
@@ -65,8 +74,10 @@ TB_EXPORT int tb_attention_decode_noalloc(const void* q, int64_t q_stride, void*
     const int64_t need = tb_attention_noalloc_floats_needed(splits, total_rows, num_heads, head_dim);
     if (need < 0) return (int)need;
     if (need > (int64_t)TB_NOALLOC_SCRATCH_FLOATS) return TB_NOALLOC_TOO_LARGE;
+    if ((int64_t)num_seqs * num_kv_heads > (int64_t)TB_NOALLOC_COUNTERS) return TB_NOALLOC_TOO_LARGE;
     float* scratch = nullptr;
-    if (int status = scratch_for_current_device(&scratch)) return status;
+    int* counters = nullptr;
+    if (int status = scratch_for_current_device(&scratch, &counters)) return status;
     const int padded = tb_attention_mma_padded_dim(head_dim);
     const int64_t part_o_floats = round_up_64((int64_t)splits * total_rows * num_heads * padded);
     float* part_o = scratch;
@@ -74,5 +85,5 @@ TB_EXPORT int tb_attention_decode_noalloc(const void* q, int64_t q_stride, void*
     return tb_attention_mma(q, q_stride, out, out_stride, cache, row_start, seq_begin, block_table, bt_stride,
                             num_seqs, total_rows, max_rows_per_seq, num_heads, num_kv_heads, head_dim, page_size,
                             window, scale, /*run_tiles=*/0, /*run_decode=*/1, splits, part_o, part_ml, part_o_floats,
-                            stream);
+                            counters, stream);
 }

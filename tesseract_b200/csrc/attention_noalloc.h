@@ -15,14 +15,17 @@
 // which this library is loaded carries that array from load until the process exits, whether the
 // entry point is ever called or not.  A call needs
 //     splits * total_rows * num_heads * (padded_head_dim + 2) floats (+ up to 63 of padding),
-// where padded_head_dim is head_dim rounded up to 32, 64, 128 or 256; a call that needs more is
-// refused with TB_NOALLOC_TOO_LARGE and nothing is launched.
+// where padded_head_dim is head_dim rounded up to 32, 64, 128 or 256; a call that needs more, or that
+// has more than TB_NOALLOC_COUNTERS (sequence, kv head) pairs (a second, 64 KiB static array counts the
+// splits that have finished for each pair), is refused with TB_NOALLOC_TOO_LARGE and nothing is launched.
 //
 // Rules of use.
 //  * The first call on each device looks the array's device address up (once, with that device
 //    current).  Make that first call outside of any stream capture.
-//  * All calls share the one array, and it keeps whatever the last call left in it.  Nothing in it
-//    has to start at zero: every slot the merge step reads is written earlier in the same call.
+//  * All calls share the arrays, and they keep whatever the last call left in them.  Nothing in the
+//    float array has to start at zero: every slot the merge step reads is written earlier in the same
+//    call.  The counters must be zero when a call starts; they are zero at load, and the split that
+//    merges puts its counter back to zero, so a call that ran to completion leaves them ready.
 //  * Because the array is shared, two calls whose kernels can overlap on the GPU (different
 //    streams, or different host threads) race on it.  Keep calls on one device in stream order.
 //  * Only sequences with at most 16 folded rows (new tokens * num_heads / num_kv_heads) are
@@ -34,6 +37,7 @@
 #include <stdint.h>
 
 #define TB_NOALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+#define TB_NOALLOC_COUNTERS 16384
 #define TB_NOALLOC_TOO_LARGE (-5)
 
 #ifdef __cplusplus

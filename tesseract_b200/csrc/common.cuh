@@ -19,6 +19,29 @@
 
 enum TbDtype : int { TB_F32 = 0, TB_BF16 = 1 };
 
+// Programmatic dependent launch.  A kernel started with tb_launch_pdl may begin while the kernel before it in
+// the stream is still draining; everything it does before pdl_wait() must not depend on that kernel's results
+// (reading weights is fine).  pdl_trigger() in a kernel lets the next such kernel start early.  Both are no-ops
+// for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t tb_launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}
+
 static inline int tb_launch_status() {
     cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? 0 : (int)err;

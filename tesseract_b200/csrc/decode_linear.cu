@@ -11,9 +11,9 @@
 //
 // Why not the library: at these sizes a decode layer is a chain of launches of a few microseconds
 // each, and the norm and activation kernels between the products cost as much as the products.
-// One CTA owns 16 output features; its 8 warps split K, each streaming its slice of the 16 weight
-// rows straight from global memory into mma.sync.m16n8k16 A fragments (weights are the 16-row
-// operand, the batch rows the 8-column operand), and are summed in a fixed order in shared memory.
+// A CTA owns tiles of 32 output features; its 16 warps split K, each streaming its slice of the 32 weight
+// rows through a private cp.async ring in shared memory into mma.sync.m16n8k16 A fragments (weights are
+// the 16-row operand, the batch rows the 8-column operand); the warps are summed in a fixed order.
 // Each lane loads 16 contiguous bytes per weight row and 32-wide K block; the products pair weight
 // and activation elements in the same permuted K order, so no shuffle or shared-memory transpose is
 // needed.  The reduction order depends on K alone.
@@ -21,8 +21,10 @@
 
 namespace {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
+constexpr int kMaxCtas = 296;  // two resident CTAs per SM
+constexpr int kStages = 3;     // ring depth per warp
 
 enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2 };
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -55,159 +57,256 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // MT: number of 8-row batch tiles (1 or 2).
 template <int MT, int PRO, int EPI>
-__global__ void __launch_bounds__(kThreads) decode_linear_kernel(const LinearParams p) {
+__global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
     const int K = p.K;
     constexpr int ROWS = 8 * MT;
 
-    // shared memory: [ROWS][K + 32] bf16 normalised activations (PRO only), then the warps' partial sums
+    // shared memory: [ROWS][K + 32] bf16 normalised activations (PRO only), the warps' partial sums, the rings
     const int x_pitch = K + 32;  // 64 bytes of padding: the eight rows a quarter-warp reads hit distinct banks
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
     float* partial = reinterpret_cast<float*>(smem + (PRO != PRO_NONE ? (size_t)ROWS * x_pitch * 2 : 0));
 
+    // K is cut into 32-wide blocks; warp w takes blocks w, w + 16, ... of every tile (fixed by K alone).  A tile
+    // is 32 output features (two 16-row operands that share the activation fragments).  A CTA walks over several
+    // tiles, so that the prologue above is paid once.  Each warp keeps a private ring of STAGES blocks in shared
+    // memory, filled by cp.async: a lane copies exactly the 16-byte pieces that it later reads back itself, so the
+    // ring needs no barrier, only cp.async.wait_group, and runs on across tile boundaries.
+    constexpr int X_BYTES = (PRO == PRO_NONE) ? 512 * MT : 0;   // activations ride along when they come from memory
+    constexpr int STAGE_BYTES = 2048 + X_BYTES;
+    constexpr int STAGES = kStages;
+    const int blocks = K / 32;
+    const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
+    const int num_tiles = p.N / 32;
+    const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    unsigned char* ring = smem + (PRO != PRO_NONE ? (size_t)ROWS * x_pitch * 2 : 0) +
+                          (size_t)kWarps * 32 * ROWS * sizeof(float) + (size_t)warp * STAGES * STAGE_BYTES;
+    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
+    const uint32_t lane_off = (uint32_t)(g * 64 + t * 16);
+    const int64_t tile_stride = (int64_t)gridDim.x * 32 * K;     // elements between this CTA's consecutive tiles
+
+    // producer cursor: tile pi, block-of-warp pj, ring slot ps
+    int pi = 0, pj = 0, ps = 0;
+    const __nv_bfloat16* p_src = p.w + ((int64_t)blockIdx.x * 32 + g) * K + 8 * t;   // row g of the current tile
+    auto issue = [&](bool with_x) {
+        if (pi < my_tiles) {
+            const int b = warp + pj * kWarps;
+            if (b < blocks) {
+                const uint32_t dst = ring_addr + (uint32_t)ps * STAGE_BYTES + lane_off;
+                const __nv_bfloat16* src = p_src + b * 32;
+                cp_async16(dst, src);
+                cp_async16(dst + 512, src + (int64_t)8 * K);
+                cp_async16(dst + 1024, src + (int64_t)16 * K);
+                cp_async16(dst + 1536, src + (int64_t)24 * K);
+                if (PRO == PRO_NONE && with_x) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int row = mt * 8 + g;
+                        if (row < p.M)
+                            cp_async16(dst + 2048 + mt * 512, p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
+                    }
+                }
+            }
+            if (++pj == bpw) {
+                pj = 0;
+                ++pi;
+                p_src += tile_stride;
+            }
+            if (++ps == STAGES) ps = 0;
+        }
+        cp_async_commit();   // a group per slot, empty or not, keeps the wait count fixed
+    };
+
+    float acc[2][MT][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
+    pdl_trigger();
+#pragma unroll
+    for (int q = 0; q < STAGES - 1; ++q) issue(false);   // weights do not depend on the kernel before: start now
+    pdl_wait();                                      // from here on the previous kernel's results are visible
+
     if (PRO != PRO_NONE) {
-        // every CTA normalises the (few) rows itself; CTA 0 also stores the new residual
-        for (int row = warp; row < ROWS; row += kWarps) {
-            __nv_bfloat16* dst = xs + (size_t)row * x_pitch;
-            if (row >= p.M) {
-                for (int j = lane * 8; j < K; j += 256) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
-                continue;
-            }
-            const __nv_bfloat16* r = p.res + (int64_t)row * K;
-            const __nv_bfloat16* u = PRO == PRO_ADD_NORM ? p.upd + (int64_t)row * K : nullptr;
-            float ss = 0.0f;
-            for (int j = lane * 8; j < K; j += 256) {
+        // Every CTA normalises the (few) rows itself, all threads side by side along K; CTA 0 also stores the
+        // new residual.  Two passes over the rows (the second one hits L1): sums of squares, then the scaling.
+        float* red = partial;  // [kWarps][ROWS] partial sums of squares (the partial-sum area is free until later)
+        float ss[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) ss[r] = 0.0f;
+        for (int j = threadIdx.x * 8; j < K; j += kThreads * 8) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r >= p.M) break;
                 float v[8];
-                Packet<__nv_bfloat16>::load(r + j, v);
+                Packet<__nv_bfloat16>::load(p.res + (int64_t)r * K + j, v);
                 if (PRO == PRO_ADD_NORM) {
                     float a[8];
-                    Packet<__nv_bfloat16>::load(u + j, a);
+                    Packet<__nv_bfloat16>::load(p.upd + (int64_t)r * K + j, a);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] += a[e];
-                    if (blockIdx.x == 0) Packet<__nv_bfloat16>::store(p.res_out + (int64_t)row * K + j, v);
+                    if (blockIdx.x == 0) Packet<__nv_bfloat16>::store(p.res_out + (int64_t)r * K + j, v);
                 }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+                for (int e = 0; e < 8; ++e) ss[r] += v[e] * v[e];
             }
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
-            for (int j = lane * 8; j < K; j += 256) {
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            ss[r] = warp_sum(ss[r]);
+            if (lane == 0) red[warp * ROWS + r] = ss[r];
+        }
+        __syncthreads();
+        float* inv_s = red + kWarps * ROWS;   // [ROWS] reciprocal root mean squares
+        if (threadIdx.x < ROWS) {
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) total += red[w * ROWS + threadIdx.x];
+            inv_s[threadIdx.x] = 1.0f / sqrtf(total / (float)K + p.eps);
+        }
+        __syncthreads();
+        for (int j = threadIdx.x * 8; j < K; j += kThreads * 8) {
+            float nw[8];
+            *reinterpret_cast<float4*>(nw) = *reinterpret_cast<const float4*>(p.norm_w + j);
+            *reinterpret_cast<float4*>(nw + 4) = *reinterpret_cast<const float4*>(p.norm_w + j + 4);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
                 float v[8];
-                Packet<__nv_bfloat16>::load(r + j, v);
-                if (PRO == PRO_ADD_NORM) {
-                    float a[8];
-                    Packet<__nv_bfloat16>::load(u + j, a);
+                if (r < p.M) {
+                    const float inv = inv_s[r];
+                    Packet<__nv_bfloat16>::load(p.res + (int64_t)r * K + j, v);
+                    if (PRO == PRO_ADD_NORM) {
+                        float a[8];
+                        Packet<__nv_bfloat16>::load(p.upd + (int64_t)r * K + j, a);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] += a[e];
+                        for (int e = 0; e < 8; ++e) v[e] += a[e];
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * nw[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
                 }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * p.norm_w[j + e];
-                Packet<__nv_bfloat16>::store(dst + j, v);
+                Packet<__nv_bfloat16>::store(xs + (size_t)r * x_pitch + j, v);
             }
         }
         __syncthreads();
     }
 
-    // K is cut into 32-wide blocks; warp w takes blocks w, w + 8, ...  (fixed by K alone)
-    const int blocks = K / 32;
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[mt][e] = 0.0f;
-    const __nv_bfloat16* w_lo = p.w + (int64_t)(n0 + g) * K + 8 * t;
-    const __nv_bfloat16* w_hi = w_lo + (int64_t)8 * K;
-
-    constexpr int UNROLL = 4;
-    for (int b0 = warp; b0 < blocks; b0 += kWarps * UNROLL) {
-        uint4 wa[UNROLL], wb[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int b = b0 + u * kWarps;
+    int cs = 0;        // consumer ring slot
+    int consumed = 0;  // the first STAGES - 1 slots were filled before pdl_wait(), without their activations
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        for (int j = 0; j < bpw; ++j) {
+            issue(true);
+            cp_async_wait<STAGES - 1>();
+            const int b = warp + j * kWarps;
             if (b < blocks) {
-                wa[u] = ldg_stream(w_lo + b * 32);
-                wb[u] = ldg_stream(w_hi + b * 32);
-            }
-        }
+                const unsigned char* st = ring + (size_t)cs * STAGE_BYTES + lane_off;
+                const uint4 w0 = *reinterpret_cast<const uint4*>(st);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(st + 512);
+                const uint4 w2 = *reinterpret_cast<const uint4*>(st + 1024);
+                const uint4 w3 = *reinterpret_cast<const uint4*>(st + 1536);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int b = b0 + u * kWarps;
-            if (b >= blocks) break;
+                for (int mt = 0; mt < MT; ++mt) {
+                    uint4 xa;
+                    const int row = mt * 8 + g;
+                    if (PRO != PRO_NONE)
+                        xa = *reinterpret_cast<const uint4*>(xs + (size_t)row * x_pitch + b * 32 + 8 * t);
+                    else if (row >= p.M)
+                        xa = make_uint4(0, 0, 0, 0);
+                    else if (consumed < STAGES - 1)
+                        xa = *reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
+                    else
+                        xa = *reinterpret_cast<const uint4*>(st + 2048 + mt * 512);
+                    mma_bf16(acc[0][mt], w0.x, w1.x, w0.y, w1.y, xa.x, xa.y);
+                    mma_bf16(acc[0][mt], w0.z, w1.z, w0.w, w1.w, xa.z, xa.w);
+                    mma_bf16(acc[1][mt], w2.x, w3.x, w2.y, w3.y, xa.x, xa.y);
+                    mma_bf16(acc[1][mt], w2.z, w3.z, w2.w, w3.w, xa.z, xa.w);
+                }
+            }
+            if (++cs == STAGES) cs = 0;
+            ++consumed;
+        }
+        // end of a tile: sum the warps in a fixed order: partial[warp][feature 0..31][batch row 0..ROWS-1]
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int n0 = tile * 32;
+        float* dst = partial + (size_t)warp * 32 * ROWS;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                uint4 xb;
-                const int row = mt * 8 + g;
-                if (PRO != PRO_NONE) {
-                    xb = *reinterpret_cast<const uint4*>(xs + (size_t)row * x_pitch + b * 32 + 8 * t);
-                } else if (row < p.M) {
-                    xb = *reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
-                } else {
-                    xb = make_uint4(0, 0, 0, 0);
+                dst[(h * 16 + g) * ROWS + mt * 8 + 2 * t] = acc[h][mt][0];
+                dst[(h * 16 + g) * ROWS + mt * 8 + 2 * t + 1] = acc[h][mt][1];
+                dst[(h * 16 + g + 8) * ROWS + mt * 8 + 2 * t] = acc[h][mt][2];
+                dst[(h * 16 + g + 8) * ROWS + mt * 8 + 2 * t + 1] = acc[h][mt][3];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
+            }
+        __syncthreads();
+        if (EPI == EPI_SWIGLU) {
+            // of every 16 features the first eight are gates, the last eight the matching up projections
+            for (int idx = threadIdx.x; idx < 16 * ROWS; idx += kThreads) {
+                const int f = idx / ROWS, m = idx - f * ROWS;   // f: activation column within the tile (0..15)
+                if (m >= p.M) continue;
+                const int gate_row = (f >> 3) * 16 + (f & 7);
+                float gate = 0.0f, up = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) {
+                    gate += partial[(size_t)w * 32 * ROWS + gate_row * ROWS + m];
+                    up += partial[(size_t)w * 32 * ROWS + (gate_row + 8) * ROWS + m];
                 }
-                mma_bf16(acc[mt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
-                mma_bf16(acc[mt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+                const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + tile * 16 + f] =
+                    __float2bfloat16_rn(act);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < 32 * ROWS; idx += kThreads) {
+                const int m = idx / 32, f = idx - m * 32;  // consecutive threads write consecutive features
+                if (m >= p.M) continue;
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) sum += partial[(size_t)w * 32 * ROWS + f * ROWS + m];
+                if (EPI == EPI_F32)
+                    reinterpret_cast<float*>(p.out)[(int64_t)m * p.out_stride + n0 + f] = sum;
+                else
+                    reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + n0 + f] =
+                        __float2bfloat16_rn(sum);
             }
         }
-    }
-
-    // sum the warps in a fixed order: partial[warp][feature 0..15][batch row 0..ROWS-1]
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        float* dst = partial + (size_t)warp * 16 * ROWS;
-        dst[g * ROWS + mt * 8 + 2 * t] = acc[mt][0];
-        dst[g * ROWS + mt * 8 + 2 * t + 1] = acc[mt][1];
-        dst[(g + 8) * ROWS + mt * 8 + 2 * t] = acc[mt][2];
-        dst[(g + 8) * ROWS + mt * 8 + 2 * t + 1] = acc[mt][3];
-    }
-    __syncthreads();
-    if (EPI == EPI_SWIGLU) {
-        // features 0..7 are gates, 8..15 the matching up projections
-        for (int idx = threadIdx.x; idx < 8 * ROWS; idx += kThreads) {
-            const int f = idx / ROWS, m = idx - f * ROWS;
-            if (m >= p.M) continue;
-            float gate = 0.0f, up = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                gate += partial[(size_t)w * 16 * ROWS + f * ROWS + m];
-                up += partial[(size_t)w * 16 * ROWS + (f + 8) * ROWS + m];
-            }
-            const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + blockIdx.x * 8 + f] =
-                __float2bfloat16_rn(act);
-        }
-    } else {
-        for (int idx = threadIdx.x; idx < 16 * ROWS; idx += kThreads) {
-            const int m = idx / 16, f = idx - m * 16;  // consecutive threads write consecutive features
-            if (m >= p.M) continue;
-            float sum = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) sum += partial[(size_t)w * 16 * ROWS + f * ROWS + m];
-            if (EPI == EPI_F32)
-                reinterpret_cast<float*>(p.out)[(int64_t)m * p.out_stride + n0 + f] = sum;
-            else
-                reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + n0 + f] = __float2bfloat16_rn(sum);
-        }
+        __syncthreads();  // the partial sums are reused by the next tile
     }
 }
 
 template <int MT, int PRO, int EPI>
 int launch(const LinearParams& p, cudaStream_t stream) {
     constexpr int ROWS = 8 * MT;
-    size_t smem = (size_t)kWarps * 16 * ROWS * sizeof(float);
+    constexpr int STAGE_BYTES = 2048 + (PRO == PRO_NONE ? 512 * MT : 0);
+    size_t smem = (size_t)kWarps * 32 * ROWS * sizeof(float) + (size_t)kWarps * kStages * STAGE_BYTES;
     if (PRO != PRO_NONE) smem += (size_t)ROWS * (p.K + 32) * 2;
     auto kernel = decode_linear_kernel<MT, PRO, EPI>;
     if (smem > 48 * 1024) {
-        if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
+        if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
-    kernel<<<p.N / 16, kThreads, smem, stream>>>(p);
-    return tb_launch_status();
+    const int tiles = p.N / 32;
+    const int per_cta = (tiles + kMaxCtas - 1) / kMaxCtas;           // tiles per CTA, evenly spread
+    const int grid = (tiles + per_cta - 1) / per_cta;
+    cudaError_t err = tb_launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, p);
+    return err == cudaSuccess ? tb_launch_status() : (int)err;
 }
 
 template <int MT>
@@ -231,8 +330,8 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
 
 // 1 if the sizes are ones this kernel takes, else 0 (the caller then uses the general path).
 TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
-    if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < 32 || K % 32 != 0) return 0;
-    if (prologue != PRO_NONE && (size_t)(M <= 8 ? 8 : 16) * (K + 32) * 2 > 160 * 1024) return 0;
+    if (M < 1 || M > 16 || N < 32 || N % 32 != 0 || K < 32 || K % 32 != 0) return 0;
+    if (prologue != PRO_NONE && (size_t)(M <= 8 ? 8 : 16) * (K + 32) * 2 > 96 * 1024) return 0;
     return 1;
 }
 

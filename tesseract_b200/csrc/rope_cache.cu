@@ -20,6 +20,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int64_t qkv_stride, co
                                      int bt_stride, const float* __restrict__ inv_freq, T* __restrict__ cache,
                                      int num_heads, int num_kv_heads, int head_dim, int page_size, int write_kv) {
     extern __shared__ float trig[];  // cos[half] then sin[half] of this row's angles, shared by all heads
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int pos = positions[row];
     const int half = head_dim >> 1;
@@ -115,15 +117,16 @@ int launch(void* qkv, int64_t qkv_stride, const int* positions, const int* seq_o
     int threads = 32;
     while (threads < 512 && threads < work) threads <<= 1;
     const size_t smem = (size_t)head_dim * sizeof(float);
+    cudaError_t err;
     if (vec)
-        rope_kv_write_kernel<T, true><<<rows, threads, smem, stream>>>(
-            (T*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
-            num_kv_heads, head_dim, page_size, write_kv);
+        err = tb_launch_pdl(rope_kv_write_kernel<T, true>, dim3(rows), dim3(threads), smem, stream, (T*)qkv, qkv_stride,
+                            positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
+                            num_kv_heads, head_dim, page_size, write_kv);
     else
-        rope_kv_write_kernel<T, false><<<rows, threads, smem, stream>>>(
-            (T*)qkv, qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
-            num_kv_heads, head_dim, page_size, write_kv);
-    return tb_launch_status();
+        err = tb_launch_pdl(rope_kv_write_kernel<T, false>, dim3(rows), dim3(threads), smem, stream, (T*)qkv,
+                            qkv_stride, positions, seq_of_row, block_table, bt_stride, inv_freq, (T*)cache, num_heads,
+                            num_kv_heads, head_dim, page_size, write_kv);
+    return err == cudaSuccess ? tb_launch_status() : (int)err;
 }
 
 }  // namespace

@@ -30,9 +30,40 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* scratch) {
     MaxIdx best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best.v) best = MaxIdx{v, i};  // ascending i per thread keeps the lowest index on ties
+    if (((uintptr_t)row & 15) == 0) {
+        // 16-byte loads, four of them in flight per thread; ascending i per thread keeps the lowest index on ties
+        const int packets = vocab >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        int i = threadIdx.x;
+        for (; i + 3 * (int)blockDim.x < packets; i += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = row4[i + u * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int base = (i + u * blockDim.x) * 4;
+                if (v[u].x > best.v) best = MaxIdx{v[u].x, base};
+                if (v[u].y > best.v) best = MaxIdx{v[u].y, base + 1};
+                if (v[u].z > best.v) best = MaxIdx{v[u].z, base + 2};
+                if (v[u].w > best.v) best = MaxIdx{v[u].w, base + 3};
+            }
+        }
+        for (; i < packets; i += blockDim.x) {
+            const float4 v = row4[i];
+            if (v.x > best.v) best = MaxIdx{v.x, i * 4};
+            if (v.y > best.v) best = MaxIdx{v.y, i * 4 + 1};
+            if (v.z > best.v) best = MaxIdx{v.z, i * 4 + 2};
+            if (v.w > best.v) best = MaxIdx{v.w, i * 4 + 3};
+        }
+        for (int j = packets * 4 + threadIdx.x; j < vocab; j += blockDim.x) {
+            const float v = row[j];
+            if (v > best.v) best = MaxIdx{v, j};
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best.v) best = MaxIdx{v, i};
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -240,10 +240,22 @@ def _scratch(device, name: str, floats: int) -> torch.Tensor:
     return buf
 
 
+_attention_counters = {}
+
+
+def _counters(device, count: int) -> torch.Tensor:
+    """Zeroed int32 arrival counters for the split decode kernel (each launch leaves them zero again)."""
+    buf = _attention_counters.get(device)
+    if buf is None or buf.numel() < count:
+        buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _attention_counters[device] = buf
+    return buf
+
+
 def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
-    """How many key splits the decode kernel uses: enough CTAs for every SM, at least two 64-key tiles each."""
+    """How many key splits the decode kernel uses: about four CTAs for every SM, at least two 64-key tiles each."""
     ctas = max(1, num_seqs * num_kv_heads)
-    want = -(-2 * _SM_COUNT // ctas)
+    want = -(-4 * _SM_COUNT // ctas)
     blocks = -(-max_context // 64)
     return max(1, min(want, -(-blocks // 2), 64))
 
@@ -268,9 +280,10 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_s
     padded = lib.tb_attention_mma_padded_dim(_i32(head_dim))
     if padded < 0:
         raise KernelError(f"attention_mma: head_dim {head_dim} is not a multiple of 16 up to 256")
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
     capacity = 0
     if run_decode and splits > 1:
+        counters = _counters(q.device, num_seqs * num_kv_heads)
         capacity = splits * rows * num_heads * padded
         part_o = _scratch(q.device, "part_o", capacity)
         part_ml = _scratch(q.device, "part_ml", splits * rows * num_heads * 2)
@@ -280,7 +293,8 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_s
                                 _i32(num_seqs), _i32(rows), _i32(max_new), _i32(num_heads), _i32(num_kv_heads),
                                 _i32(head_dim), _i32(page_size), _i32(window), _f32(scale),
                                 _i32(1 if run_tiles else 0), _i32(1 if run_decode else 0), _i32(splits),
-                                _ptr(part_o), _ptr(part_ml), _i64(capacity), _stream()), "attention_mma")
+                                _ptr(part_o), _ptr(part_ml), _i64(capacity), _ptr(counters), _stream()),
+           "attention_mma")
     return out
 
 
