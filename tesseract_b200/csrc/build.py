@@ -43,6 +43,7 @@ SOURCES: Dict[str, List[str]] = {
     "attention_noalloc": [],
     "gemm_f32": [],
     "decode_linear": [],
+    "gemm_tcgen05": [],
     "sampling": [],
 }
 

@@ -1,0 +1,316 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: C[M,N] = A[M,K] . W[N,K]^T, 32-bit accumulation.
+//
+// The Blackwell-native path for prompt-sized batches.  One CTA computes a 128 x 256 tile of C:
+//   * warp 0, one elected lane: TMA producer.  Tiles of A (128 x 64) and W (256 x 64) are brought into a
+//     four-stage ring in shared memory by cp.async.bulk.tensor with the 128-byte swizzle; completion is
+//     signalled on an mbarrier per stage (no multicast: every CTA issues its own loads).
+//   * warp 1, one elected lane: issues tcgen05.mma (M128 x N256 x K16, operands from shared memory through
+//     64-bit matrix descriptors, accumulator in tensor memory) and hands each stage back with tcgen05.commit.
+//   * warps 4..7: epilogue.  Each warp reads its 32 lanes of the accumulator with tcgen05.ld, 32 columns at
+//     a time, and stores bfloat16 (or 32-bit) rows, or applies SwiGLU to a weight whose rows interleave eight
+//     gate rows and their eight up rows: out[m, j] = round(silu(gate_j) * up_j) on the unrounded accumulators
+//     (the reference multiplies rounded projections, src/cuda/kernels.rs:191-208; here one rounding fewer).
+// Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by the TMA unit and never stored.
+// Every wait on an mbarrier is bounded: a wait that runs out sets *error, tells the other roles to stop, and the
+// CTA still frees its tensor memory before it returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int kThreads = 256;
+constexpr uint32_t kATileBytes = BM * BK * 2;   // 16 KiB
+constexpr uint32_t kBTileBytes = BN * BK * 2;   // 32 KiB
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+constexpr uint32_t kTmemColumns = 256;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false if the barrier did not flip within the limit or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023) == 1023 && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
+// start address, leading offset 1 (unused for swizzled K-major), 1024 bytes between groups of eight rows,
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor: D = F32, A = B = BF16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+struct GemmParams {
+    void* out;
+    int64_t out_stride;
+    int M, N, K;
+    int* error;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the swizzled tiles need 1024-byte alignment
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), done_bar = smem_u32(&bars[2 * STAGES]);
+    const uint32_t tiles = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        for (int kb = 0; kb < k_blocks; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t parity = ((kb / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
+            if (!mbar_wait(empty0 + 8 * s, parity, &abort_flag)) {
+                abort_flag = 1;
+                atomicExch(p.error, 1);
+                break;
+            }
+            mbar_expect_tx(full0 + 8 * s, kStageBytes);
+            const uint32_t a_dst = tiles + s * kStageBytes;
+            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
+            tma_load_2d(a_dst + kATileBytes, &map_b, full0 + 8 * s, kb * BK, n0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+            const int s = kb % STAGES;
+            if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, &abort_flag)) {
+                abort_flag = 1;
+                atomicExch(p.error, 2);
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = tiles + s * kStageBytes, b_addr = a_addr + kATileBytes;
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+                // inside the 128-byte swizzle atom a step of 16 elements along K is 32 bytes of start address
+                umma_bf16(tmem_base, umma_desc_k_sw128(a_addr + kk * 32), umma_desc_k_sw128(b_addr + kk * 32), idesc,
+                          (kb | kk) != 0);
+            }
+            umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+        }
+        if (ok) umma_commit(done_bar);            // the accumulator is complete once all products are done
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;             // a warp may touch tensor-memory lanes 32*(warp % 4) .. +31
+        const int row = m0 + quarter * 32 + lane;
+        if (mbar_wait(done_bar, 0, &abort_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t acc[32];
+                tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, acc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = n0 + c * 32;
+                if (row >= p.M || col0 >= p.N) continue;
+                if (EPI == EPI_F32) {
+                    float* dst = reinterpret_cast<float*>(p.out) + (int64_t)row * p.out_stride + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (col0 + j < p.N)
+                            *reinterpret_cast<float4*>(dst + j) =
+                                make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
+                                            __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+                } else if (EPI == EPI_BF16) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (col0 + j >= p.N) break;
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j + e]);
+                        Packet<__nv_bfloat16>::store(dst + j, v);
+                    }
+                } else {
+                    // columns come in blocks of sixteen: eight gates, then their eight up projections
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0 / 2;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 16) {
+                        if (col0 + j >= p.N) break;
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float gate = __uint_as_float(acc[j + e]), up = __uint_as_float(acc[j + 8 + e]);
+                            v[e] = gate * (1.0f / (1.0f + expf(-gate))) * up;
+                        }
+                        Packet<__nv_bfloat16>::store(dst + j / 2, v);
+                    }
+                }
+            }
+        } else {
+            abort_flag = 1;
+            atomicExch(p.error, 3);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bfloat16 matrix with `stride` elements between rows, cut into boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return TB_ERR_BAD_SIZE;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {stride * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : TB_ERR_BAD_SIZE;
+}
+
+}  // namespace
+
+// 1 if the kernel takes these sizes.  K and the row strides must be multiples of 8 (16-byte TMA strides), N of 8
+// (16 for the SwiGLU epilogue).
+TB_EXPORT int tb_gemm_tcgen05_supported(int M, int N, int K, int epilogue) {
+    if (M < 1 || N < 8 || K < 8 || K % 8 != 0 || N % 8 != 0) return 0;
+    if (epilogue == EPI_SWIGLU && N % 16 != 0) return 0;
+    return 1;
+}
+
+// error: device int, set non-zero if a bounded wait ran out (the result is then unusable).
+TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, int64_t w_stride, void* out,
+                              int64_t out_stride, int M, int N, int K, int epilogue, int* error,
+                              cudaStream_t stream) {
+    if (!tb_gemm_tcgen05_supported(M, N, K, epilogue)) return TB_ERR_BAD_SIZE;
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16 != 0 || a_stride % 8 != 0 || w_stride % 8 != 0 ||
+        out_stride % 8 != 0)
+        return TB_ERR_BAD_ALIGN;
+    CUtensorMap map_a, map_b;
+    if (int status = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_stride, BM)) return status;
+    if (int status = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, BN)) return status;
+    GemmParams p;
+    p.out = out;
+    p.out_stride = out_stride;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.error = error;
+    const size_t smem = (size_t)STAGES * kStageBytes + 1024;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+#define TB_LAUNCH(E)                                                                                          \
+    {                                                                                                         \
+        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                               (int)smem);                                                    \
+        if (err != cudaSuccess) return (int)err;                                                              \
+        gemm_tcgen05_kernel<E><<<grid, kThreads, smem, stream>>>(map_a, map_b, p);                           \
+    }
+    if (epilogue == EPI_BF16) TB_LAUNCH(EPI_BF16)
+    else if (epilogue == EPI_SWIGLU) TB_LAUNCH(EPI_SWIGLU)
+    else if (epilogue == EPI_F32) TB_LAUNCH(EPI_F32)
+    else return TB_ERR_BAD_SIZE;
+#undef TB_LAUNCH
+    return tb_launch_status();
+}

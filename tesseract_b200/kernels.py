@@ -346,3 +346,50 @@ def decode_linear(weight: torch.Tensor, out: torch.Tensor, *, x: Optional[torch.
                                 _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(prologue), _i32(epilogue),
                                 _stream()), "decode_linear")
     return out
+
+
+_tcgen05_error = {}
+
+
+def _error_word(device) -> torch.Tensor:
+    word = _tcgen05_error.get(device)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _tcgen05_error[device] = word
+    return word
+
+
+def gemm_tcgen05_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    return bool(load_library("gemm_tcgen05").tb_gemm_tcgen05_supported(_i32(rows), _i32(out_features),
+                                                                      _i32(in_features), _i32(epilogue)))
+
+
+def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16) -> torch.Tensor:
+    """``out = a @ weight^T`` on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
+
+    ``EPI_BF16`` / ``EPI_F32`` store ``[M, N]``; ``EPI_SWIGLU`` takes a weight whose rows interleave eight gate rows
+    and their eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``.
+    """
+    _cuda(a, weight, out)
+    m, k = a.shape
+    n = weight.shape[0]
+    _need(a.dtype == weight.dtype == torch.bfloat16, "gemm_tcgen05 takes bfloat16 operands")
+    _need(weight.shape[1] == k and a.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1, "gemm layout")
+    width = n // 2 if epilogue == EPI_SWIGLU else n
+    _need(out.shape == (m, width), "gemm_tcgen05 out shape")
+    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemm_tcgen05 out dtype")
+    lib = load_library("gemm_tcgen05")
+    _check(lib.tb_gemm_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
+                               _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
+                               _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    return out
+
+
+def tcgen05_error(device=None) -> int:
+    """Non-zero if a bounded wait inside a tcgen05 kernel ran out since the last call (synchronises)."""
+    total = 0
+    for dev, word in _tcgen05_error.items():
+        if device is None or dev == device:
+            total |= int(word.item())
+            word.zero_()
+    return total

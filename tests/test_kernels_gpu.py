@@ -475,3 +475,30 @@ def test_decode_linear_refuses_other_sizes():
         kernels.decode_linear(torch.zeros(64, 72, dtype=torch.bfloat16, device="cuda"),
                               torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda"),
                               x=torch.zeros(2, 72, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (1, 256, 64), (130, 264, 72),
+                                     (2048, 3072, 2048), (333, 1000, 520), (77, 16, 8)])
+def test_gemm_tcgen05(m, n, k):
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
+    want = a.double() @ w.double().T
+    out32 = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    kernels.gemm_tcgen05(dev(a), dev(w), out32, epilogue=kernels.EPI_F32)
+    assert kernels.tcgen05_error() == 0, "a bounded wait inside the kernel ran out"
+    torch.testing.assert_close(out32.cpu().double(), want, rtol=1e-4, atol=1e-4)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_tcgen05(dev(a), dev(w), out)
+    assert kernels.tcgen05_error() == 0
+    torch.testing.assert_close(out.cpu().double(), want, rtol=1e-2, atol=1e-2)
+    if n % 16 == 0:
+        gate, up = w[: n // 2], w[n // 2:]
+        merged = torch.stack([gate.view(n // 16, 8, k), up.view(n // 16, 8, k)], dim=1).reshape(n, k).contiguous()
+        act = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_tcgen05(dev(a), dev(merged), act, epilogue=kernels.EPI_SWIGLU)
+        assert kernels.tcgen05_error() == 0
+        g, u = a.double() @ gate.double().T, a.double() @ up.double().T
+        torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
