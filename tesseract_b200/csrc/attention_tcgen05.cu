@@ -1,0 +1,433 @@
+// Prompt-portion attention on the fifth-generation tensor cores (bfloat16, head_dim 64), over cache pages.
+//
+// Same mathematics and the same folding of grouped query heads into tile rows as attention_mma.cu (which see):
+// one CTA owns 128 folded rows (query position x head of the group) of one sequence and one kv head, and
+// walks over the sequence's keys in blocks of 128.  Per block:
+//   S = Q . K^T        tcgen05.mma, M128 x N128 x K64, both operands in shared memory (K-major, 128-byte swizzle),
+//                      accumulator in tensor memory (128 columns)
+//   softmax            four warps, one thread per row: tcgen05.ld of the row, scale, mask, running maximum,
+//                      2^x, 32-bit row sum, probabilities rounded to bfloat16 into a swizzled P tile in shared memory
+//   O_blk = P . V      tcgen05.mma, M128 x N64 x K128, P K-major, V MN-major (the cache's [key][dim] rows as they
+//                      are), into 64 further columns of tensor memory
+//   O = O * corr + O_blk  in registers of the row's thread (tcgen05.ld of 64 columns)
+// Warps 0-3 are the softmax / correction / epilogue warps (warp w owns tensor-memory lanes 32w..32w+31), warps 5-7
+// bring K and V blocks into a ring of shared-memory stages with cp.async through the block table, and one lane
+// of warp 4 issues the tensor-core instructions.  Roles meet on mbarriers; every wait is bounded, and a wait that
+// runs out sets *error, stops the other roles, and the CTA still frees its tensor memory.
+// Two CTAs fit on an SM (about 100 KiB of shared memory and 256 tensor-memory columns each), so one CTA's softmax
+// overlaps the other's products.
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 64;            // head_dim this kernel is built for
+constexpr int BM = 128;          // folded query rows per CTA
+constexpr int BN = 128;          // keys per block
+constexpr int STAGES = 2;        // K/V ring depth
+constexpr int kThreads = 256;
+constexpr int kLoaderThreads = 96;    // warps 5..7
+constexpr uint32_t kTileBytes = BN * D * 2;           // 16 KiB: one K or V block, also the Q tile and half a P tile
+constexpr uint32_t kTmemColumns = 256;                // S: columns 0..127, O_blk: columns 128..191
+constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMasked = -1.0e30f;
+
+struct TcAttnParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const __nv_bfloat16* cache;
+    const int* row_start;
+    const int* seq_begin;
+    const int* block_table;
+    int* error;
+    int64_t q_stride, out_stride;
+    int bt_stride;
+    int num_heads, num_kv_heads, group, page_shift, page_size, window;
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255) == 255 && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+// makes this thread's earlier shared-memory writes visible to the tensor core's (asynchronous) reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile of 128-byte rows with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+// Matrix descriptors for such tiles: version 1, SWIZZLE_128B, 1024 bytes between groups of eight rows.
+// lbo: 1 for K-major tiles (the field is not used there); for MN-major tiles the distance between 64-element
+// atoms along MN in 16-byte units (one atom here, so it is not used either).
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr, uint32_t lbo) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)lbo << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// D = F32, A = B = BF16; b_mn = 1 when B is MN-major (bit 16); N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(const TcAttnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
+    // barriers: kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 3];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, kv_head = blockIdx.y;
+    const int first_row = p.row_start[seq];
+    const int q_len = p.row_start[seq + 1] - first_row;
+    const int n_rows = q_len * p.group;
+    const int n_tiles = (n_rows + BM - 1) / BM;
+    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) return;     // short sequences belong to the decode kernel
+    if (smem_u32(smem) & 1023u) {                               // never expected: refuse rather than compute garbage
+        if (threadIdx.x == 0) atomicExch(p.error, 99);
+        return;
+    }
+    const int r0 = (n_tiles - 1 - blockIdx.x) * BM;             // heavy tiles first
+    const int begin = p.seq_begin[seq];
+    const int* table = p.block_table + (int64_t)seq * p.bt_stride;
+
+    const uint32_t q_tile = smem_u32(smem);
+    const uint32_t p_tile = q_tile + kTileBytes;                // two 16 KiB halves (keys 0..63 | 64..127)
+    const uint32_t kv_tiles = p_tile + 2 * kTileBytes;          // [stage][K | V]
+    const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[STAGES]);
+    const uint32_t s_full = smem_u32(&bars[2 * STAGES]), p_ready = s_full + 8, o_full = s_full + 16;
+
+    const int last_row = min(n_rows, r0 + BM) - 1;
+    const int key_hi = begin + last_row / p.group;
+    const int key_lo = p.window > 0 ? max(0, begin + r0 / p.group - p.window + 1) : 0;
+    const int kb_first = key_lo / BN, kb_last = key_hi / BN;
+    const int n_blocks = kb_last - kb_first + 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(kv_full + 8 * s, kLoaderThreads);
+            mbar_init(kv_empty + 8 * s, 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, BM);
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // the Q tile: every thread copies its share of the 128 rows x 8 chunks, swizzled like the K/V tiles
+    for (int idx = threadIdx.x; idx < BM * 8; idx += kThreads) {
+        const int r = idx >> 3, c = idx & 7;
+        const int fr = r0 + r;
+        const bool ok = fr < n_rows;
+        const __nv_bfloat16* src = p.q;
+        if (ok) {
+            const int qpos = fr / p.group, g = fr - qpos * p.group;
+            src = p.q + (int64_t)(first_row + qpos) * p.q_stride + (int64_t)(kv_head * p.group + g) * D + c * 8;
+        }
+        cp_async16(q_tile + sw128(r, c), src, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BN;
+
+    if (warp >= 5) {
+        // ------------------------------------------------------------ loaders: K and V blocks through the block table
+        const int tid = threadIdx.x - 160;
+        const int64_t head_block = (int64_t)p.page_size * D;
+        const int64_t page_block = 2 * (int64_t)p.num_kv_heads * head_block;
+        const __nv_bfloat16* k_base = p.cache + (int64_t)kv_head * head_block;
+        const __nv_bfloat16* v_base = k_base + (int64_t)p.num_kv_heads * head_block;
+        bool ok = true;
+        // A loader runs one block ahead of its own completion: start block it, then publish block it - 1.
+        for (int it = 0; it < n_blocks; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(kv_empty + 8 * s, ((it / STAGES) & 1) ^ 1, &abort_flag)) { ok = false; break; }
+            const uint32_t dst = kv_tiles + s * 2 * kTileBytes;
+            const int key0 = (kb_first + it) * BN;
+            for (int idx = tid; idx < BN * 8; idx += kLoaderThreads) {
+                const int r = idx >> 3, c = idx & 7;
+                const int key = key0 + r;
+                const bool valid = key >= key_lo && key <= key_hi;
+                int64_t off = 0;
+                if (valid) {
+                    const int page = table[key >> p.page_shift];
+                    off = (int64_t)page * page_block + (int64_t)(key & (p.page_size - 1)) * D + c * 8;
+                }
+                cp_async16(dst + sw128(r, c), k_base + off, valid);
+                cp_async16(dst + kTileBytes + sw128(r, c), v_base + off, valid);
+            }
+            cp_async_commit();
+            if (it > 0) {
+                cp_async_wait<1>();
+                fence_async_smem();
+                mbar_arrive(kv_full + 8 * ((it - 1) % STAGES));
+            }
+        }
+        if (ok) {
+            cp_async_wait<0>();
+            fence_async_smem();
+            mbar_arrive(kv_full + 8 * ((n_blocks - 1) % STAGES));
+        } else {
+            cp_async_wait<0>();
+            abort_flag = 1;
+            atomicExch(p.error, 10);
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------ the issuer: one lane feeds the tensor core
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, D, 1);
+            auto issue_qk = [&](int j) {
+                const int s = j % STAGES;
+                if (!mbar_wait(kv_full + 8 * s, (j / STAGES) & 1, &abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t k_tile = kv_tiles + s * 2 * kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma(tmem_s, desc_sw128(q_tile + kk * 32, 1), desc_sw128(k_tile + kk * 32, 1), idesc_qk, kk != 0);
+                umma_commit(s_full);
+                return true;
+            };
+            bool ok = issue_qk(0);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                // the softmax warps have read S_j and written P_j
+                if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kTileBytes + kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
+                         desc_sw128(v_tile + kk * 2048, 1024 >> 4), idesc_pv, kk != 0);
+                umma_commit(o_full);
+                umma_commit(kv_empty + 8 * (j % STAGES));
+                if (j + 1 < n_blocks) ok = issue_qk(j + 1);   // S is free again: the next block's scores
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicExch(p.error, 20);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax, correction, epilogue: one thread per row
+        const int r = warp * 32 + lane;                 // row of the tile = tensor-memory lane
+        const int fr = r0 + r;
+        const int pos = fr < n_rows ? begin + fr / p.group : -1;
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // rows of this warp span positions [warp_lo_pos, ...]: blocks at or below warp_lo_pos need no mask
+        const int warp_first = r0 + warp * 32;
+        const bool all_rows = warp_first + 32 <= n_rows;
+        const int warp_lo_pos = begin + warp_first / p.group;
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        float m = kMasked, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int key0 = (kb_first + j) * BN;
+            if (!mbar_wait(s_full, j & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const bool full = all_rows && p.window <= 0 && key0 + BN - 1 <= warp_lo_pos;   // uniform across the warp
+            // pass 1: the row's maximum over the block
+            float block_max = kMasked;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_load_32(tmem_s + lane_base + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c * 32 + i;
+                    const bool valid = full || (key >= lo && key <= pos);
+                    block_max = fmaxf(block_max, valid ? v[i] * p.scale_log2 : kMasked);
+                }
+            }
+            const float m_new = fmaxf(m, block_max);
+            const float corr = fast_exp2(m - m_new);
+            m = m_new;
+            l *= corr;
+            // pass 2: probabilities, their 32-bit sum, and the bfloat16 P tile
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_load_32(tmem_s + lane_base + c * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pr[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = key0 + c * 32 + i + e;
+                        const bool valid = full || (key >= lo && key <= pos);
+                        pr[e] = valid ? fast_exp2(v[i + e] * p.scale_log2 - m) : 0.0f;
+                        l += pr[e];
+                    }
+                    packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+                }
+                // 32 keys = 4 chunks of 16 bytes in this row of the P tile (half c / 2, chunks (c % 2) * 4 ..)
+                unsigned char* dst = smem + kTileBytes + (c >> 1) * kTileBytes;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    *reinterpret_cast<uint4*>(dst + sw128(r, (c & 1) * 4 + q4)) =
+                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(p_ready);
+            // O = O * corr + P_j V_j
+            if (!mbar_wait(o_full, j & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                float v[32];
+                tmem_load_32(tmem_o + lane_base + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + v[i];
+            }
+            tc_fence_before();
+        }
+        if (ok && pos >= 0) {
+            const int qpos = fr / p.group, g = fr - qpos * p.group;
+            const float inv = 1.0f / fmaxf(l, 1.0e-8f);
+            __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
+#pragma unroll
+            for (int i = 0; i < D; i += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = o[i + e] * inv;
+                Packet<__nv_bfloat16>::store(dst + i, v);
+            }
+        }
+        if (!ok) {
+            abort_flag = 1;
+            atomicExch(p.error, 30);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+    }
+}
+
+}  // namespace
+
+// 1 if this kernel takes the sizes (else the caller uses the mma.sync kernel).
+TB_EXPORT int tb_attention_tcgen05_supported(int num_heads, int num_kv_heads, int head_dim, int page_size) {
+    if (head_dim != D) return 0;
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return 0;
+    if (page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
+    return 1;
+}
+
+// Attention of the sequences with more than 16 folded rows of a packed batch (the others are left to the split
+// decode kernel).  Arguments as tb_attention_mma; error: device int, set non-zero if a bounded wait ran out.
+TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
+                                   const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
+                                   int num_seqs, int max_rows_per_seq, int num_heads, int num_kv_heads, int head_dim,
+                                   int page_size, int window, float scale, int* error, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    if (!tb_attention_tcgen05_supported(num_heads, num_kv_heads, head_dim, page_size)) return TB_ERR_BAD_SIZE;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
+        return TB_ERR_BAD_ALIGN;
+    if (num_seqs > 65535 || num_kv_heads > 65535) return TB_ERR_BAD_SIZE;
+    TcAttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.out = (__nv_bfloat16*)out;
+    p.cache = (const __nv_bfloat16*)cache;
+    p.row_start = row_start;
+    p.seq_begin = seq_begin;
+    p.block_table = block_table;
+    p.error = error;
+    p.q_stride = q_stride;
+    p.out_stride = out_stride;
+    p.bt_stride = bt_stride;
+    p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads;
+    p.group = num_heads / num_kv_heads;
+    p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window;
+    p.scale_log2 = scale * kLog2e;
+    const size_t smem = (size_t)(1 + 2 + 2 * STAGES) * kTileBytes;
+    cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    const int max_folded = max_rows_per_seq * p.group;
+    dim3 grid((max_folded + BM - 1) / BM, num_kv_heads, num_seqs);
+    attention_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(p);
+    return tb_launch_status();
+}

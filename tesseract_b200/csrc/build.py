@@ -41,6 +41,7 @@ SOURCES: Dict[str, List[str]] = {
     "attention_rows": [],
     "attention_mma": [],
     "attention_noalloc": [],
+    "attention_tcgen05": [],
     "gemm_f32": [],
     "decode_linear": [],
     "gemm_tcgen05": [],

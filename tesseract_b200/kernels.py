@@ -393,3 +393,31 @@ def tcgen05_error(device=None) -> int:
             total |= int(word.item())
             word.zero_()
     return total
+
+
+def attention_tcgen05_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return bool(load_library("attention_tcgen05").tb_attention_tcgen05_supported(
+        _i32(num_heads), _i32(num_kv_heads), _i32(head_dim), _i32(page_size)))
+
+
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,
+                      seq_begin: torch.Tensor, block_table: torch.Tensor, num_seqs: int, max_new: int, num_heads: int,
+                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+    """Prompt-portion attention on the tcgen05 tensor cores: the sequences of the batch with more than 16 folded
+    rows (``new tokens * num_heads / num_kv_heads``); rows of shorter sequences are left untouched."""
+    _cuda(q, out, cache, row_start, seq_begin, block_table)
+    _need(q.dtype == out.dtype == cache.dtype == torch.bfloat16, "attention_tcgen05 takes bfloat16")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim and out.shape == q.shape,
+          "q/out layout")
+    _need(row_start.dtype == torch.int32 and seq_begin.dtype == torch.int32 and block_table.dtype == torch.int32,
+          "row_start, seq_begin and block_table must be int32")
+    _need(row_start.numel() >= num_seqs + 1 and seq_begin.numel() >= num_seqs, "sequence metadata too short")
+    _need(block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[0] >= num_seqs, "block table")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache layout")
+    lib = load_library("attention_tcgen05")
+    _check(lib.tb_attention_tcgen05(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                    _ptr(row_start), _ptr(seq_begin), _ptr(block_table), _i32(block_table.stride(0)),
+                                    _i32(num_seqs), _i32(max_new), _i32(num_heads), _i32(num_kv_heads),
+                                    _i32(head_dim), _i32(page_size), _i32(window), _f32(scale),
+                                    _ptr(_error_word(q.device)), _stream()), "attention_tcgen05")
+    return out

@@ -51,6 +51,7 @@ class Attention(Mixer):
         fused = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)
         self.qkv_proj = Linear(fused, runtime)
         self.o_proj = Linear(tensors["o"], runtime)
+        self._tcgen05 = None      # decided at the first prompt portion (needs the cache's page size)
         position_spec = spec.children.get("position")
         if position_spec is None:
             position_spec = PartSpec.make("none")
@@ -107,6 +108,16 @@ class Attention(Mixer):
         long_seqs = any(n * fold > 16 for n in ctx.host_new)
         short_seqs = any(n * fold <= 16 for n in ctx.host_new)
         splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context) if short_seqs else 1
-        kernels.attention_mma(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table, ctx.num_seqs,
-                              ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
-                              self.window, self.scale, long_seqs, short_seqs, splits)
+        if long_seqs and self._tcgen05 is None:
+            self._tcgen05 = kernels.attention_tcgen05_supported(self.num_heads, self.num_kv_heads, self.head_dim,
+                                                                cache.page_size)
+        if long_seqs and self._tcgen05:
+            # prompt portions on the fifth-generation tensor cores; decode rows (if any) by the split kernel
+            kernels.attention_tcgen05(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
+                                      ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
+                                      cache.page_size, self.window, self.scale)
+            long_seqs = False
+        if long_seqs or short_seqs:
+            kernels.attention_mma(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
+                                  ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
+                                  cache.page_size, self.window, self.scale, long_seqs, short_seqs, splits)

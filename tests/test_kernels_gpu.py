@@ -502,3 +502,37 @@ def test_gemm_tcgen05(m, n, k):
         assert kernels.tcgen05_error() == 0
         g, u = a.double() @ gate.double().T, a.double() @ up.double().T
         torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("lengths, new, nh, nkv, page_size, window", [
+    ([40], [40], 4, 4, 16, 0),                                  # a single block, rows beyond the sequence masked
+    ([100, 70], [30, 1], 8, 8, 16, 0),                          # no grouping; the decode row is left to the other kernel
+    ([513], [513], 32, 8, 16, 0),                               # many tiles and blocks of one long prompt
+    ([700, 300, 129], [129, 300, 5], 8, 2, 16, 0),              # portions at offsets, blocks crossing page edges
+    ([1000], [200], 4, 1, 64, 0),                               # one kv head, larger pages
+    ([600, 90], [260, 90], 4, 2, 16, 100),                      # sliding window
+    ([300], [17], 16, 1, 16, 0),                                # a group of 16: two tokens fill a tile row block
+])
+def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window):
+    from tesseract_b200 import kernels
+
+    d = 64
+    case = paged_case(torch.bfloat16, lengths, new, nh, nkv, d, page_size, seed=sum(lengths))
+    scale = 1.0 / math.sqrt(d)
+    rows = case["q"].shape[0]
+    row_start = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32)
+    seq_begin = torch.tensor([n - q for n, q in zip(lengths, new)], dtype=torch.int32)
+    out = torch.full((rows, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.attention_tcgen05(dev(case["q"]).view(rows, nh * d), out, dev(case["cache"]), dev(row_start), dev(seq_begin),
+                              dev(case["table"]), len(lengths), max(new), nh, nkv, d, page_size, window, scale)
+    assert kernels.tcgen05_error() == 0, "a bounded wait inside the kernel ran out"
+    want = plain_paged_attention(case, scale, window or None).reshape(rows, nh * d)
+    fold = nh // nkv
+    at = 0
+    for n in new:
+        got = out[at:at + n].cpu()
+        if n * fold > 16:
+            torch.testing.assert_close(got.double(), want[at:at + n], rtol=2e-2, atol=2e-2)
+        else:
+            assert torch.isnan(got.float()).all()           # short sequences are not this kernel's
+        at += n
