@@ -10,12 +10,19 @@
 //   O_blk = P . V      tcgen05.mma, M128 x N64 x K128, P K-major, V MN-major (the cache's [key][dim] rows as they
 //                      are), into 64 further columns of tensor memory
 //   O = O * corr + O_blk  in registers of the row's thread (tcgen05.ld of 64 columns)
-// Warps 0-3 are the softmax / correction / epilogue warps (warp w owns tensor-memory lanes 32w..32w+31), warps 5-7
-// bring K and V blocks into a ring of shared-memory stages with cp.async through the block table, and one lane
-// of warp 4 issues the tensor-core instructions.  Roles meet on mbarriers; every wait is bounded, and a wait that
+// Warps 0-3 are the softmax / correction / epilogue warps (warp w owns tensor-memory lanes 32w..32w+31); one lane
+// of warp 5 brings K and V blocks into a ring of shared-memory stages, page by page through the block table, with
+// cp.async.bulk.tensor over a five-dimensional tensor map of the cache (no multicast); one lane of warp 4 issues
+// the tensor-core instructions.  Roles meet on mbarriers; every wait is bounded, and a wait that
 // runs out sets *error, stops the other roles, and the CTA still frees its tensor memory.
 // Two CTAs fit on an SM (about 100 KiB of shared memory and 256 tensor-memory columns each), so one CTA's softmax
 // overlaps the other's products.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "common.cuh"
 
 namespace {
@@ -24,8 +31,7 @@ constexpr int D = 64;            // head_dim this kernel is built for
 constexpr int BM = 128;          // folded query rows per CTA
 constexpr int BN = 128;          // keys per block
 constexpr int STAGES = 2;        // K/V ring depth
-constexpr int kThreads = 256;
-constexpr int kLoaderThreads = 96;    // warps 5..7
+constexpr int kThreads = 192;         // warps 0..3 softmax, warp 4 issuer, warp 5 TMA producer
 constexpr uint32_t kTileBytes = BN * D * 2;           // 16 KiB: one K or V block, also the Q tile and half a P tile
 constexpr uint32_t kTmemColumns = 256;                // S: columns 0..127, O_blk: columns 128..191
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -68,6 +74,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if ((spin & 255) == 255 && *abort_flag) return false;
     }
     return false;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of the cache tensor [page][K|V][kv_head][page_size][64]: `rows` consecutive keys of one page, one head.
+__device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map, uint32_t bar, int key_in_page,
+                                            int kv_head, int which, int page) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
@@ -131,7 +147,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(const TcAttnParams p) {
+__global__ void __launch_bounds__(kThreads, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
     // barriers: kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 3];
@@ -168,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(const Tc
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(kv_full + 8 * s, kLoaderThreads);
+            mbar_init(kv_full + 8 * s, 1);
             mbar_init(kv_empty + 8 * s, 1);
         }
         mbar_init(s_full, 1);
@@ -202,47 +219,34 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(const Tc
     const uint32_t tmem_base = tmem_base_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BN;
 
-    if (warp >= 5) {
-        // ------------------------------------------------------------ loaders: K and V blocks through the block table
-        const int tid = threadIdx.x - 160;
-        const int64_t head_block = (int64_t)p.page_size * D;
-        const int64_t page_block = 2 * (int64_t)p.num_kv_heads * head_block;
-        const __nv_bfloat16* k_base = p.cache + (int64_t)kv_head * head_block;
-        const __nv_bfloat16* v_base = k_base + (int64_t)p.num_kv_heads * head_block;
-        bool ok = true;
-        // A loader runs one block ahead of its own completion: start block it, then publish block it - 1.
-        for (int it = 0; it < n_blocks; ++it) {
-            const int s = it % STAGES;
-            if (!mbar_wait(kv_empty + 8 * s, ((it / STAGES) & 1) ^ 1, &abort_flag)) { ok = false; break; }
-            const uint32_t dst = kv_tiles + s * 2 * kTileBytes;
-            const int key0 = (kb_first + it) * BN;
-            for (int idx = tid; idx < BN * 8; idx += kLoaderThreads) {
-                const int r = idx >> 3, c = idx & 7;
-                const int key = key0 + r;
-                const bool valid = key >= key_lo && key <= key_hi;
-                int64_t off = 0;
-                if (valid) {
-                    const int page = table[key >> p.page_shift];
-                    off = (int64_t)page * page_block + (int64_t)(key & (p.page_size - 1)) * D + c * 8;
+    if (warp == 5) {
+        // ------------------------------------------------------------ TMA producer: K and V blocks, page by page
+        if (lane == 0) {
+            const int rows_per_copy = min(p.page_size, BN);          // keys one bulk copy brings
+            const int copies = BN / rows_per_copy;
+            const int last_page = key_hi >> p.page_shift;            // pages past it hold nothing of this sequence
+            bool ok = true;
+            for (int it = 0; it < n_blocks; ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(kv_empty + 8 * s, ((it / STAGES) & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                const uint32_t dst = kv_tiles + s * 2 * kTileBytes;
+                const int key0 = (kb_first + it) * BN;
+                mbar_expect_tx(kv_full + 8 * s, 2 * kTileBytes);
+                for (int c = 0; c < copies; ++c) {
+                    const int key = key0 + c * rows_per_copy;
+                    const int logical = key >> p.page_shift;
+                    // keys past the sequence come from the scratch page: finite values that the mask removes
+                    const int page = logical <= last_page ? table[logical] : 0;
+                    const int in_page = key & (p.page_size - 1);
+                    const uint32_t at = dst + (uint32_t)(c * rows_per_copy) * 128;
+                    tma_load_kv(at, &cache_map, kv_full + 8 * s, in_page, kv_head, 0, page);
+                    tma_load_kv(at + kTileBytes, &cache_map, kv_full + 8 * s, in_page, kv_head, 1, page);
                 }
-                cp_async16(dst + sw128(r, c), k_base + off, valid);
-                cp_async16(dst + kTileBytes + sw128(r, c), v_base + off, valid);
             }
-            cp_async_commit();
-            if (it > 0) {
-                cp_async_wait<1>();
-                fence_async_smem();
-                mbar_arrive(kv_full + 8 * ((it - 1) % STAGES));
+            if (!ok) {
+                abort_flag = 1;
+                atomicExch(p.error, 10);
             }
-        }
-        if (ok) {
-            cp_async_wait<0>();
-            fence_async_smem();
-            mbar_arrive(kv_full + 8 * ((n_blocks - 1) % STAGES));
-        } else {
-            cp_async_wait<0>();
-            abort_flag = 1;
-            atomicExch(p.error, 10);
         }
     } else if (warp == 4) {
         // ------------------------------------------------------------ the issuer: one lane feeds the tensor core
@@ -382,6 +386,48 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(const Tc
     }
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Tensor map of one cache entry [pages][2][kv_heads][page_size][64] (bfloat16), boxes of min(page_size, 128) keys
+// of one head with the 128-byte swizzle.  Maps are kept per (pointer, geometry): a cache entry lives as long as
+// its model.
+const CUtensorMap* cache_map_for(const void* cache, int pages, int num_kv_heads, int page_size) {
+    static std::mutex lock;
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> maps;
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_tuple(cache, pages, num_kv_heads, page_size);
+    auto found = maps.find(key);
+    if (found != maps.end()) return &found->second;
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return nullptr;
+    CUtensorMap map;
+    const cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)page_size, (cuuint64_t)num_kv_heads, 2, (cuuint64_t)pages};
+    const cuuint64_t row = (cuuint64_t)D * 2;
+    const cuuint64_t strides[4] = {row, row * page_size, row * page_size * num_kv_heads,
+                                   row * page_size * num_kv_heads * 2};
+    const cuuint32_t box[5] = {(cuuint32_t)D, (cuuint32_t)(page_size < BN ? page_size : BN), 1, 1, 1};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    return &maps.emplace(key, map).first->second;
+}
+
 }  // namespace
 
 // 1 if this kernel takes the sizes (else the caller uses the mma.sync kernel).
@@ -397,12 +443,15 @@ TB_EXPORT int tb_attention_tcgen05_supported(int num_heads, int num_kv_heads, in
 TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                    const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
                                    int num_seqs, int max_rows_per_seq, int num_heads, int num_kv_heads, int head_dim,
-                                   int page_size, int window, float scale, int* error, cudaStream_t stream) {
+                                   int page_size, int cache_pages, int window, float scale, int* error,
+                                   cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     if (!tb_attention_tcgen05_supported(num_heads, num_kv_heads, head_dim, page_size)) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
         return TB_ERR_BAD_ALIGN;
     if (num_seqs > 65535 || num_kv_heads > 65535) return TB_ERR_BAD_SIZE;
+    const CUtensorMap* map = cache_map_for(cache, cache_pages, num_kv_heads, page_size);
+    if (map == nullptr) return TB_ERR_BAD_SIZE;
     TcAttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.out = (__nv_bfloat16*)out;
@@ -428,6 +477,6 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     if (err != cudaSuccess) return (int)err;
     const int max_folded = max_rows_per_seq * p.group;
     dim3 grid((max_folded + BM - 1) / BM, num_kv_heads, num_seqs);
-    attention_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(p);
+    attention_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(*map, p);
     return tb_launch_status();
 }

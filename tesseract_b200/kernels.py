@@ -418,6 +418,6 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, r
     _check(lib.tb_attention_tcgen05(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                     _ptr(row_start), _ptr(seq_begin), _ptr(block_table), _i32(block_table.stride(0)),
                                     _i32(num_seqs), _i32(max_new), _i32(num_heads), _i32(num_kv_heads),
-                                    _i32(head_dim), _i32(page_size), _i32(window), _f32(scale),
+                                    _i32(head_dim), _i32(page_size), _i32(cache.shape[0]), _i32(window), _f32(scale),
                                     _ptr(_error_word(q.device)), _stream()), "attention_tcgen05")
     return out

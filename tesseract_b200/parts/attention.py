@@ -27,7 +27,7 @@ from .linear import Linear
 
 @MIXERS.register("attention")
 class Attention(Mixer):
-    """params: ``hidden_size, num_heads, num_kv_heads, head_dim``, optional ``window``, ``scale``.
+    """params: ``hidden_size, num_heads, num_kv_heads, head_dim``, optional ``window``, ``scale``, ``prompt_kernel``.
     weights: ``q, k, v, o``.  children: ``position`` (a position encoding spec)."""
 
     accepts_deferred_norm = True
@@ -51,6 +51,11 @@ class Attention(Mixer):
         fused = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)
         self.qkv_proj = Linear(fused, runtime)
         self.o_proj = Linear(tensors["o"], runtime)
+        # Which kernel runs prompt portions in bfloat16: "mma" (mma.sync tiles, the faster one today) or "tcgen05"
+        # (tensor-memory accumulators; head_dim 64 only, falls back to "mma" for other sizes).
+        self.prompt_kernel = str(p.get("prompt_kernel") or "mma")
+        if self.prompt_kernel not in ("mma", "tcgen05"):
+            raise ValueError(f"prompt_kernel must be 'mma' or 'tcgen05', got '{self.prompt_kernel}'")
         self._tcgen05 = None      # decided at the first prompt portion (needs the cache's page size)
         position_spec = spec.children.get("position")
         if position_spec is None:
@@ -108,7 +113,7 @@ class Attention(Mixer):
         long_seqs = any(n * fold > 16 for n in ctx.host_new)
         short_seqs = any(n * fold <= 16 for n in ctx.host_new)
         splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context) if short_seqs else 1
-        if long_seqs and self._tcgen05 is None:
+        if long_seqs and self.prompt_kernel == "tcgen05" and self._tcgen05 is None:
             self._tcgen05 = kernels.attention_tcgen05_supported(self.num_heads, self.num_kv_heads, self.head_dim,
                                                                 cache.page_size)
         if long_seqs and self._tcgen05:

@@ -270,3 +270,50 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     assert stepper.cache.admit("q2")
     again = stepper.step([StepEntry("q2", seqs["q"], [19])]).cpu().double()
     torch.testing.assert_close(again[0], plain["q"][19], rtol=2e-5, atol=2e-5)
+
+
+def test_attention_part_with_the_tcgen05_prompt_kernel():
+    """The same mixer with prompt portions on the tcgen05 kernel: portions, decode rows beside them, page reuse."""
+    from tesseract_b200 import kernels
+    from tesseract_b200.cache import CacheManager
+    from tesseract_b200.config import PartSpec
+    from tesseract_b200.parts import MIXERS
+
+    torch.manual_seed(3)
+    rt = runtime(torch.bfloat16)
+    hidden, nh, nkv, d = 128, 8, 2, 64
+    position = PartSpec.make("rotary", {"head_dim": d, "theta": 10000.0, "scaling": None})
+    weights = {"q": torch.randn(nh * d, hidden) * 0.1, "k": torch.randn(nkv * d, hidden) * 0.1,
+               "v": torch.randn(nkv * d, hidden) * 0.1, "o": torch.randn(hidden, nh * d) * 0.1}
+    weights = {k: v.to(torch.bfloat16) for k, v in weights.items()}
+    outs = {}
+    for kernel in ("mma", "tcgen05"):
+        spec = PartSpec.make("attention", {"hidden_size": hidden, "num_heads": nh, "num_kv_heads": nkv, "head_dim": d,
+                                           "window": None, "scale": None, "prompt_kernel": kernel},
+                             {"q": "q", "k": "k", "v": "v", "o": "o"}, {"position": position})
+        mixer = MIXERS.get("attention")(spec, weights, rt)
+        cache = CacheManager([mixer.cache_need()], [None], num_pages=40, page_size=16, max_requests=2,
+                             dtype=torch.bfloat16, device=rt.device, max_step_tokens=256)
+        gen = torch.Generator().manual_seed(5)
+        xs = {"a": torch.randn(300, hidden, generator=gen).to(torch.bfloat16),
+              "b": torch.randn(140, hidden, generator=gen).to(torch.bfloat16)}
+        cuts = {"a": [130, 169, 1], "b": [1, 138, 1]}
+        got = {"a": [], "b": []}
+        for r in xs:
+            assert cache.admit(r)
+        for step in range(3):
+            news = [cuts[r][step] for r in ("a", "b")]
+            for r, n in zip(("a", "b"), news):
+                cache.extend(r, n)
+            ctx = context_for(cache, ["a", "b"], news)
+            x = torch.cat([xs[r][cache.length(r):cache.length(r) + n] for r, n in zip(("a", "b"), news)]).cuda()
+            y = mixer.forward(x, ctx, cache.bindings[0]).cpu()
+            at = 0
+            for r, n in zip(("a", "b"), news):
+                got[r].append(y[at:at + n])
+                at += n
+                cache.commit(r, n)
+        outs[kernel] = {r: torch.cat(v).float() for r, v in got.items()}
+        assert kernels.tcgen05_error() == 0
+    for r in ("a", "b"):
+        torch.testing.assert_close(outs["tcgen05"][r], outs["mma"][r], rtol=3e-2, atol=3e-2)
