@@ -7,9 +7,9 @@
 //                      accumulator in tensor memory (128 columns)
 //   softmax            four warps, one thread per row: tcgen05.ld of the row, scale, mask, running maximum,
 //                      2^x, 32-bit row sum, probabilities rounded to bfloat16 into a swizzled P tile in shared memory
-//   O_blk = P . V      tcgen05.mma, M128 x N64 x K128, P K-major, V MN-major (the cache's [key][dim] rows as they
-//                      are), into 64 further columns of tensor memory
-//   O = O * corr + O_blk  in registers of the row's thread (tcgen05.ld of 64 columns)
+//   O += P . V         tcgen05.mma, M128 x N64 x K128, P K-major, V MN-major (the cache's [key][dim] rows as they
+//                      are), accumulating in 64 further columns of tensor memory; when a row's maximum jumps by
+//                      more than 2^8 its thread rescales that row of O in place (tcgen05.ld / tcgen05.st)
 // Warps 0-3 are the softmax / correction / epilogue warps (warp w owns tensor-memory lanes 32w..32w+31); one lane
 // of warp 5 brings K and V blocks into a ring of shared-memory stages, page by page through the block table, with
 // cp.async.bulk.tensor over a five-dimensional tensor map of the cache (no multicast); one lane of warp 4 issues
@@ -137,6 +137,30 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31,%32};"
+        ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]),
+          "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]),
+          "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]),
+          "f"(v[27]), "f"(v[28]), "f"(v[29]), "f"(v[30]), "f"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -150,8 +174,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __global__ void __launch_bounds__(kThreads, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
-    // barriers: kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 3];
+    // barriers: kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full, s_free
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -175,6 +199,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const uint32_t kv_tiles = p_tile + 2 * kTileBytes;          // [stage][K | V]
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[STAGES]);
     const uint32_t s_full = smem_u32(&bars[2 * STAGES]), p_ready = s_full + 8, o_full = s_full + 16;
+    const uint32_t s_free = s_full + 24;
 
     const int last_row = min(n_rows, r0 + BM) - 1;
     const int key_hi = begin + last_row / p.group;
@@ -191,6 +216,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         mbar_init(s_full, 1);
         mbar_init(p_ready, BM);
         mbar_init(o_full, 1);
+        mbar_init(s_free, BM);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 4) {
@@ -266,17 +292,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             };
             bool ok = issue_qk(0);
             for (int j = 0; j < n_blocks && ok; ++j) {
-                // the softmax warps have read S_j and written P_j
+                // as soon as the softmax warps hold S_j in registers the next block's scores may overwrite it
+                if (j + 1 < n_blocks) {
+                    if (!mbar_wait(s_free, j & 1, &abort_flag)) { ok = false; break; }
+                    ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                // P_j is in shared memory (and O has been rescaled if the maximum jumped): O += P_j V_j
                 if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kTileBytes + kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
                     umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
-                         desc_sw128(v_tile + kk * 2048, 1024 >> 4), idesc_pv, kk != 0);
+                         desc_sw128(v_tile + kk * 2048, 1024 >> 4), idesc_pv, (j | kk) != 0);
                 umma_commit(o_full);
                 umma_commit(kv_empty + 8 * (j % STAGES));
-                if (j + 1 < n_blocks) ok = issue_qk(j + 1);   // S is free again: the next block's scores
             }
             if (!ok) {
                 abort_flag = 1;
@@ -294,9 +325,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         const int warp_first = r0 + warp * 32;
         const bool all_rows = warp_first + 32 <= n_rows;
         const int warp_lo_pos = begin + warp_first / p.group;
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        // The running output lives in tensor memory (P.V accumulates there).  m is the maximum that the stored
+        // probabilities and O are scaled by; it is only raised (and O rescaled) when a block's maximum exceeds it
+        // by more than 2^8, which keeps every probability at or below 256 and makes the rescaling rare.
         float m = kMasked, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
@@ -304,74 +335,131 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             if (!mbar_wait(s_full, j & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
             const bool full = all_rows && p.window <= 0 && key0 + BN - 1 <= warp_lo_pos;   // uniform across the warp
-            // pass 1: the row's maximum over the block
-            float block_max = kMasked;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                tmem_load_32(tmem_s + lane_base + c * 32, v);
+            // Pass 1: the row's maximum over the block, 32 columns at a time (the next chunk is in flight while one
+            // is reduced; four partial maxima keep the dependency chains short).
+            uint32_t ca[32], cb[32];
+            float mx[4] = {kMasked, kMasked, kMasked, kMasked};
+            const int lo_col = lo - key0, hi_col = pos - key0;     // this row sees columns lo_col..hi_col of the block
+            // (the scale is positive, so the maximum of the raw scores is scaled once at the end; blocks that need
+            // no mask take the short path: one instruction per element)
+            auto reduce_max = [&](const uint32_t (&chunk)[32], int c) {
+                if (full) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c * 32 + i;
-                    const bool valid = full || (key >= lo && key <= pos);
-                    block_max = fmaxf(block_max, valid ? v[i] * p.scale_log2 : kMasked);
+                    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(chunk[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const bool valid = c * 32 + i >= lo_col && c * 32 + i <= hi_col;
+                        mx[i & 3] = fmaxf(mx[i & 3], valid ? __uint_as_float(chunk[i]) : kMasked);
+                    }
+                }
+            };
+            tmem_load_32_nowait(tmem_s + lane_base, ca);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 32, cb);
+            reduce_max(ca, 0);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
+            reduce_max(cb, 1);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
+            reduce_max(ca, 2);
+            tmem_wait_ld();
+            reduce_max(cb, 3);
+            const float raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float block_max = raw_max > 0.5f * kMasked ? raw_max * p.scale_log2 : kMasked;
+            // P_{j-1} V_{j-1} must be complete before the P tile is overwritten (and before O is rescaled)
+            if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, &abort_flag)) { ok = false; break; }
+            const bool jump = block_max > m + 8.0f;
+            if (__any_sync(0xffffffffu, jump)) {
+                const float m_new = fmaxf(m, block_max);
+                const float corr = fast_exp2(m - m_new);
+                m = m_new;
+                l *= corr;
+                if (j > 0) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        float v[32];
+                        tmem_load_32(tmem_o + lane_base + c * 32, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] *= corr;
+                        tmem_store_32(tmem_o + lane_base + c * 32, v);
+                    }
                 }
             }
-            const float m_new = fmaxf(m, block_max);
-            const float corr = fast_exp2(m - m_new);
-            m = m_new;
-            l *= corr;
-            // pass 2: probabilities, their 32-bit sum, and the bfloat16 P tile
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                tmem_load_32(tmem_s + lane_base + c * 32, v);
+            // Pass 2: probabilities, their 32-bit sum (four partial sums), and the bfloat16 P tile.
+            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            auto emit = [&](const uint32_t (&chunk)[32], int c) {
                 uint32_t packed[16];
+                const float neg_m = -m;
+                if (full) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pr[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int key = key0 + c * 32 + i + e;
-                        const bool valid = full || (key >= lo && key <= pos);
-                        pr[e] = valid ? fast_exp2(v[i + e] * p.scale_log2 - m) : 0.0f;
-                        l += pr[e];
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(chunk[i]), p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(chunk[i + 1]), p.scale_log2, neg_m));
+                        ls[(i >> 1) & 3] += p0 + p1;
+                        packed[i >> 1] = pack_bf16(p0, p1);
                     }
-                    packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float pr[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const bool valid = c * 32 + i + e >= lo_col && c * 32 + i + e <= hi_col;
+                            pr[e] = valid ? fast_exp2(fmaf(__uint_as_float(chunk[i + e]), p.scale_log2, neg_m)) : 0.0f;
+                        }
+                        ls[(i >> 1) & 3] += pr[0] + pr[1];
+                        packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+                    }
                 }
-                // 32 keys = 4 chunks of 16 bytes in this row of the P tile (half c / 2, chunks (c % 2) * 4 ..)
                 unsigned char* dst = smem + kTileBytes + (c >> 1) * kTileBytes;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                     *reinterpret_cast<uint4*>(dst + sw128(r, (c & 1) * 4 + q4)) =
                         make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-            }
+            };
+            tmem_load_32_nowait(tmem_s + lane_base, ca);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 32, cb);
+            emit(ca, 0);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
+            emit(cb, 1);
+            tmem_wait_ld();
+            tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
+            emit(ca, 2);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(s_free);                       // S has been read: the issuer may start the next block's scores
+            emit(cb, 3);
+            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(p_ready);
-            // O = O * corr + P_j V_j
-            if (!mbar_wait(o_full, j & 1, &abort_flag)) { ok = false; break; }
+        }
+        if (ok && !mbar_wait(o_full, (n_blocks - 1) & 1, &abort_flag)) ok = false;
+        if (ok) {
             tc_fence_after();
+            const float inv = 1.0f / fmaxf(l, 1.0e-8f);
+            const int qpos = pos >= 0 ? fr / p.group : 0, g = pos >= 0 ? fr - qpos * p.group : 0;
+            __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 float v[32];
                 tmem_load_32(tmem_o + lane_base + c * 32, v);
+                if (pos >= 0) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + v[i];
+                    for (int i = 0; i < 32; i += 8) {
+                        float w8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) w8[e] = v[i + e] * inv;
+                        Packet<__nv_bfloat16>::store(dst + c * 32 + i, w8);
+                    }
+                }
             }
             tc_fence_before();
-        }
-        if (ok && pos >= 0) {
-            const int qpos = fr / p.group, g = fr - qpos * p.group;
-            const float inv = 1.0f / fmaxf(l, 1.0e-8f);
-            __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
-#pragma unroll
-            for (int i = 0; i < D; i += 8) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = o[i + e] * inv;
-                Packet<__nv_bfloat16>::store(dst + i, v);
-            }
         }
         if (!ok) {
             abort_flag = 1;

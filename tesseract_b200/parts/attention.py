@@ -51,9 +51,9 @@ class Attention(Mixer):
         fused = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)
         self.qkv_proj = Linear(fused, runtime)
         self.o_proj = Linear(tensors["o"], runtime)
-        # Which kernel runs prompt portions in bfloat16: "mma" (mma.sync tiles, the faster one today) or "tcgen05"
-        # (tensor-memory accumulators; head_dim 64 only, falls back to "mma" for other sizes).
-        self.prompt_kernel = str(p.get("prompt_kernel") or "mma")
+        # Which kernel runs prompt portions in bfloat16: "tcgen05" (tensor-memory accumulators, TMA-fed; head_dim 64
+        # only, other sizes fall back) or "mma" (mma.sync tiles, every head size).
+        self.prompt_kernel = str(p.get("prompt_kernel") or "tcgen05")
         if self.prompt_kernel not in ("mma", "tcgen05"):
             raise ValueError(f"prompt_kernel must be 'mma' or 'tcgen05', got '{self.prompt_kernel}'")
         self._tcgen05 = None      # decided at the first prompt portion (needs the cache's page size)
