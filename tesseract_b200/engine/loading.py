@@ -39,7 +39,10 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device_index: int = 0) -
     """Read ``config.json``, pick the architecture, check and load the checkpoint, build the parts."""
     import tesseract_b200.models  # noqa: F401  (registers architectures and parts)
 
+    from .. import kernels
+
     device = require_cuda(device_index)
+    kernels.prepare(parse_dtype(dtype))
     architecture, config, spec = load_model_description(model_dir)
     tensors = check_and_load(model_dir, expected_tensors(spec), architecture.ignorable_tensors(config))
     return DecoderModel(spec, tensors, Runtime(parse_dtype(dtype), device))

@@ -42,6 +42,21 @@ def _check(status: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {status} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
 
 
+_LIBRARIES = {
+    torch.float32: ("elementwise", "norm", "rope_cache", "attention_rows", "gemm_f32", "sampling"),
+    torch.bfloat16: ("elementwise", "norm", "rope_cache", "attention_mma", "attention_tcgen05", "decode_linear",
+                     "sampling"),
+}
+
+
+def prepare(dtype: torch.dtype) -> None:
+    """Build, side by side, the kernel libraries that a model of this dtype uses (they would otherwise be built
+    one after the other, each at its first call)."""
+    from .csrc.build import ensure_built
+
+    ensure_built(_LIBRARIES.get(dtype, ()))
+
+
 def _code(dtype: torch.dtype) -> int:
     try:
         return _DTYPE_CODE[dtype]
