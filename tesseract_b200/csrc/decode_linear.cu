@@ -11,7 +11,7 @@
 //
 // Why not the library: at these sizes a decode layer is a chain of launches of a few microseconds
 // each, and the norm and activation kernels between the products cost as much as the products.
-// A CTA owns tiles of 32 output features; its 16 warps split K, each streaming its slice of the 32 weight
+// A CTA owns tiles of 32 (or, for narrow outputs, 16) output features; its 16 warps split K, each streaming its slice of the 32 weight
 // rows through a private cp.async ring in shared memory into mma.sync.m16n8k16 A fragments (weights are
 // the 16-row operand, the batch rows the 8-column operand); the warps are summed in a fixed order.
 // Each lane loads 16 contiguous bytes per weight row and 32-wide K block; the products pair weight
@@ -24,7 +24,8 @@ namespace {
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxCtas = 296;  // two resident CTAs per SM
-constexpr int kStages = 3;     // ring depth per warp
+// Ring depth per warp (deeper rings were measured and bought nothing: two resident CTAs matter more).
+__host__ __device__ constexpr int ring_depth(int nh) { return 3; }
 
 enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2 };
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -65,7 +66,8 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 // MT: number of 8-row batch tiles (1 or 2).
-template <int MT, int PRO, int EPI>
+// NH: 16-feature halves per tile (2 where there are tiles enough for every SM, else 1).
+template <int MT, int PRO, int EPI, int NH>
 __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,37 +86,36 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     // memory, filled by cp.async: a lane copies exactly the 16-byte pieces that it later reads back itself, so the
     // ring needs no barrier, only cp.async.wait_group, and runs on across tile boundaries.
     constexpr int X_BYTES = (PRO == PRO_NONE) ? 512 * MT : 0;   // activations ride along when they come from memory
-    constexpr int STAGE_BYTES = 2048 + X_BYTES;
-    constexpr int STAGES = kStages;
+    constexpr int TF = 16 * NH;                                  // features per tile
+    constexpr int STAGE_BYTES = 1024 * NH + X_BYTES;
+    constexpr int STAGES = ring_depth(NH);
     const int blocks = K / 32;
     const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
-    const int num_tiles = p.N / 32;
+    const int num_tiles = p.N / TF;
     const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     unsigned char* ring = smem + (PRO != PRO_NONE ? (size_t)ROWS * x_pitch * 2 : 0) +
-                          (size_t)kWarps * 32 * ROWS * sizeof(float) + (size_t)warp * STAGES * STAGE_BYTES;
+                          (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)warp * STAGES * STAGE_BYTES;
     const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
     const uint32_t lane_off = (uint32_t)(g * 64 + t * 16);
-    const int64_t tile_stride = (int64_t)gridDim.x * 32 * K;     // elements between this CTA's consecutive tiles
+    const int64_t tile_stride = (int64_t)gridDim.x * TF * K;     // elements between this CTA's consecutive tiles
 
     // producer cursor: tile pi, block-of-warp pj, ring slot ps
     int pi = 0, pj = 0, ps = 0;
-    const __nv_bfloat16* p_src = p.w + ((int64_t)blockIdx.x * 32 + g) * K + 8 * t;   // row g of the current tile
+    const __nv_bfloat16* p_src = p.w + ((int64_t)blockIdx.x * TF + g) * K + 8 * t;   // row g of the current tile
     auto issue = [&](bool with_x) {
         if (pi < my_tiles) {
             const int b = warp + pj * kWarps;
             if (b < blocks) {
                 const uint32_t dst = ring_addr + (uint32_t)ps * STAGE_BYTES + lane_off;
                 const __nv_bfloat16* src = p_src + b * 32;
-                cp_async16(dst, src);
-                cp_async16(dst + 512, src + (int64_t)8 * K);
-                cp_async16(dst + 1024, src + (int64_t)16 * K);
-                cp_async16(dst + 1536, src + (int64_t)24 * K);
+#pragma unroll
+                for (int h = 0; h < 2 * NH; ++h) cp_async16(dst + 512 * h, src + (int64_t)(8 * h) * K);
                 if (PRO == PRO_NONE && with_x) {
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         const int row = mt * 8 + g;
                         if (row < p.M)
-                            cp_async16(dst + 2048 + mt * 512, p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
+                            cp_async16(dst + 1024 * NH + mt * 512, p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
                     }
                 }
             }
@@ -128,9 +129,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
         cp_async_commit();   // a group per slot, empty or not, keeps the wait count fixed
     };
 
-    float acc[2][MT][4];
+    float acc[NH][MT][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
+    for (int h = 0; h < NH; ++h)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -215,10 +216,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
             const int b = warp + j * kWarps;
             if (b < blocks) {
                 const unsigned char* st = ring + (size_t)cs * STAGE_BYTES + lane_off;
-                const uint4 w0 = *reinterpret_cast<const uint4*>(st);
-                const uint4 w1 = *reinterpret_cast<const uint4*>(st + 512);
-                const uint4 w2 = *reinterpret_cast<const uint4*>(st + 1024);
-                const uint4 w3 = *reinterpret_cast<const uint4*>(st + 1536);
+                uint4 w[2 * NH];
+#pragma unroll
+                for (int h = 0; h < 2 * NH; ++h) w[h] = *reinterpret_cast<const uint4*>(st + 512 * h);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     uint4 xa;
@@ -230,11 +230,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
                     else if (consumed < STAGES - 1)
                         xa = *reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
                     else
-                        xa = *reinterpret_cast<const uint4*>(st + 2048 + mt * 512);
-                    mma_bf16(acc[0][mt], w0.x, w1.x, w0.y, w1.y, xa.x, xa.y);
-                    mma_bf16(acc[0][mt], w0.z, w1.z, w0.w, w1.w, xa.z, xa.w);
-                    mma_bf16(acc[1][mt], w2.x, w3.x, w2.y, w3.y, xa.x, xa.y);
-                    mma_bf16(acc[1][mt], w2.z, w3.z, w2.w, w3.w, xa.z, xa.w);
+                        xa = *reinterpret_cast<const uint4*>(st + 1024 * NH + mt * 512);
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        mma_bf16(acc[h][mt], w[2 * h].x, w[2 * h + 1].x, w[2 * h].y, w[2 * h + 1].y, xa.x, xa.y);
+                        mma_bf16(acc[h][mt], w[2 * h].z, w[2 * h + 1].z, w[2 * h].w, w[2 * h + 1].w, xa.z, xa.w);
+                    }
                 }
             }
             if (++cs == STAGES) cs = 0;
@@ -242,10 +243,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
         }
         // end of a tile: sum the warps in a fixed order: partial[warp][feature 0..31][batch row 0..ROWS-1]
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-        const int n0 = tile * 32;
-        float* dst = partial + (size_t)warp * 32 * ROWS;
+        const int n0 = tile * TF;
+        float* dst = partial + (size_t)warp * TF * ROWS;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < NH; ++h)
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 dst[(h * 16 + g) * ROWS + mt * 8 + 2 * t] = acc[h][mt][0];
@@ -258,27 +259,27 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
         __syncthreads();
         if (EPI == EPI_SWIGLU) {
             // of every 16 features the first eight are gates, the last eight the matching up projections
-            for (int idx = threadIdx.x; idx < 16 * ROWS; idx += kThreads) {
-                const int f = idx / ROWS, m = idx - f * ROWS;   // f: activation column within the tile (0..15)
+            for (int idx = threadIdx.x; idx < 8 * NH * ROWS; idx += kThreads) {
+                const int f = idx / ROWS, m = idx - f * ROWS;   // f: activation column within the tile
                 if (m >= p.M) continue;
                 const int gate_row = (f >> 3) * 16 + (f & 7);
                 float gate = 0.0f, up = 0.0f;
 #pragma unroll
                 for (int w = 0; w < kWarps; ++w) {
-                    gate += partial[(size_t)w * 32 * ROWS + gate_row * ROWS + m];
-                    up += partial[(size_t)w * 32 * ROWS + (gate_row + 8) * ROWS + m];
+                    gate += partial[(size_t)w * TF * ROWS + gate_row * ROWS + m];
+                    up += partial[(size_t)w * TF * ROWS + (gate_row + 8) * ROWS + m];
                 }
                 const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + tile * 16 + f] =
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + tile * 8 * NH + f] =
                     __float2bfloat16_rn(act);
             }
         } else {
-            for (int idx = threadIdx.x; idx < 32 * ROWS; idx += kThreads) {
-                const int m = idx / 32, f = idx - m * 32;  // consecutive threads write consecutive features
+            for (int idx = threadIdx.x; idx < TF * ROWS; idx += kThreads) {
+                const int m = idx / TF, f = idx - m * TF;  // consecutive threads write consecutive features
                 if (m >= p.M) continue;
                 float sum = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kWarps; ++w) sum += partial[(size_t)w * 32 * ROWS + f * ROWS + m];
+                for (int w = 0; w < kWarps; ++w) sum += partial[(size_t)w * TF * ROWS + f * ROWS + m];
                 if (EPI == EPI_F32)
                     reinterpret_cast<float*>(p.out)[(int64_t)m * p.out_stride + n0 + f] = sum;
                 else
@@ -290,23 +291,31 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     }
 }
 
-template <int MT, int PRO, int EPI>
-int launch(const LinearParams& p, cudaStream_t stream) {
+template <int MT, int PRO, int EPI, int NH>
+int launch_tiles(const LinearParams& p, cudaStream_t stream) {
     constexpr int ROWS = 8 * MT;
-    constexpr int STAGE_BYTES = 2048 + (PRO == PRO_NONE ? 512 * MT : 0);
-    size_t smem = (size_t)kWarps * 32 * ROWS * sizeof(float) + (size_t)kWarps * kStages * STAGE_BYTES;
+    constexpr int TF = 16 * NH;
+    constexpr int STAGE_BYTES = 1024 * NH + (PRO == PRO_NONE ? 512 * MT : 0);
+    size_t smem = (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)kWarps * ring_depth(NH) * STAGE_BYTES;
     if (PRO != PRO_NONE) smem += (size_t)ROWS * (p.K + 32) * 2;
-    auto kernel = decode_linear_kernel<MT, PRO, EPI>;
+    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH>;
     if (smem > 48 * 1024) {
         if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
-    const int tiles = p.N / 32;
+    const int tiles = p.N / TF;
     const int per_cta = (tiles + kMaxCtas - 1) / kMaxCtas;           // tiles per CTA, evenly spread
     const int grid = (tiles + per_cta - 1) / per_cta;
     cudaError_t err = tb_launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, p);
     return err == cudaSuccess ? tb_launch_status() : (int)err;
+}
+
+template <int MT, int PRO, int EPI>
+int launch(const LinearParams& p, cudaStream_t stream) {
+    // 32-feature tiles when there are enough of them to give every SM work, else 16-feature tiles
+    if (p.N % 32 == 0 && p.N / 32 >= 148) return launch_tiles<MT, PRO, EPI, 2>(p, stream);
+    return launch_tiles<MT, PRO, EPI, 1>(p, stream);
 }
 
 template <int MT>
@@ -330,7 +339,7 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
 
 // 1 if the sizes are ones this kernel takes, else 0 (the caller then uses the general path).
 TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
-    if (M < 1 || M > 16 || N < 32 || N % 32 != 0 || K < 32 || K % 32 != 0) return 0;
+    if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < 32 || K % 32 != 0) return 0;
     if (prologue != PRO_NONE && (size_t)(M <= 8 ? 8 : 16) * (K + 32) * 2 > 96 * 1024) return 0;
     return 1;
 }

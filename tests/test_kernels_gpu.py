@@ -396,7 +396,7 @@ def test_silu_mul_interleaved_layout():
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n, k", [(32, 32), (96, 96), (160, 64), (2048, 2048), (384, 320), (1024, 4096)])
+@pytest.mark.parametrize("n, k", [(16, 32), (48, 96), (160, 64), (2048, 2048), (384, 320), (1024, 4096)])
 def test_decode_linear_plain_and_f32(m, n, k):
     from tesseract_b200 import kernels
 
@@ -467,7 +467,7 @@ def test_decode_linear_refuses_other_sizes():
     from tesseract_b200 import kernels
 
     assert not kernels.decode_linear_supported(17, 64, 64)
-    assert not kernels.decode_linear_supported(4, 48, 64)
+    assert not kernels.decode_linear_supported(4, 72, 64)
     assert not kernels.decode_linear_supported(4, 64, 72)
     assert kernels.decode_linear_supported(16, 128256, 2048, kernels.PRO_ADD_NORM)
     assert not kernels.decode_linear_supported(16, 64, 8192, kernels.PRO_ADD_NORM)      # rows would not fit shared memory
