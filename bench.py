@@ -268,6 +268,109 @@ def run_ours(args):
     return 0
 
 
+def run_kernels(args):
+    """Each hot kernel alone at the 1B model's sizes: device time per launch, in a CUDA graph of 16 launches over 16
+    distinct weight or cache buffers (so that nothing stays in L2 from one launch to the next)."""
+    import math
+
+    import torch
+
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    pk = peaks()
+    out_lines = {}
+
+    def timed(fns, reps=20):
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for f in fns:
+                f()
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1000 / reps / len(fns)
+
+    m = args.batch
+    for name, n, k, fused in (("qkv", 3072, 2048, True), ("o", 2048, 2048, False), ("gate_up", 16384, 2048, True),
+                              ("down", 2048, 8192, False)):
+        ws = [(torch.randn(n, k, device=dev) / math.sqrt(k)).to(torch.bfloat16) for _ in range(16)]
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        upd = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        nw = torch.ones(k, device=dev)
+        out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        res_out = torch.empty_like(x)
+        mb = n * k * 2 / 1e6
+        entry = {"weight_mb": mb, "hbm_floor_us": mb / pk["hbm_gbs"] * 1e3,
+                 "library_us": timed([lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]),
+                 "decode_linear_us": timed([lambda w=w: kernels.decode_linear(w, out, x=x) for w in ws])}
+        if fused:
+            entry["decode_linear_add_norm_us"] = timed([lambda w=w: kernels.decode_linear(
+                w, out, residual=x, update=upd, norm_weight=nw, eps=1e-5, residual_out=res_out) for w in ws])
+        out_lines[f"decode_linear_m{m}_{name}"] = entry
+        del ws
+
+    nh, nkv, d, ps, ctx = 32, 8, 64, PAGE_SIZE, 2100
+    for batch in (1, 8, 64):
+        pages = -(-ctx // ps)
+        caches = [torch.randn(batch * pages + 1, 2, nkv, ps, d, device=dev).to(torch.bfloat16) for _ in range(16)]
+        table = (torch.arange(batch * pages, device=dev, dtype=torch.int32).view(batch, pages) + 1).contiguous()
+        q = torch.randn(batch, nh * d, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        row_start = torch.arange(batch + 1, device=dev, dtype=torch.int32)
+        seq_begin = torch.full((batch,), ctx - 1, device=dev, dtype=torch.int32)
+        splits = kernels.attention_splits(batch, nkv, ctx)
+        us = timed([lambda c=c: kernels.attention_mma(q, out, c, row_start, seq_begin, table, batch, 1, nh, nkv, d, ps, 0,
+                                                      0.125, False, True, splits) for c in caches])
+        mb = batch * ctx * 2 * nkv * d * 2 / 1e6
+        out_lines[f"attention_decode_b{batch}_ctx{ctx}"] = {"kv_mb": mb, "hbm_floor_us": mb / pk["hbm_gbs"] * 1e3,
+                                                           "splits": splits, "us": us}
+        del caches
+
+    tokens = PROMPT_TOKENS
+    pages = tokens // ps
+    caches = [torch.randn(pages + 1, 2, nkv, ps, d, device=dev).to(torch.bfloat16) for _ in range(16)]
+    table = (torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages) + 1).contiguous()
+    q = torch.randn(tokens, nh * d, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    row_start = torch.tensor([0, tokens], device=dev, dtype=torch.int32)
+    seq_begin = torch.zeros(1, device=dev, dtype=torch.int32)
+    flops = 2 * tokens * tokens * d * nh
+    t_mma = timed([lambda c=c: kernels.attention_mma(q, out, c, row_start, seq_begin, table, 1, tokens, nh, nkv, d, ps, 0,
+                                                     0.125, True, False, 1) for c in caches])
+    t_tc = timed([lambda c=c: kernels.attention_tcgen05(q, out, c, row_start, seq_begin, table, 1, tokens, nh, nkv, d,
+                                                        ps, 0, 0.125) for c in caches])
+    out_lines[f"attention_prefill_{tokens}"] = {"causal_gflop": flops / 1e9, "mma_sync_us": t_mma,
+                                                "mma_sync_tflops": flops / t_mma / 1e6, "tcgen05_us": t_tc,
+                                                "tcgen05_tflops": flops / t_tc / 1e6}
+    del caches
+
+    for name, n, k in (("qkv", 3072, 2048), ("o", 2048, 2048), ("gate_up", 16384, 2048), ("down", 2048, 8192)):
+        ws = [(torch.randn(n, k, device=dev) / math.sqrt(k)).to(torch.bfloat16) for _ in range(8)]
+        x = torch.randn(tokens, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(tokens, n, device=dev, dtype=torch.bfloat16)
+        fl = 2 * tokens * n * k
+        t_lib = timed([lambda w=w: torch.mm(x, w.t(), out=out) for w in ws], reps=5)
+        t_own = timed([lambda w=w: kernels.gemm_tcgen05(x, w, out) for w in ws], reps=5)
+        out_lines[f"gemm_m{tokens}_{name}"] = {"gflop": fl / 1e9, "library_us": t_lib, "library_tflops": fl / t_lib / 1e6,
+                                               "tcgen05_us": t_own, "tcgen05_tflops": fl / t_own / 1e6}
+        del ws
+    out_lines["tcgen05_wait_timeouts"] = kernels.tcgen05_error()
+    print(json.dumps({"only": "kernels", "peaks": pk, "kernels": out_lines}))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -276,7 +379,7 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     parser.add_argument("--no-graphs", action="store_true", help="decode without CUDA-graph replay")
     args = parser.parse_args()
@@ -285,6 +388,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
+    if args.only == "kernels":
+        return run_kernels(args)
     return run_ours(args)
 
 
