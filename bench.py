@@ -283,6 +283,7 @@ def run_kernels(args):
     out_lines = {}
 
     def timed(fns, reps=20):
+        torch.cuda.synchronize()          # the inputs were made on the default stream: they must exist first
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
             for f in fns:

@@ -17,15 +17,11 @@
 // runs out sets *error, stops the other roles, and the CTA still frees its tensor memory.
 // Two CTAs fit on an SM (about 100 KiB of shared memory and 256 tensor-memory columns each), so one CTA's softmax
 // overlaps the other's products.
-#include <cuda.h>
-
-#include <map>
-#include <mutex>
-#include <tuple>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace {
+
+using namespace tbtma;
 
 constexpr int D = 64;            // head_dim this kernel is built for
 constexpr int BM = 128;          // folded query rows per CTA
@@ -34,7 +30,6 @@ constexpr int STAGES = 2;        // K/V ring depth
 constexpr int kThreads = 192;         // warps 0..3 softmax, warp 4 issuer, warp 5 TMA producer
 constexpr uint32_t kTileBytes = BN * D * 2;           // 16 KiB: one K or V block, also the Q tile and half a P tile
 constexpr uint32_t kTmemColumns = 256;                // S: columns 0..127, O_blk: columns 128..191
-constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
 
@@ -52,39 +47,6 @@ struct TcAttnParams {
     float scale_log2;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255) == 255 && *abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// One box of the cache tensor [page][K|V][kv_head][page_size][64]: `rows` consecutive keys of one page, one head.
-__device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map, uint32_t bar, int key_in_page,
-                                            int kv_head, int which, int page) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
-}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
@@ -217,7 +179,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         mbar_init(p_ready, BM);
         mbar_init(o_full, 1);
         mbar_init(s_free, BM);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -474,48 +436,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-// Tensor map of one cache entry [pages][2][kv_heads][page_size][64] (bfloat16), boxes of min(page_size, 128) keys
-// of one head with the 128-byte swizzle.  Maps are kept per (pointer, geometry): a cache entry lives as long as
-// its model.
-const CUtensorMap* cache_map_for(const void* cache, int pages, int num_kv_heads, int page_size) {
-    static std::mutex lock;
-    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> maps;
-    std::lock_guard<std::mutex> guard(lock);
-    const auto key = std::make_tuple(cache, pages, num_kv_heads, page_size);
-    auto found = maps.find(key);
-    if (found != maps.end()) return &found->second;
-    EncodeTiledFn fn = encode_tiled();
-    if (fn == nullptr) return nullptr;
-    CUtensorMap map;
-    const cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)page_size, (cuuint64_t)num_kv_heads, 2, (cuuint64_t)pages};
-    const cuuint64_t row = (cuuint64_t)D * 2;
-    const cuuint64_t strides[4] = {row, row * page_size, row * page_size * num_kv_heads,
-                                   row * page_size * num_kv_heads * 2};
-    const cuuint32_t box[5] = {(cuuint32_t)D, (cuuint32_t)(page_size < BN ? page_size : BN), 1, 1, 1};
-    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
-    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, elem,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return nullptr;
-    return &maps.emplace(key, map).first->second;
-}
-
 }  // namespace
 
 // 1 if this kernel takes the sizes (else the caller uses the mma.sync kernel).
@@ -538,7 +458,7 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
         return TB_ERR_BAD_ALIGN;
     if (num_seqs > 65535 || num_kv_heads > 65535) return TB_ERR_BAD_SIZE;
-    const CUtensorMap* map = cache_map_for(cache, cache_pages, num_kv_heads, page_size);
+    const CUtensorMap* map = cache_map_for(cache, cache_pages, num_kv_heads, page_size, BN);
     if (map == nullptr) return TB_ERR_BAD_SIZE;
     TcAttnParams p;
     p.q = (const __nv_bfloat16*)q;

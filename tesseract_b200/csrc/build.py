@@ -31,6 +31,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 # Files a source includes besides common.cuh and its own header (they count for its hash).
 INCLUDES: Dict[str, List[str]] = {
     "attention_noalloc": ["attention_mma.cu", "attention_noalloc.h"],
+    "attention_tcgen05": ["tma.cuh"],
 }
 
 # Every source file, with the extra flags it needs.

@@ -1,0 +1,100 @@
+// Bulk tensor copies (TMA) and mbarriers, shared by the kernels that stream cache pages.
+//
+// A cache entry [pages][K|V][kv_heads][page_size][head_dim] (bfloat16, head_dim 64) is described to the TMA unit
+// once by a five-dimensional tensor map; a copy then brings min(page_size, max_rows) consecutive keys of one page
+// and one head into shared memory as rows of 128 bytes with the 128-byte swizzle (16-byte chunk index XOR row
+// mod 8), the layout that both ldmatrix-fed mma.sync tiles and tcgen05 matrix descriptors read.  No copy uses
+// cluster multicast.  Every wait on an mbarrier is bounded.
+#pragma once
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace tbtma {
+
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// False if the barrier did not flip within the limit, or another thread of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255) == 255 && *abort_flag) return false;
+    }
+    return false;
+}
+
+// One box of the cache tensor: keys key_in_page.. of `page`, head `kv_head`, K (which = 0) or V (which = 1).
+__device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map, uint32_t bar, int key_in_page,
+                                            int kv_head, int which, int page) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Tensor map of one cache entry with head_dim 64, boxes of min(page_size, max_rows) keys of one head.  Maps are
+// kept per (pointer, geometry): a cache entry lives as long as its model.
+inline const CUtensorMap* cache_map_for(const void* cache, int pages, int num_kv_heads, int page_size, int max_rows) {
+    static std::mutex lock;
+    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> maps;
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_tuple(cache, pages, num_kv_heads, page_size, max_rows);
+    auto found = maps.find(key);
+    if (found != maps.end()) return &found->second;
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return nullptr;
+    CUtensorMap map;
+    const cuuint64_t dims[5] = {64, (cuuint64_t)page_size, (cuuint64_t)num_kv_heads, 2, (cuuint64_t)pages};
+    const cuuint64_t row = 64 * 2;
+    const cuuint64_t strides[4] = {row, row * page_size, row * page_size * num_kv_heads,
+                                   row * page_size * num_kv_heads * 2};
+    const cuuint32_t box[5] = {64, (cuuint32_t)(page_size < max_rows ? page_size : max_rows), 1, 1, 1};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    return &maps.emplace(key, map).first->second;
+}
+
+}  // namespace tbtma
