@@ -11,11 +11,12 @@
 //   tb_attention_tiles   : one CTA per (128-row tile, kv head, sequence); its 8 warps own 16 rows
 //                          each and share every K/V tile.  For sequences with more than 16 rows.
 //   tb_attention_decode  : sequences with at most 16 rows (decode, and tiny portions); one CTA per
-//                          (key split, kv head, sequence); its 4 warps share the 16 rows and own 16
-//                          keys of every 64-key tile, are merged in shared memory, and the split that finishes
-//                          last merges all splits from 32-bit partials in scratch memory.
-// K/V tiles come in through cp.async (16-byte chunks, XOR-swizzled in shared memory, double
-// buffered); the products are mma.sync.m16n8k16 bf16 with fragments from ldmatrix.
+//                          (key split, kv head, sequence); its 4 warps share the 16 rows, each streams every
+//                          fourth tile of 32 (16 for wide heads) keys through a ring of its own, they are merged
+//                          in shared memory, and the split that finishes last merges all splits from 32-bit
+//                          partials in scratch memory.
+// K/V tiles come in through cp.async (16-byte chunks, XOR-swizzled in shared memory, rings of three
+// stages); the products are mma.sync.m16n8k16 bf16 with fragments from ldmatrix.
 // head_dim may be any multiple of 16 up to 256: tiles are zero-padded to 32/64/128/256 columns.
 #include "common.cuh"
 
@@ -25,6 +26,10 @@ constexpr int kThreads = 128;
 constexpr int kWarps = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
+// split decode kernel: keys per warp tile and depth of each warp's ring
+template <int D>
+constexpr int kDecodeKeys = D <= 64 ? 32 : 16;
+constexpr int kDecodeStages = 3;  // deeper rings measured no faster: a lone warp is bound by its own instruction chain
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -328,72 +333,13 @@ __global__ void __launch_bounds__(WARPS * 32, (D <= 64 ? 2 : 1)) attention_tiles
     }
 }
 
-// ------------------------------------------------------------------------------------------------
-// Decode and tiny portions (at most 16 folded rows): one CTA per (key split, kv head, sequence).
+// Tail of the decode kernels: merges the CTA's four warps (each saw some of the split's keys) through shared
+// memory, stores the split's partial result, and lets the split that finishes last merge all splits.
 template <int D>
-__global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
-    constexpr int BN = 64;
-    extern __shared__ __align__(128) unsigned char smem[];
-    pdl_trigger();
-    pdl_wait();
-    const int split = blockIdx.x, kv_head = blockIdx.y, seq = blockIdx.z;
-    const int first_row = p.row_start[seq];
-    const int q_len = p.row_start[seq + 1] - first_row;
-    const int n_rows = q_len * p.group;
-    if (n_rows > 16 || n_rows == 0) return;
-    const int begin = p.seq_begin[seq];
-    const int* table = p.block_table + (int64_t)seq * p.bt_stride;
+__device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char* smem, int split, int kv_head, int seq,
+                                              int first_row, int n_rows, float (&o)[D / 8][4], float (&m)[2],
+                                              float (&l)[2]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    const uint32_t q_tile = smem_u32(smem);
-    const uint32_t kv_tiles = q_tile + 16 * D * 2;
-    constexpr uint32_t kTileBytes = BN * D * 2;
-
-    const int key_hi = begin + q_len - 1;
-    const int key_lo = p.window > 0 ? max(0, begin - p.window + 1) : 0;
-    const int kb_first = key_lo / BN, kb_end = key_hi / BN + 1;
-    const int per_split = (kb_end - kb_first + p.splits - 1) / p.splits;
-    const int b0 = kb_first + split * per_split;
-    const int b1 = min(kb_end, b0 + per_split);
-
-    int pos[2], lo[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int fr = (lane >> 2) + i * 8;
-        pos[i] = fr < n_rows ? begin + fr / p.group : -1;
-        lo[i] = p.window > 0 ? max(0, pos[i] - p.window + 1) : 0;
-    }
-    float o[D / 8][4], m[2] = {kMasked, kMasked}, l[2] = {0.0f, 0.0f};
-#pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
-
-    if (b0 < b1) {
-        load_q_tile<D, 16>(q_tile, p, first_row, kv_head, 0, n_rows);
-        load_kv_tile<D, BN>(kv_tiles, p, table, kv_head, 0, b0 * BN, key_lo, key_hi);
-        load_kv_tile<D, BN>(kv_tiles + kTileBytes, p, table, kv_head, 1, b0 * BN, key_lo, key_hi);
-        cp_async_commit();
-        for (int kb = b0; kb < b1; ++kb) {
-            const int stage = (kb - b0) & 1;
-            if (kb + 1 < b1) {
-                const uint32_t next = kv_tiles + (stage ^ 1) * 2 * kTileBytes;
-                load_kv_tile<D, BN>(next, p, table, kv_head, 0, (kb + 1) * BN, key_lo, key_hi);
-                load_kv_tile<D, BN>(next + kTileBytes, p, table, kv_head, 1, (kb + 1) * BN, key_lo, key_hi);
-                cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
-            __syncthreads();
-            if (kb * BN + warp * 16 <= key_hi) {
-                const uint32_t cur = kv_tiles + stage * 2 * kTileBytes;
-                warp_attend<D, 16>(q_tile, 0, cur, cur + kTileBytes, warp * 16, kb * BN + warp * 16, pos, lo,
-                                   p.scale_log2, o, m, l);
-            }
-            __syncthreads();
-        }
-    }
     // merge the four warps (each saw a quarter of the keys) through shared memory
     float* sm_m = reinterpret_cast<float*>(smem);             // [warps][16]
     float* sm_l = sm_m + kWarps * 16;                         // [warps][16]
@@ -502,6 +448,129 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     }
 }
 
+// One warp copies NK keys of one kv head's K and V (keys key0.. of the sequence) into its own swizzled tiles.
+template <int D, int NK>
+__device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, const AttnParams& p, const int* table,
+                                             int kv_head, int key0, int key_lo, int key_hi) {
+    constexpr int CH = D / 8;
+    static_assert((NK * CH) % 32 == 0, "a warp copies whole passes of 32 chunks");
+    const int lane = threadIdx.x & 31;
+    const int64_t head_block = (int64_t)p.page_size * p.head_dim;
+    const int64_t page_block = 2 * (int64_t)p.num_kv_heads * head_block;
+    const int64_t v_offset = (int64_t)p.num_kv_heads * head_block;
+    const __nv_bfloat16* base = p.cache + (int64_t)kv_head * head_block;
+#pragma unroll
+    for (int pass = 0; pass < NK * CH / 32; ++pass) {
+        const int idx = pass * 32 + lane;
+        const int r = idx / CH, c = idx % CH;
+        const int key = key0 + r;
+        const bool ok = key >= key_lo && key <= key_hi && c * 8 < p.head_dim;
+        const __nv_bfloat16* src = base;
+        if (ok) {
+            const int page = table[key >> p.page_shift];
+            src = base + (int64_t)page * page_block + (int64_t)(key & (p.page_size - 1)) * p.head_dim + c * 8;
+        }
+        const uint32_t offset = tile_offset<D>(r, c);
+        cp_async16(k_tile + offset, src, ok);
+        cp_async16(v_tile + offset, src + v_offset, ok);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode and tiny portions (at most 16 folded rows): one CTA per (key split, kv head, sequence).  The split's
+// keys are cut into tiles of NK keys; warp w takes every fourth tile and streams its tiles through a ring of its
+// own (cp.async groups, waits and __syncwarp only), so no warp ever waits for another inside the loop and each
+// keeps STAGES - 1 tiles in flight.
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
+    constexpr int NK = kDecodeKeys<D>;
+    constexpr int STAGES = kDecodeStages;
+    constexpr bool QREG = D <= 128;
+    constexpr uint32_t kTileBytes = NK * D * 2;
+    constexpr uint32_t kStageBytes = 2 * kTileBytes;
+    extern __shared__ __align__(128) unsigned char smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int split = blockIdx.x, kv_head = blockIdx.y, seq = blockIdx.z;
+    const int first_row = p.row_start[seq];
+    const int q_len = p.row_start[seq + 1] - first_row;
+    const int n_rows = q_len * p.group;
+    if (n_rows > 16 || n_rows == 0) return;
+    const int begin = p.seq_begin[seq];
+    const int* table = p.block_table + (int64_t)seq * p.bt_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t q_tile = smem_u32(smem);
+    const uint32_t ring = q_tile + 16 * D * 2 + warp * (STAGES * kStageBytes);
+
+    const int key_hi = begin + q_len - 1;
+    const int key_lo = p.window > 0 ? max(0, begin - p.window + 1) : 0;
+    const int lo_max = p.window > 0 ? max(0, key_hi - p.window + 1) : 0;  // first key that every row sees
+    const int kb_first = key_lo / NK, kb_end = key_hi / NK + 1;
+    const int per_split = (kb_end - kb_first + p.splits - 1) / p.splits;
+    const int b0 = kb_first + split * per_split;
+    const int b1 = min(kb_end, b0 + per_split);
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int fr = (lane >> 2) + i * 8;
+        pos[i] = fr < n_rows ? begin + fr / p.group : -1;
+        lo[i] = p.window > 0 ? max(0, pos[i] - p.window + 1) : 0;
+    }
+    float o[D / 8][4], m[2] = {kMasked, kMasked}, l[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+
+    if (b0 < b1) {
+        load_q_tile<D, 16>(q_tile, p, first_row, kv_head, 0, n_rows);
+        cp_async_commit();
+        int kb_load = b0 + warp;
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (kb_load < b1)
+                warp_load_kv<D, NK>(ring + st * kStageBytes, ring + st * kStageBytes + kTileBytes, p, table, kv_head,
+                                    kb_load * NK, key_lo, key_hi);
+            cp_async_commit();  // one group per stage, empty or not, keeps the wait count fixed
+            kb_load += kWarps;
+        }
+        cp_async_wait<STAGES - 1>();  // the query tile is the oldest group
+        __syncthreads();
+        uint32_t qf[QREG ? D / 16 : 1][4];
+        if (QREG) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                ldmatrix_x4(qf[ks], q_tile + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+        }
+        int it = 0;
+        for (int kb = b0 + warp; kb < b1; kb += kWarps, ++it) {
+            if (kb_load < b1) {
+                const uint32_t dst = ring + ((it + STAGES - 1) % STAGES) * kStageBytes;
+                warp_load_kv<D, NK>(dst, dst + kTileBytes, p, table, kv_head, kb_load * NK, key_lo, key_hi);
+            }
+            cp_async_commit();
+            kb_load += kWarps;
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const uint32_t cur = ring + (it % STAGES) * kStageBytes;
+            // no mask when every row sees every key of the tile
+            const bool full = kb * NK >= lo_max && kb * NK + NK - 1 <= begin;
+            if (full)
+                warp_attend<D, NK, QREG, false>(q_tile, 0, cur, cur + kTileBytes, 0, kb * NK, pos, lo, p.scale_log2,
+                                                o, m, l, qf);
+            else
+                warp_attend<D, NK, QREG, true>(q_tile, 0, cur, cur + kTileBytes, 0, kb * NK, pos, lo, p.scale_log2,
+                                               o, m, l, qf);
+            __syncwarp();  // every lane is done with this stage before the next copy overwrites it
+        }
+        cp_async_wait<0>();
+    }
+    __syncthreads();  // the rings become the merge area
+    decode_finish<D>(p, smem, split, kv_head, seq, first_row, n_rows, o, m, l);
+}
+
 template <int D>
 int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_tiles, int run_decode,
                cudaStream_t stream) {
@@ -521,10 +590,10 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
         if (int status = tb_launch_status()) return status;
     }
     if (run_decode) {
-        const size_t tiles = (size_t)16 * D * 2 + (size_t)2 * 2 * 64 * D * 2;
         const size_t merge_a = (size_t)(2 * kWarps * 16 + kWarps * 16 * D) * sizeof(float);
         const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
         const size_t merge = merge_a > merge_b ? merge_a : merge_b;
+        const size_t tiles = (size_t)16 * D * 2 + (size_t)kWarps * kDecodeStages * 2 * kDecodeKeys<D> * D * 2;
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = attention_decode_kernel<D>;
         if (smem > 48 * 1024) {

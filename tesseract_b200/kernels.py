@@ -267,12 +267,22 @@ def _counters(device, count: int) -> torch.Tensor:
     return buf
 
 
-def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
-    """How many key splits the decode kernel uses: about four CTAs for every SM, at least two 64-key tiles each."""
+def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64) -> int:
+    """How many key splits the decode kernel uses.
+
+    A CTA's four warps each stream every fourth tile of 32 keys (16 for head sizes above 64) at about a
+    microsecond a tile, and merging splits costs about five; two CTAs fit an SM.  The choice minimises that
+    estimate over the split counts that keep all CTAs resident at once (at most 16)."""
+    tiles = -(-max_context // (32 if head_dim <= 64 else 16))
     ctas = max(1, num_seqs * num_kv_heads)
-    want = -(-4 * _SM_COUNT // ctas)
-    blocks = -(-max_context // 64)
-    return max(1, min(want, -(-blocks // 2), 64))
+    limit = max(1, min(16, 2 * _SM_COUNT // ctas))
+    best, best_cost = 1, float("inf")
+    for splits in range(1, limit + 1):
+        per_warp = -(-(-(-tiles // splits)) // 4)
+        cost = per_warp + (5.0 if splits > 1 else 0.0) + 0.15 * splits
+        if cost < best_cost:
+            best, best_cost = splits, cost
+    return best
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,

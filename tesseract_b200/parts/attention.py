@@ -112,7 +112,7 @@ class Attention(Mixer):
         fold = self.num_heads // self.num_kv_heads
         long_seqs = any(n * fold > 16 for n in ctx.host_new)
         short_seqs = any(n * fold <= 16 for n in ctx.host_new)
-        splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context) if short_seqs else 1
+        splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context, self.head_dim) if short_seqs else 1
         if long_seqs and self.prompt_kernel == "tcgen05" and self._tcgen05 is None:
             self._tcgen05 = kernels.attention_tcgen05_supported(self.num_heads, self.num_kv_heads, self.head_dim,
                                                                 cache.page_size)
