@@ -11,9 +11,10 @@
 //   tb_attention_tiles   : one CTA per (128-row tile, kv head, sequence); its 8 warps own 16 rows
 //                          each and share every K/V tile.  For sequences with more than 16 rows.
 //   tb_attention_decode  : sequences with at most 16 rows (decode, and tiny portions); one CTA per
-//                          (key split, kv head, sequence); its 4 warps share the 16 rows, each streams every
-//                          fourth tile of 32 (16 for wide heads) keys through a ring of its own, they are merged
-//                          in shared memory, and the split that finishes last merges all splits from 32-bit
+//                          (key split, kv head, sequence); its 8 warps (4 for the widest heads) share the 16
+//                          rows, each streams every eighth tile of 16 keys through a ring of its own, they are
+//                          merged in shared memory, and the splits are merged through the shared memory of a
+//                          thread-block cluster (up to 8 splits) or by the split that finishes last from 32-bit
 //                          partials in scratch memory.
 // K/V tiles come in through cp.async (16-byte chunks, XOR-swizzled in shared memory, rings of three
 // stages); the products are mma.sync.m16n8k16 bf16 with fragments from ldmatrix.
@@ -26,9 +27,12 @@ constexpr int kThreads = 128;
 constexpr int kWarps = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
-// split decode kernel: keys per warp tile and depth of each warp's ring
+// split decode kernel: keys per warp tile, depth of each warp's ring, warps per CTA (eight while three stages of
+// every warp fit shared memory twice over or, for wide heads, once)
+constexpr int kDecodeKeys = 16;
 template <int D>
-constexpr int kDecodeKeys = D <= 64 ? 32 : 16;
+constexpr int kDecodeWarps = D <= 128 ? 8 : 4;
+constexpr int kMaxClusterSplits = 8;  // the portable limit of a thread-block cluster
 constexpr int kDecodeStages = 3;  // deeper rings measured no faster: a lone warp is bound by its own instruction chain
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -66,6 +70,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Thread-block clusters: a barrier over all CTAs of the cluster and a load from a peer CTA's shared memory.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bf16 tile, XOR-swizzled so that the
 // eight rows an ldmatrix reads fall into distinct bank groups.
 template <int D>
@@ -88,6 +109,7 @@ struct AttnParams {
     int64_t q_stride, out_stride;
     int bt_stride, total_rows;
     int num_heads, num_kv_heads, group, head_dim, page_shift, page_size, window, splits;
+    int cluster;                 // decode: the splits of a (sequence, kv head) are one thread-block cluster
     float scale_log2;            // scale * log2(e): scores are kept in the base-2 domain
 };
 
@@ -333,17 +355,21 @@ __global__ void __launch_bounds__(WARPS * 32, (D <= 64 ? 2 : 1)) attention_tiles
     }
 }
 
-// Tail of the decode kernels: merges the CTA's four warps (each saw some of the split's keys) through shared
-// memory, stores the split's partial result, and lets the split that finishes last merge all splits.
-template <int D>
+// Tail of the decode kernel: merges the CTA's four warps (each saw some of the split's keys) through shared
+// memory and then the splits, in ascending order whichever way they meet: as a thread-block cluster the splits
+// leave their partial results in shared memory and the first CTA reads them from its peers; otherwise they go
+// to scratch memory and the split that finishes last merges them.
+template <int D, int WARPS>
 __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char* smem, int split, int kv_head, int seq,
                                               int first_row, int n_rows, float (&o)[D / 8][4], float (&m)[2],
                                               float (&l)[2]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // merge the four warps (each saw a quarter of the keys) through shared memory
     float* sm_m = reinterpret_cast<float*>(smem);             // [warps][16]
-    float* sm_l = sm_m + kWarps * 16;                         // [warps][16]
-    float* sm_o = sm_l + kWarps * 16;                         // [warps][16][D]
+    float* sm_l = sm_m + WARPS * 16;                         // [warps][16]
+    float* sm_o = sm_l + WARPS * 16;                         // [warps][16][D]
+    float* x_ml = sm_o + WARPS * 16 * D;                     // [2][16]  this split's maximum and sum (cluster merge)
+    float* x_acc = x_ml + 32;                                 // [16][D]  this split's accumulator
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
@@ -361,14 +387,14 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_rows * D; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < n_rows * D; idx += (WARPS * 32)) {
         const int r = idx / D, col = idx - r * D;
         float big = kMasked;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) big = fmaxf(big, sm_m[w * 16 + r]);
+        for (int w = 0; w < WARPS; ++w) big = fmaxf(big, sm_m[w * 16 + r]);
         float acc = 0.0f, sum = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float wgt = exp2f(sm_m[w * 16 + r] - big);
             acc += wgt * sm_o[(w * 16 + r) * D + col];
             sum += wgt * sm_l[w * 16 + r];
@@ -380,6 +406,12 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
             if (col < p.head_dim)
                 p.out[(int64_t)row * p.out_stride + (int64_t)head * p.head_dim + col] =
                     __float2bfloat16_rn(acc / fmaxf(sum, 1.0e-8f));
+        } else if (p.cluster) {
+            x_acc[idx] = acc;
+            if (col == 0) {
+                x_ml[r] = sum > 0.0f ? big : kMasked;
+                x_ml[16 + r] = sum;
+            }
         } else {
             const int64_t slot = ((int64_t)split * p.total_rows + row) * p.num_heads + head;
             p.part_o[slot * D + col] = acc;
@@ -390,6 +422,29 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
         }
     }
     if (p.splits == 1) return;
+    if (p.cluster) {
+        cluster_sync();  // every split's partial result is in its shared memory
+        if (cluster_rank() == 0) {
+            for (int idx = threadIdx.x; idx < n_rows * D; idx += (WARPS * 32)) {
+                const int r = idx / D, col = idx - r * D;
+                if (col >= p.head_dim) continue;
+                float big = kMasked;
+                for (int s = 0; s < p.splits; ++s) big = fmaxf(big, ld_cluster_f32(x_ml + r, s));
+                float acc = 0.0f, sum = 0.0f;
+                for (int s = 0; s < p.splits; ++s) {
+                    const float l_s = ld_cluster_f32(x_ml + 16 + r, s);
+                    const float w = l_s > 0.0f ? exp2f(ld_cluster_f32(x_ml + r, s) - big) : 0.0f;
+                    sum += w * l_s;
+                    acc += w * ld_cluster_f32(x_acc + idx, s);
+                }
+                const int qpos = r / p.group, g = r - qpos * p.group;
+                p.out[(int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * p.head_dim + col] =
+                    __float2bfloat16_rn(acc / fmaxf(sum, 1.0e-8f));
+            }
+        }
+        cluster_sync();  // no CTA leaves while a peer may still read its shared memory
+        return;
+    }
 
     // The split that arrives last merges all of them (a fixed order over the splits, so the result does not
     // depend on which one that is) and leaves the counter at zero for the next launch.
@@ -409,7 +464,7 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
     float* wgt = reinterpret_cast<float*>(smem);              // [splits][16]
     float* row_big = wgt + p.splits * 16;                     // [16]
     float* row_sum = row_big + 16;                            // [16]
-    for (int idx = threadIdx.x; idx < p.splits * n_rows; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < p.splits * n_rows; idx += (WARPS * 32)) {
         const int s = idx / n_rows, r = idx - s * n_rows;
         const int qpos = r / p.group, g = r - qpos * p.group;
         const int64_t slot = ((int64_t)s * p.total_rows + first_row + qpos) * p.num_heads + kv_head * p.group + g;
@@ -432,7 +487,7 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
         row_sum[r] = sum;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_rows * D; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < n_rows * D; idx += (WARPS * 32)) {
         const int r = idx / D, col = idx - r * D;
         if (col >= p.head_dim) continue;
         const int qpos = r / p.group, g = r - qpos * p.group;
@@ -478,24 +533,27 @@ __device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, c
 
 // ------------------------------------------------------------------------------------------------
 // Decode and tiny portions (at most 16 folded rows): one CTA per (key split, kv head, sequence).  The split's
-// keys are cut into tiles of NK keys; warp w takes every fourth tile and streams its tiles through a ring of its
+// keys are cut into tiles of NK keys; warp w takes every WARPS-th tile and streams its tiles through a ring of its
 // own (cp.async groups, waits and __syncwarp only), so no warp ever waits for another inside the loop and each
 // keeps STAGES - 1 tiles in flight.
-template <int D>
-__global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
-    constexpr int NK = kDecodeKeys<D>;
+template <int D, int WARPS, int NK>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p) {
     constexpr int STAGES = kDecodeStages;
     constexpr bool QREG = D <= 128;
     constexpr uint32_t kTileBytes = NK * D * 2;
     constexpr uint32_t kStageBytes = 2 * kTileBytes;
     extern __shared__ __align__(128) unsigned char smem[];
+    // The kernel before this one in the stream wrote this step's queries and keys.  Sequence metadata, block
+    // tables and the keys of earlier steps do not depend on it and are fetched before waiting for it.
     pdl_trigger();
-    pdl_wait();
     const int split = blockIdx.x, kv_head = blockIdx.y, seq = blockIdx.z;
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
-    if (n_rows > 16 || n_rows == 0) return;
+    if (n_rows > 16 || n_rows == 0) {
+        pdl_wait();
+        return;
+    }
     const int begin = p.seq_begin[seq];
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -524,19 +582,29 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
 
+    bool waited = false;
     if (b0 < b1) {
-        load_q_tile<D, 16>(q_tile, p, first_row, kv_head, 0, n_rows);
-        cp_async_commit();
         int kb_load = b0 + warp;
 #pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
-            if (kb_load < b1)
+            if (kb_load < b1) {
+                if (!waited && (kb_load + 1) * NK > begin) {  // the tile holds keys of this step
+                    pdl_wait();
+                    waited = true;
+                }
                 warp_load_kv<D, NK>(ring + st * kStageBytes, ring + st * kStageBytes + kTileBytes, p, table, kv_head,
                                     kb_load * NK, key_lo, key_hi);
+            }
             cp_async_commit();  // one group per stage, empty or not, keeps the wait count fixed
-            kb_load += kWarps;
+            kb_load += WARPS;
         }
-        cp_async_wait<STAGES - 1>();  // the query tile is the oldest group
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+        load_q_tile<D, 16, WARPS * 32>(q_tile, p, first_row, kv_head, 0, n_rows);
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
         uint32_t qf[QREG ? D / 16 : 1][4];
         if (QREG) {
@@ -545,13 +613,13 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
                 ldmatrix_x4(qf[ks], q_tile + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
         }
         int it = 0;
-        for (int kb = b0 + warp; kb < b1; kb += kWarps, ++it) {
+        for (int kb = b0 + warp; kb < b1; kb += WARPS, ++it) {
             if (kb_load < b1) {
                 const uint32_t dst = ring + ((it + STAGES - 1) % STAGES) * kStageBytes;
                 warp_load_kv<D, NK>(dst, dst + kTileBytes, p, table, kv_head, kb_load * NK, key_lo, key_hi);
             }
             cp_async_commit();
-            kb_load += kWarps;
+            kb_load += WARPS;
             cp_async_wait<STAGES - 1>();
             __syncwarp();
             const uint32_t cur = ring + (it % STAGES) * kStageBytes;
@@ -567,8 +635,9 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
         }
         cp_async_wait<0>();
     }
+    if (!waited) pdl_wait();
     __syncthreads();  // the rings become the merge area
-    decode_finish<D>(p, smem, split, kv_head, seq, first_row, n_rows, o, m, l);
+    decode_finish<D, WARPS>(p, smem, split, kv_head, seq, first_row, n_rows, o, m, l);
 }
 
 template <int D>
@@ -590,18 +659,36 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
         if (int status = tb_launch_status()) return status;
     }
     if (run_decode) {
-        const size_t merge_a = (size_t)(2 * kWarps * 16 + kWarps * 16 * D) * sizeof(float);
+        constexpr int warps = kDecodeWarps<D>;
+        const size_t merge_a = (size_t)(2 * warps * 16 + warps * 16 * D + 32 + 16 * D) * sizeof(float);
         const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
         const size_t merge = merge_a > merge_b ? merge_a : merge_b;
-        const size_t tiles = (size_t)16 * D * 2 + (size_t)kWarps * kDecodeStages * 2 * kDecodeKeys<D> * D * 2;
+        const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages * 2 * kDecodeKeys * D * 2;
         const size_t smem = tiles > merge ? tiles : merge;
-        auto kernel = attention_decode_kernel<D>;
+        auto kernel = attention_decode_kernel<D, warps, kDecodeKeys>;
         if (smem > 48 * 1024) {
             cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess) return (int)err;
         }
-        dim3 grid(p.splits, p.num_kv_heads, num_seqs);
-        if (cudaError_t err = tb_launch_pdl(kernel, grid, dim3(kThreads), smem, stream, p)) return (int)err;
+        // programmatic dependent launch; the splits of a (sequence, kv head) as one cluster when they fit one
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(p.splits, p.num_kv_heads, num_seqs);
+        config.blockDim = dim3(warps * 32);
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[0].val.programmaticStreamSerializationAllowed = 1;
+        config.numAttrs = 1;
+        if (p.cluster) {
+            attributes[1].id = cudaLaunchAttributeClusterDimension;
+            attributes[1].val.clusterDim.x = p.splits;
+            attributes[1].val.clusterDim.y = 1;
+            attributes[1].val.clusterDim.z = 1;
+            config.numAttrs = 2;
+        }
+        config.attrs = attributes;
+        if (cudaError_t err = cudaLaunchKernelEx(&config, kernel, p)) return (int)err;
         if (int status = tb_launch_status()) return status;
     }
     return 0;
@@ -618,7 +705,8 @@ TB_EXPORT int tb_attention_mma_padded_dim(int head_dim) {
 // Attention of every row of a packed batch over its sequence's cached keys (bfloat16).
 //   run_tiles  : launch the tile kernel (sequences with more than 16 folded rows)
 //   run_decode : launch the split kernel (sequences with at most 16 folded rows) with `splits` key splits;
-//                splits > 1 needs scratch: part_o float[splits * total_rows * num_heads * padded_dim],
+//                2 to 8 splits meet as a thread-block cluster and use no scratch; more than 8 need
+//                part_o float[splits * total_rows * num_heads * padded_dim] and
 //                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o;
 //                counters int[num_seqs * num_kv_heads], all zero before the first launch (each launch leaves
 //                them zero again).
@@ -636,7 +724,8 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
     if (num_seqs > 65535 || num_kv_heads > 65535 || num_heads > 65535) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || (q_stride % 8) != 0) return TB_ERR_BAD_ALIGN;
     if (splits < 1) splits = 1;
-    if (run_decode && splits > 1) {
+    const int cluster = splits >= 2 && splits <= kMaxClusterSplits;
+    if (run_decode && splits > 1 && !cluster) {
         const int64_t need = (int64_t)splits * total_rows * num_heads * padded;
         if (part_o == nullptr || part_ml == nullptr || counters == nullptr || need > scratch_floats) return -5;
     }
@@ -663,6 +752,7 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.splits = splits;
+    p.cluster = cluster;
     p.scale_log2 = scale * kLog2e;
     const int max_folded = max_rows_per_seq * p.group;
     switch (padded) {

@@ -270,16 +270,19 @@ def _counters(device, count: int) -> torch.Tensor:
 def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64) -> int:
     """How many key splits the decode kernel uses.
 
-    A CTA's four warps each stream every fourth tile of 32 keys (16 for head sizes above 64) at about a
-    microsecond a tile, and merging splits costs about five; two CTAs fit an SM.  The choice minimises that
-    estimate over the split counts that keep all CTAs resident at once (at most 16)."""
-    tiles = -(-max_context // (32 if head_dim <= 64 else 16))
+    A CTA's eight warps (four for head sizes above 128) each stream every eighth tile of 16 keys at about
+    0.65 microseconds a tile; merging splits costs about 2.5 microseconds inside a thread-block cluster (up to
+    8 splits) and 5 through scratch memory; two CTAs fit an SM.  The choice minimises that estimate over the
+    split counts that keep all CTAs resident at once (at most 16)."""
+    tiles = -(-max_context // 16)
+    warps = 8 if head_dim <= 128 else 4
     ctas = max(1, num_seqs * num_kv_heads)
     limit = max(1, min(16, 2 * _SM_COUNT // ctas))
     best, best_cost = 1, float("inf")
     for splits in range(1, limit + 1):
-        per_warp = -(-(-(-tiles // splits)) // 4)
-        cost = per_warp + (5.0 if splits > 1 else 0.0) + 0.15 * splits
+        per_warp = -(-(-(-tiles // splits)) // warps)
+        merge = 0.0 if splits == 1 else 2.5 if splits <= 8 else 5.0
+        cost = 0.65 * per_warp + merge + 0.15 * splits
         if cost < best_cost:
             best, best_cost = splits, cost
     return best

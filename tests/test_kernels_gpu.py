@@ -333,6 +333,8 @@ def run_attention_mma(case, nh, nkv, d, page_size, window, scale, splits):
     ([17, 16, 15, 33], [1, 1, 1, 1], 6, 3, 48, 16, 0, 1),             # decode rows at pages' edges
     ([17, 16, 15, 333], [1, 1, 1, 1], 6, 3, 48, 16, 0, 3),            # the same, keys split three ways
     ([700, 64, 65, 1], [1, 1, 1, 1], 32, 8, 64, 16, 0, 8),            # more splits than some sequences have tiles
+    ([900, 64, 65, 1], [1, 1, 2, 1], 32, 8, 64, 16, 0, 12),           # too many splits for a cluster: scratch memory
+    ([500, 40], [1, 1], 8, 2, 128, 16, 0, 5),                          # five splits of a wide head as a cluster
     ([40, 129, 2, 64], [40, 5, 2, 17], 4, 2, 16, 16, 0, 2),           # long and short sequences in one batch
     ([300, 31], [1, 31], 3, 1, 32, 32, 0, 4),                          # one kv head, larger pages
     ([100, 70], [30, 1], 8, 8, 64, 16, 0, 1),                          # no grouping

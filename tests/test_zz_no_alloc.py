@@ -57,7 +57,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib = _library()
     nh, nkv, d, page_size = 32, 8, 64, 16
     scale = 1.0 / math.sqrt(d)
-    calls = [([700, 64, 65, 1], [1, 1, 1, 1], 8, 11), ([2100, 300, 31], [1, 2, 1], 5, 12)]
+    calls = [([700, 64, 65, 1], [1, 1, 1, 1], 12, 11), ([2100, 300, 31], [1, 2, 1], 9, 12)]   # more than 8 splits use the scratch
     for lengths, new, splits, seed in calls:          # the second call finds the first call's leftovers
         case = paged_case(torch.bfloat16, lengths, new, nh, nkv, d, page_size, seed=seed)
         want = run_attention_mma(case, nh, nkv, d, page_size, 0, scale, splits)
