@@ -110,6 +110,13 @@ struct AttnParams {
     int bt_stride, total_rows;
     int num_heads, num_kv_heads, group, head_dim, page_shift, page_size, window, splits;
     int cluster;                 // decode: the splits of a (sequence, kv head) are one thread-block cluster
+    // decode with the rotation fused in (every sequence brings exactly one row): q is read unrotated from the
+    // packed projection rows [q heads | k heads | v heads], rotated here, and the CTA whose keys include the new
+    // position rotates the new key and (write_kv) stores it and the new value into their cache page.
+    const __nv_bfloat16* qkv;    // null: q holds rotated queries and the cache already holds the new keys
+    const float* inv_freq;       // [head_dim / 2] or null (no rotation)
+    int64_t qkv_stride;
+    int write_kv;
     float scale_log2;            // scale * log2(e): scores are kept in the base-2 domain
 };
 
@@ -550,7 +557,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
-    if (n_rows > 16 || n_rows == 0) {
+    if (n_rows > 16 || n_rows == 0 || (p.qkv != nullptr && q_len != 1)) {
         pdl_wait();
         return;
     }
@@ -560,6 +567,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
 
     const uint32_t q_tile = smem_u32(smem);
     const uint32_t ring = q_tile + 16 * D * 2 + warp * (STAGES * kStageBytes);
+    float* trig = reinterpret_cast<float*>(smem + 16 * D * 2 + WARPS * STAGES * kStageBytes);   // [D] (fused rotation)
+    __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(trig + D);                          // [2][D]
 
     const int key_hi = begin + q_len - 1;
     const int key_lo = p.window > 0 ? max(0, begin - p.window + 1) : 0;
@@ -568,6 +577,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
     const int per_split = (kb_end - kb_first + p.splits - 1) / p.splits;
     const int b0 = kb_first + split * per_split;
     const int b1 = min(kb_end, b0 + per_split);
+    const int kb_new = begin / NK;                       // fused rotation: the tile of the new key
+    const bool owns_new = p.qkv != nullptr && kb_new >= b0 && kb_new < b1;
 
     int pos[2], lo[2];
 #pragma unroll
@@ -584,6 +595,21 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
 
     bool waited = false;
     if (b0 < b1) {
+        if (p.qkv != nullptr) {
+            // angles of the one new position: angle_i = float(position) * inv_freq[i], 32-bit, accurate functions
+            const int half = p.head_dim >> 1;
+            for (int i = threadIdx.x; i < half; i += WARPS * 32) {
+                float c = 1.0f, s = 0.0f;
+                if (p.inv_freq != nullptr) {
+                    const float angle = (float)begin * p.inv_freq[i];
+                    c = cosf(angle);
+                    s = sinf(angle);
+                }
+                trig[i] = c;
+                trig[half + i] = s;
+            }
+            __syncthreads();
+        }
         int kb_load = b0 + warp;
 #pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
@@ -602,7 +628,75 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
             pdl_wait();
             waited = true;
         }
-        load_q_tile<D, 16, WARPS * 32>(q_tile, p, first_row, kv_head, 0, n_rows);
+        if (p.qkv == nullptr) {
+            load_q_tile<D, 16, WARPS * 32>(q_tile, p, first_row, kv_head, 0, n_rows);
+        } else {
+            // rotate-half on the way in (src/cuda/kernels.rs:210-282), a pair (x[i], x[half + i]) at a time; the
+            // columns beyond head_dim and the rows beyond the group are zero
+            const int half = p.head_dim >> 1;
+            const __nv_bfloat16* row = p.qkv + (int64_t)first_row * p.qkv_stride;
+            auto put = [&](unsigned char* tile_or_null, __nv_bfloat16* linear, int r, int col, float v) {
+                const __nv_bfloat16 b = __float2bfloat16_rn(v);
+                if (tile_or_null != nullptr)
+                    *reinterpret_cast<__nv_bfloat16*>(tile_or_null + tile_offset<D>(r, col >> 3) + (col & 7) * 2) = b;
+                else
+                    linear[col] = b;
+                return b;
+            };
+            auto pair_columns = [&](int i, int& c0, int& c1) {
+                if (i < half) { c0 = i; c1 = half + i; }
+                else { c0 = p.head_dim + 2 * (i - half); c1 = c0 + 1; }
+            };
+#pragma unroll 2
+            for (int idx = threadIdx.x; idx < 16 * (D / 2); idx += WARPS * 32) {
+                const int r = idx / (D / 2), i = idx - r * (D / 2);
+                int c0, c1;
+                pair_columns(i, c0, c1);
+                float a = 0.0f, b = 0.0f;
+                if (r < n_rows && i < half) {
+                    const __nv_bfloat16* x = row + (int64_t)(kv_head * p.group + r) * p.head_dim;
+                    const float lo = __bfloat162float(x[i]), hi = __bfloat162float(x[half + i]);
+                    const float c = trig[i], s = trig[half + i];
+                    a = lo * c - hi * s;
+                    b = hi * c + lo * s;
+                }
+                put(smem, nullptr, r, c0, a);
+                put(smem, nullptr, r, c1, b);
+            }
+            if (owns_new && p.write_kv) {
+                // the new key (rotated) and value of this kv head: to the staging rows and to the cache page
+                const __nv_bfloat16* k = row + (int64_t)(p.num_heads + kv_head) * p.head_dim;
+                const __nv_bfloat16* v = k + (int64_t)p.num_kv_heads * p.head_dim;
+                const int64_t head_block = (int64_t)p.page_size * p.head_dim;
+                __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(p.cache) +
+                                      ((int64_t)table[begin >> p.page_shift] * 2 * p.num_kv_heads + kv_head) * head_block +
+                                      (int64_t)(begin & (p.page_size - 1)) * p.head_dim;
+                __nv_bfloat16* vdst = kdst + (int64_t)p.num_kv_heads * head_block;
+                for (int i = threadIdx.x; i < D / 2; i += WARPS * 32) {
+                    int c0, c1;
+                    pair_columns(i, c0, c1);
+                    float a = 0.0f, b = 0.0f;
+                    __nv_bfloat16 v0 = __float2bfloat16_rn(0.0f), v1 = v0;
+                    if (i < half) {
+                        const float lo = __bfloat162float(k[i]), hi = __bfloat162float(k[half + i]);
+                        const float c = trig[i], s = trig[half + i];
+                        a = lo * c - hi * s;
+                        b = hi * c + lo * s;
+                        v0 = v[c0];
+                        v1 = v[c1];
+                    }
+                    const __nv_bfloat16 k0 = put(nullptr, new_kv, 0, c0, a), k1 = put(nullptr, new_kv, 0, c1, b);
+                    new_kv[D + c0] = v0;
+                    new_kv[D + c1] = v1;
+                    if (i < half) {
+                        kdst[c0] = k0;
+                        kdst[c1] = k1;
+                        vdst[c0] = v0;
+                        vdst[c1] = v1;
+                    }
+                }
+            }
+        }
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
@@ -623,6 +717,16 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
             cp_async_wait<STAGES - 1>();
             __syncwarp();
             const uint32_t cur = ring + (it % STAGES) * kStageBytes;
+            if (owns_new && p.write_kv && kb == kb_new) {
+                // the copy may have read the page before this CTA's store reached it: take the staged rows
+                if (lane < D / 8) {
+                    const uint32_t off = tile_offset<D>(begin - kb_new * NK, lane);
+                    const uint4* staged = reinterpret_cast<const uint4*>(new_kv);
+                    *reinterpret_cast<uint4*>(smem + (cur - q_tile) + off) = staged[lane];
+                    *reinterpret_cast<uint4*>(smem + (cur - q_tile) + kTileBytes + off) = staged[D / 8 + lane];
+                }
+                __syncwarp();
+            }
             // no mask when every row sees every key of the tile
             const bool full = kb * NK >= lo_max && kb * NK + NK - 1 <= begin;
             if (full)
@@ -663,7 +767,8 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
         const size_t merge_a = (size_t)(2 * warps * 16 + warps * 16 * D + 32 + 16 * D) * sizeof(float);
         const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
         const size_t merge = merge_a > merge_b ? merge_a : merge_b;
-        const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages * 2 * kDecodeKeys * D * 2;
+        const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages * 2 * kDecodeKeys * D * 2 +
+                             (size_t)D * sizeof(float) + (size_t)2 * D * 2;   // + rotation angles, staged new key/value
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = attention_decode_kernel<D, warps, kDecodeKeys>;
         if (smem > 48 * 1024) {
@@ -710,19 +815,21 @@ TB_EXPORT int tb_attention_mma_padded_dim(int head_dim) {
 //                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o;
 //                counters int[num_seqs * num_kv_heads], all zero before the first launch (each launch leaves
 //                them zero again).
-TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
-                               const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
-                               int num_seqs, int total_rows, int max_rows_per_seq, int num_heads, int num_kv_heads,
-                               int head_dim, int page_size, int window, float scale, int run_tiles, int run_decode,
-                               int splits, float* part_o, float* part_ml, int64_t scratch_floats,
-                               int* counters, cudaStream_t stream) {
+static int attention_entry(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
+                           const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
+                           int num_seqs, int total_rows, int max_rows_per_seq, int num_heads, int num_kv_heads,
+                           int head_dim, int page_size, int window, float scale, int run_tiles, int run_decode,
+                           int splits, float* part_o, float* part_ml, int64_t scratch_floats, int* counters,
+                           const void* qkv, int64_t qkv_stride, const float* inv_freq, int write_kv,
+                           cudaStream_t stream) {
     if (num_seqs == 0 || total_rows == 0) return 0;
     const int padded = tb_attention_mma_padded_dim(head_dim);
     if (padded < 0) return padded;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return TB_ERR_BAD_SIZE;
     if (page_size < 8 || (page_size & (page_size - 1)) != 0) return TB_ERR_BAD_SIZE;
     if (num_seqs > 65535 || num_kv_heads > 65535 || num_heads > 65535) return TB_ERR_BAD_SIZE;
-    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || (q_stride % 8) != 0) return TB_ERR_BAD_ALIGN;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache | (uintptr_t)qkv) % 16 != 0 || (q_stride % 8) != 0)
+        return TB_ERR_BAD_ALIGN;
     if (splits < 1) splits = 1;
     const int cluster = splits >= 2 && splits <= kMaxClusterSplits;
     if (run_decode && splits > 1 && !cluster) {
@@ -753,6 +860,10 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
     p.window = window;
     p.splits = splits;
     p.cluster = cluster;
+    p.qkv = (const __nv_bfloat16*)qkv;
+    p.qkv_stride = qkv_stride;
+    p.inv_freq = inv_freq;
+    p.write_kv = write_kv;
     p.scale_log2 = scale * kLog2e;
     const int max_folded = max_rows_per_seq * p.group;
     switch (padded) {
@@ -761,4 +872,34 @@ TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64
         case 128: return launch_all<128>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
         default: return launch_all<256>(p, num_seqs, max_folded, run_tiles, run_decode, stream);
     }
+}
+
+TB_EXPORT int tb_attention_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
+                               const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
+                               int num_seqs, int total_rows, int max_rows_per_seq, int num_heads, int num_kv_heads,
+                               int head_dim, int page_size, int window, float scale, int run_tiles, int run_decode,
+                               int splits, float* part_o, float* part_ml, int64_t scratch_floats,
+                               int* counters, cudaStream_t stream) {
+    return attention_entry(q, q_stride, out, out_stride, cache, row_start, seq_begin, block_table, bt_stride, num_seqs,
+                           total_rows, max_rows_per_seq, num_heads, num_kv_heads, head_dim, page_size, window, scale,
+                           run_tiles, run_decode, splits, part_o, part_ml, scratch_floats, counters, nullptr, 0,
+                           nullptr, 0, stream);
+}
+
+// Decode step with the position encoding and the cache write folded in: every sequence brings exactly one row.
+// qkv holds the packed projection rows [q heads | k heads | v heads] (unrotated, row stride qkv_stride); queries
+// and the new key are rotated by angle_i = float(position) * inv_freq[i] (inv_freq null: no rotation), and with
+// write_kv the new key and value are stored into the cache page of their position (cache is written here).
+// Scratch arguments as for tb_attention_mma.
+TB_EXPORT int tb_attention_decode_rope(const void* qkv, int64_t qkv_stride, void* out, int64_t out_stride, void* cache,
+                                       const int* row_start, const int* seq_begin, const int* block_table,
+                                       int bt_stride, int num_seqs, int num_heads, int num_kv_heads, int head_dim,
+                                       int page_size, int window, float scale, const float* inv_freq, int write_kv,
+                                       int splits, float* part_o, float* part_ml, int64_t scratch_floats,
+                                       int* counters, cudaStream_t stream) {
+    if (qkv == nullptr || qkv_stride % 8 != 0 || (head_dim & 1)) return TB_ERR_BAD_ALIGN;
+    return attention_entry(qkv, qkv_stride, out, out_stride, cache, row_start, seq_begin, block_table, bt_stride,
+                           num_seqs, num_seqs, 1, num_heads, num_kv_heads, head_dim, page_size, window, scale,
+                           /*run_tiles=*/0, /*run_decode=*/1, splits, part_o, part_ml, scratch_floats, counters, qkv,
+                           qkv_stride, inv_freq, write_kv, stream);
 }

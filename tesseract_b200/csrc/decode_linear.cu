@@ -24,8 +24,10 @@ namespace {
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxCtas = 296;  // two resident CTAs per SM
-// Ring depth per warp (deeper rings were measured and bought nothing: two resident CTAs matter more).
-__host__ __device__ constexpr int ring_depth(int nh) { return 3; }
+// Ring depth per warp: three stages where two CTAs share an SM (deeper rings were measured and bought nothing
+// there), six where a product has so few tiles that an SM holds one CTA, which then has to cover the memory
+// latency alone.
+__host__ __device__ constexpr int ring_depth(bool deep) { return deep ? 6 : 3; }
 
 enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2 };
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -67,7 +69,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // MT: number of 8-row batch tiles (1 or 2).
 // NH: 16-feature halves per tile (2 where there are tiles enough for every SM, else 1).
-template <int MT, int PRO, int EPI, int NH>
+template <int MT, int PRO, int EPI, int NH, bool DEEP>
 __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     constexpr int X_BYTES = (PRO == PRO_NONE) ? 512 * MT : 0;   // activations ride along when they come from memory
     constexpr int TF = 16 * NH;                                  // features per tile
     constexpr int STAGE_BYTES = 1024 * NH + X_BYTES;
-    constexpr int STAGES = ring_depth(NH);
+    constexpr int STAGES = ring_depth(DEEP);
     const int blocks = K / 32;
     const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
     const int num_tiles = p.N / TF;
@@ -103,9 +105,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     int pi = 0, pj = 0, ps = 0;
     const __nv_bfloat16* p_src = p.w + ((int64_t)blockIdx.x * TF + g) * K + 8 * t;   // row g of the current tile
     auto issue = [&](bool with_x) {
+        int issued = -1;   // the K block whose weights went out (for the caller that adds the activations later)
         if (pi < my_tiles) {
             const int b = warp + pj * kWarps;
             if (b < blocks) {
+                issued = b;
                 const uint32_t dst = ring_addr + (uint32_t)ps * STAGE_BYTES + lane_off;
                 const __nv_bfloat16* src = p_src + b * 32;
 #pragma unroll
@@ -127,6 +131,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
             if (++ps == STAGES) ps = 0;
         }
         cp_async_commit();   // a group per slot, empty or not, keeps the wait count fixed
+        return issued;
     };
 
     float acc[NH][MT][4];
@@ -137,32 +142,74 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
     pdl_trigger();
+    int early[STAGES - 1];
 #pragma unroll
-    for (int q = 0; q < STAGES - 1; ++q) issue(false);   // weights do not depend on the kernel before: start now
+    for (int q = 0; q < STAGES - 1; ++q) early[q] = issue(false);   // weights do not depend on the kernel before
     pdl_wait();                                      // from here on the previous kernel's results are visible
+    if (PRO == PRO_NONE) {
+        // the activations of the blocks above, a group each: the loop's wait count then covers them as well
+#pragma unroll
+        for (int q = 0; q < STAGES - 1; ++q) {
+            if (early[q] >= 0) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int row = mt * 8 + g;
+                    if (row < p.M)
+                        cp_async16(ring_addr + (uint32_t)q * STAGE_BYTES + lane_off + 1024 * NH + mt * 512,
+                                   p.x + (int64_t)row * p.x_stride + early[q] * 32 + 8 * t);
+                }
+            }
+            cp_async_commit();
+        }
+    }
 
     if (PRO != PRO_NONE) {
         // Every CTA normalises the (few) rows itself, all threads side by side along K; CTA 0 also stores the
         // new residual.  Two passes over the rows (the second one hits L1): sums of squares, then the scaling.
+        // Eight rows at a time, all their loads issued before the first use (rows beyond M repeat row M - 1, so
+        // that no load depends on a branch), four elements per thread and row.
         float* red = partial;  // [kWarps][ROWS] partial sums of squares (the partial-sum area is free until later)
+        auto load_rows = [&](int r0, int j, float (&c)[8][4]) {
+            uint2 a[8], b[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int row = min(r0 + r, p.M - 1);
+                a[r] = *reinterpret_cast<const uint2*>(p.res + (int64_t)row * K + j);
+                if (PRO == PRO_ADD_NORM) b[r] = *reinterpret_cast<const uint2*>(p.upd + (int64_t)row * K + j);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                c[r][0] = __uint_as_float(a[r].x << 16);
+                c[r][1] = __uint_as_float(a[r].x & 0xffff0000u);
+                c[r][2] = __uint_as_float(a[r].y << 16);
+                c[r][3] = __uint_as_float(a[r].y & 0xffff0000u);
+                if (PRO == PRO_ADD_NORM) {
+                    c[r][0] += __uint_as_float(b[r].x << 16);
+                    c[r][1] += __uint_as_float(b[r].x & 0xffff0000u);
+                    c[r][2] += __uint_as_float(b[r].y << 16);
+                    c[r][3] += __uint_as_float(b[r].y & 0xffff0000u);
+                }
+            }
+        };
+        auto pack4 = [](const float (&v)[4]) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+            return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        };
         float ss[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) ss[r] = 0.0f;
-        for (int j = threadIdx.x * 8; j < K; j += kThreads * 8) {
+        for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-                if (r >= p.M) break;
-                float v[8];
-                Packet<__nv_bfloat16>::load(p.res + (int64_t)r * K + j, v);
-                if (PRO == PRO_ADD_NORM) {
-                    float a[8];
-                    Packet<__nv_bfloat16>::load(p.upd + (int64_t)r * K + j, a);
+            for (int r0 = 0; r0 < ROWS; r0 += 8) {
+                float c[8][4];
+                load_rows(r0, j, c);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] += a[e];
-                    if (blockIdx.x == 0) Packet<__nv_bfloat16>::store(p.res_out + (int64_t)r * K + j, v);
+                for (int r = 0; r < 8; ++r) {
+                    if (PRO == PRO_ADD_NORM && blockIdx.x == 0 && r0 + r < p.M)
+                        *reinterpret_cast<uint2*>(p.res_out + (int64_t)(r0 + r) * K + j) = pack4(c[r]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ss[r0 + r] += c[r][e] * c[r][e];
                 }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) ss[r] += v[e] * v[e];
             }
         }
 #pragma unroll
@@ -179,36 +226,25 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
             inv_s[threadIdx.x] = 1.0f / sqrtf(total / (float)K + p.eps);
         }
         __syncthreads();
-        for (int j = threadIdx.x * 8; j < K; j += kThreads * 8) {
-            float nw[8];
-            *reinterpret_cast<float4*>(nw) = *reinterpret_cast<const float4*>(p.norm_w + j);
-            *reinterpret_cast<float4*>(nw + 4) = *reinterpret_cast<const float4*>(p.norm_w + j + 4);
+        for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
+            const float4 nw = *reinterpret_cast<const float4*>(p.norm_w + j);
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-                float v[8];
-                if (r < p.M) {
-                    const float inv = inv_s[r];
-                    Packet<__nv_bfloat16>::load(p.res + (int64_t)r * K + j, v);
-                    if (PRO == PRO_ADD_NORM) {
-                        float a[8];
-                        Packet<__nv_bfloat16>::load(p.upd + (int64_t)r * K + j, a);
+            for (int r0 = 0; r0 < ROWS; r0 += 8) {
+                float c[8][4];
+                load_rows(r0, j, c);
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] += a[e];
-                    }
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * nw[e];
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+                for (int r = 0; r < 8; ++r) {
+                    const float inv = inv_s[r0 + r];
+                    float v[4] = {c[r][0] * inv * nw.x, c[r][1] * inv * nw.y, c[r][2] * inv * nw.z, c[r][3] * inv * nw.w};
+                    if (r0 + r >= p.M) v[0] = v[1] = v[2] = v[3] = 0.0f;
+                    *reinterpret_cast<uint2*>(xs + (size_t)(r0 + r) * x_pitch + j) = pack4(v);
                 }
-                Packet<__nv_bfloat16>::store(xs + (size_t)r * x_pitch + j, v);
             }
         }
         __syncthreads();
     }
 
     int cs = 0;        // consumer ring slot
-    int consumed = 0;  // the first STAGES - 1 slots were filled before pdl_wait(), without their activations
     for (int ti = 0; ti < my_tiles; ++ti) {
         for (int j = 0; j < bpw; ++j) {
             issue(true);
@@ -227,8 +263,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
                         xa = *reinterpret_cast<const uint4*>(xs + (size_t)row * x_pitch + b * 32 + 8 * t);
                     else if (row >= p.M)
                         xa = make_uint4(0, 0, 0, 0);
-                    else if (consumed < STAGES - 1)
-                        xa = *reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + b * 32 + 8 * t);
                     else
                         xa = *reinterpret_cast<const uint4*>(st + 1024 * NH + mt * 512);
 #pragma unroll
@@ -239,7 +273,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
                 }
             }
             if (++cs == STAGES) cs = 0;
-            ++consumed;
         }
         // end of a tile: sum the warps in a fixed order: partial[warp][feature 0..31][batch row 0..ROWS-1]
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
@@ -291,14 +324,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     }
 }
 
-template <int MT, int PRO, int EPI, int NH>
+template <int MT, int PRO, int EPI, int NH, bool DEEP>
 int launch_tiles(const LinearParams& p, cudaStream_t stream) {
     constexpr int ROWS = 8 * MT;
     constexpr int TF = 16 * NH;
     constexpr int STAGE_BYTES = 1024 * NH + (PRO == PRO_NONE ? 512 * MT : 0);
-    size_t smem = (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)kWarps * ring_depth(NH) * STAGE_BYTES;
+    size_t smem = (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)kWarps * ring_depth(DEEP) * STAGE_BYTES;
     if (PRO != PRO_NONE) smem += (size_t)ROWS * (p.K + 32) * 2;
-    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH>;
+    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, DEEP>;
     if (smem > 48 * 1024) {
         if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -314,8 +347,15 @@ int launch_tiles(const LinearParams& p, cudaStream_t stream) {
 template <int MT, int PRO, int EPI>
 int launch(const LinearParams& p, cudaStream_t stream) {
     // 32-feature tiles when there are enough of them to give every SM work, else 16-feature tiles
-    if (p.N % 32 == 0 && p.N / 32 >= 148) return launch_tiles<MT, PRO, EPI, 2>(p, stream);
-    return launch_tiles<MT, PRO, EPI, 1>(p, stream);
+    if (p.N % 32 == 0 && p.N / 32 >= 148) return launch_tiles<MT, PRO, EPI, 2, false>(p, stream);
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
+    }
+    if (p.N / 16 <= sms) return launch_tiles<MT, PRO, EPI, 1, true>(p, stream);   // one CTA per SM at most
+    return launch_tiles<MT, PRO, EPI, 1, false>(p, stream);
 }
 
 template <int MT>

@@ -326,6 +326,50 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_s
     return out
 
 
+def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,
+                          seq_begin: torch.Tensor, block_table: torch.Tensor, num_seqs: int, num_heads: int,
+                          num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                          inv_freq: Optional[torch.Tensor], write_kv: bool, splits: int) -> torch.Tensor:
+    """Decode attention with the rotation and the cache write folded in (bfloat16, one row per sequence).
+
+    ``qkv`` holds the unrotated packed projections ``[q heads | k heads | v heads]`` of the ``num_seqs`` rows.
+    Queries and new keys are rotated inside the kernel (``inv_freq`` None: no rotation); with ``write_kv`` the new
+    key and value go into the cache page of their position."""
+    _cuda(qkv, out, cache, row_start, seq_begin, block_table, inv_freq)
+    _need(qkv.dtype == out.dtype == cache.dtype == torch.bfloat16, "attention_decode_rope takes bfloat16")
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[0] == num_seqs
+          and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qkv layout")
+    _need(out.stride(1) == 1 and tuple(out.shape) == (num_seqs, num_heads * head_dim), "out layout")
+    _need(row_start.dtype == torch.int32 and seq_begin.dtype == torch.int32 and block_table.dtype == torch.int32,
+          "row_start, seq_begin and block_table must be int32")
+    _need(row_start.numel() >= num_seqs + 1 and seq_begin.numel() >= num_seqs, "sequence metadata too short")
+    _need(block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[0] >= num_seqs, "block table")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache layout")
+    _need(num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16, "at most 16 query heads per kv head")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous() and inv_freq.numel() == head_dim // 2,
+              "inv_freq must be float32 [head_dim / 2]")
+    lib = load_library("attention_mma")
+    padded = lib.tb_attention_mma_padded_dim(_i32(head_dim))
+    if padded < 0:
+        raise KernelError(f"attention_decode_rope: head_dim {head_dim} is not a multiple of 16 up to 256")
+    part_o = part_ml = counters = None
+    capacity = 0
+    if splits > 8:
+        counters = _counters(qkv.device, num_seqs * num_kv_heads)
+        part_o = _scratch(qkv.device, "part_o", splits * num_seqs * num_heads * padded)
+        part_ml = _scratch(qkv.device, "part_ml", splits * num_seqs * num_heads * 2)
+        capacity = part_o.numel()
+    _check(lib.tb_attention_decode_rope(_ptr(qkv), _i64(qkv.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                        _ptr(row_start), _ptr(seq_begin), _ptr(block_table),
+                                        _i32(block_table.stride(0)), _i32(num_seqs), _i32(num_heads),
+                                        _i32(num_kv_heads), _i32(head_dim), _i32(page_size), _i32(window),
+                                        _f32(scale), _ptr(inv_freq), _i32(1 if write_kv else 0), _i32(splits),
+                                        _ptr(part_o), _ptr(part_ml), _i64(capacity), _ptr(counters), _stream()),
+           "attention_decode_rope")
+    return out
+
+
 PRO_NONE, PRO_NORM, PRO_ADD_NORM = 0, 1, 2
 EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
 

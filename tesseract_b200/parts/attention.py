@@ -89,8 +89,19 @@ class Attention(Mixer):
         if qkv is None:
             qkv = self.qkv_proj.forward(x)
         inv_freq = self.position.rotary_inv_freq
+        rows = qkv.shape[0]
+        attended = torch.empty((rows, self.q_width), dtype=qkv.dtype, device=qkv.device)
+        fold = self.num_heads // self.num_kv_heads
+        if (not self.runtime.is_float32 and fold <= 16 and ctx.max_new == 1 and ctx.num_seqs == rows
+                and (inv_freq is not None or self.position.kind == "none")):
+            # a pure decode step: rotation, cache write and attention in one kernel
+            splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context, self.head_dim)
+            kernels.attention_decode_rope(qkv, attended, cache.storage, ctx.row_start, ctx.seq_begin,
+                                          group.block_table, ctx.num_seqs, self.num_heads, self.num_kv_heads,
+                                          self.head_dim, cache.page_size, self.window, self.scale, inv_freq,
+                                          cache.writes, splits)
+            return self.o_proj.forward(attended)
         if inv_freq is None and self.position.kind != "none":
-            rows = qkv.shape[0]
             q_view = qkv[:, :self.q_width].view(rows, self.num_heads, self.head_dim)
             k_view = qkv[:, self.q_width:self.q_width + self.kv_width].view(rows, self.num_kv_heads, self.head_dim)
             self.position.apply(q_view, k_view, ctx.positions)
@@ -98,7 +109,6 @@ class Attention(Mixer):
                               self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
                               write_kv=cache.writes)
         q = qkv[:, :self.q_width]
-        attended = torch.empty((qkv.shape[0], self.q_width), dtype=qkv.dtype, device=qkv.device)
         self._attend(q, attended, cache, ctx, group)
         return self.o_proj.forward(attended)
 

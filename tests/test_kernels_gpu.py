@@ -328,6 +328,54 @@ def run_attention_mma(case, nh, nkv, d, page_size, window, scale, splits):
     return out
 
 
+@pytest.mark.parametrize("lengths, nh, nkv, d, page_size, window, splits, scaling, write_kv", [
+    ([1, 16, 17, 333], 6, 3, 48, 16, 0, 1, None, True),               # the new key first, last and alone in a page
+    ([700, 64, 65, 1, 33], 32, 8, 64, 16, 0, 4, "llama3", True),      # splits as a cluster
+    ([2100, 500], 8, 2, 128, 32, 0, 12, "llama3", True),              # splits through scratch memory
+    ([150, 64, 10], 4, 2, 32, 16, 24, 2, None, True),                 # sliding window
+    ([90, 41], 5, 5, 256, 16, 0, 2, None, True),                      # the widest head, no grouping
+    ([129, 40], 4, 1, 16, 16, 0, 3, "none", True),                    # no rotation at all
+    ([129, 40], 8, 2, 64, 16, 0, 3, "llama3", False),                 # reads a cache that another layer wrote
+])
+def test_attention_decode_rope_equals_rope_then_attention(lengths, nh, nkv, d, page_size, window, splits, scaling,
+                                                          write_kv):
+    """The fused decode kernel against the two kernels it replaces: same output bits, same cache bits."""
+    from tesseract_b200 import kernels
+    from tesseract_b200.parts.rotary import rotary_inverse_frequencies
+
+    case = paged_case(torch.bfloat16, lengths, [1] * len(lengths), nh, nkv, d, page_size, seed=21)
+    n = len(lengths)
+    inv_freq = None
+    if scaling != "none":
+        rope = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                    original_max_position_embeddings=64) if scaling else None
+        inv_freq = dev(torch.from_numpy(rotary_inverse_frequencies(d, 500000.0 if scaling else 10000.0, rope)))
+    torch.manual_seed(3)
+    qkv = dev(torch.randn(n, (nh + 2 * nkv) * d).to(torch.bfloat16))
+    row_start = dev(torch.arange(n + 1, dtype=torch.int32))
+    seq_begin = dev(torch.tensor([length - 1 for length in lengths], dtype=torch.int32))
+    table, positions, seq_of_row = dev(case["table"]), dev(case["positions"]), dev(case["seq_of_row"])
+    scale = 1.0 / math.sqrt(d)
+
+    cache_a, qkv_a = dev(case["cache"]).clone(), qkv.clone()
+    kernels.rope_kv_write(qkv_a, positions, seq_of_row, table, inv_freq, cache_a, nh, nkv, d, page_size,
+                          write_kv=write_kv)
+    out_a = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.attention_mma(qkv_a[:, :nh * d], out_a, cache_a, row_start, seq_begin, table, n, 1, nh, nkv, d, page_size,
+                          window, scale, False, True, splits)
+
+    cache_b = dev(case["cache"]).clone()
+    out_b = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.attention_decode_rope(qkv, out_b, cache_b, row_start, seq_begin, table, n, nh, nkv, d, page_size, window,
+                                  scale, inv_freq, write_kv, splits)
+    torch.cuda.synchronize()
+    assert not torch.isnan(out_b.float()).any()
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(cache_a, cache_b)
+    if not write_kv:
+        assert torch.equal(cache_b, dev(case["cache"]))                # a reader leaves the cache alone
+
+
 @pytest.mark.parametrize("lengths, new, nh, nkv, d, page_size, window, splits", [
     ([1], [1], 1, 1, 16, 16, 0, 1),
     ([17, 16, 15, 33], [1, 1, 1, 1], 6, 3, 48, 16, 0, 1),             # decode rows at pages' edges
