@@ -23,11 +23,8 @@ namespace {
 
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-constexpr int kMaxCtas = 296;  // two resident CTAs per SM
-// Ring depth per warp: three stages where two CTAs share an SM (deeper rings were measured and bought nothing
-// there), six where a product has so few tiles that an SM holds one CTA, which then has to cover the memory
-// latency alone.
-__host__ __device__ constexpr int ring_depth(bool deep) { return deep ? 6 : 3; }
+// One CTA per SM (the prologue, which every CTA repeats, then costs each SM once) with rings deep enough for it
+// to cover the memory latency alone: five stages of 32-feature tiles or six of 16-feature tiles per warp.
 
 enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2 };
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -53,13 +50,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-    uint4 v;  // weights are read once: do not keep them in L1
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
@@ -69,8 +59,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // MT: number of 8-row batch tiles (1 or 2).
 // NH: 16-feature halves per tile (2 where there are tiles enough for every SM, else 1).
-template <int MT, int PRO, int EPI, int NH, bool DEEP>
-__global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const LinearParams p) {
+template <int MT, int PRO, int EPI, int NH, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -90,7 +80,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     constexpr int X_BYTES = (PRO == PRO_NONE) ? 512 * MT : 0;   // activations ride along when they come from memory
     constexpr int TF = 16 * NH;                                  // features per tile
     constexpr int STAGE_BYTES = 1024 * NH + X_BYTES;
-    constexpr int STAGES = ring_depth(DEEP);
     const int blocks = K / 32;
     const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
     const int num_tiles = p.N / TF;
@@ -142,6 +131,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
     pdl_trigger();
+    float4 nw_first = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // the norm's weights are weights too: fetch them early
+    if (PRO != PRO_NONE && (int)threadIdx.x * 4 < K) nw_first = *reinterpret_cast<const float4*>(p.norm_w + threadIdx.x * 4);
     int early[STAGES - 1];
 #pragma unroll
     for (int q = 0; q < STAGES - 1; ++q) early[q] = issue(false);   // weights do not depend on the kernel before
@@ -198,6 +189,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
         float ss[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) ss[r] = 0.0f;
+        // With eight rows and K up to four elements per thread the sums stay in registers between the two
+        // passes and the rows are read once; otherwise the second pass reads them again.
+        const bool keep = MT == 1 && K <= kThreads * 4;
+        float kept[8][4];
         for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
@@ -208,7 +203,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
                     if (PRO == PRO_ADD_NORM && blockIdx.x == 0 && r0 + r < p.M)
                         *reinterpret_cast<uint2*>(p.res_out + (int64_t)(r0 + r) * K + j) = pack4(c[r]);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) ss[r0 + r] += c[r][e] * c[r][e];
+                    for (int e = 0; e < 4; ++e) {
+                        ss[r0 + r] += c[r][e] * c[r][e];
+                        if (MT == 1) kept[r][e] = c[r][e];
+                    }
                 }
             }
         }
@@ -227,15 +225,21 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
         }
         __syncthreads();
         for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
-            const float4 nw = *reinterpret_cast<const float4*>(p.norm_w + j);
+            const float4 nw = j == (int)threadIdx.x * 4 ? nw_first : *reinterpret_cast<const float4*>(p.norm_w + j);
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
                 float c[8][4];
-                load_rows(r0, j, c);
+                if (!keep) load_rows(r0, j, c);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     const float inv = inv_s[r0 + r];
-                    float v[4] = {c[r][0] * inv * nw.x, c[r][1] * inv * nw.y, c[r][2] * inv * nw.z, c[r][3] * inv * nw.w};
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] = (MT == 1 && keep) ? kept[r][e] : c[r][e];
+                    v[0] *= inv * nw.x;
+                    v[1] *= inv * nw.y;
+                    v[2] *= inv * nw.z;
+                    v[3] *= inv * nw.w;
                     if (r0 + r >= p.M) v[0] = v[1] = v[2] = v[3] = 0.0f;
                     *reinterpret_cast<uint2*>(xs + (size_t)(r0 + r) * x_pitch + j) = pack4(v);
                 }
@@ -324,21 +328,44 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Linear
     }
 }
 
-template <int MT, int PRO, int EPI, int NH, bool DEEP>
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
+    }
+    return sms;
+}
+
+// 32-feature tiles where that still gives every SM a tile, else 16-feature tiles.
+bool wide_tiles(int N) { return N % 32 == 0 && N / 32 >= sm_count(); }
+// ring depth: deep for up to eight rows; sixteen rows need the room for their activations and partial sums
+constexpr int stages_for(int nh, int rows8) { return rows8 > 1 ? 3 : nh == 2 ? 5 : 6; }
+
+size_t smem_bytes(int rows8, bool prologue, int nh, int K) {
+    const int rows = 8 * rows8, tf = 16 * nh;
+    const size_t stage = 1024 * nh + (prologue ? 0 : 512 * rows8);
+    size_t smem = (size_t)kWarps * tf * rows * sizeof(float) + (size_t)kWarps * stages_for(nh, rows8) * stage;
+    if (prologue) smem += (size_t)rows * (K + 32) * 2;
+    return smem;
+}
+
+constexpr size_t kMaxSmem = 220 * 1024;
+
+template <int MT, int PRO, int EPI, int NH>
 int launch_tiles(const LinearParams& p, cudaStream_t stream) {
-    constexpr int ROWS = 8 * MT;
     constexpr int TF = 16 * NH;
-    constexpr int STAGE_BYTES = 1024 * NH + (PRO == PRO_NONE ? 512 * MT : 0);
-    size_t smem = (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)kWarps * ring_depth(DEEP) * STAGE_BYTES;
-    if (PRO != PRO_NONE) smem += (size_t)ROWS * (p.K + 32) * 2;
-    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, DEEP>;
+    const size_t smem = smem_bytes(MT, PRO != PRO_NONE, NH, p.K);
+    if (smem > kMaxSmem) return TB_ERR_BAD_SIZE;
+    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, stages_for(NH, MT)>;
     if (smem > 48 * 1024) {
-        if (smem > 220 * 1024) return TB_ERR_BAD_SIZE;
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
     const int tiles = p.N / TF;
-    const int per_cta = (tiles + kMaxCtas - 1) / kMaxCtas;           // tiles per CTA, evenly spread
+    const int max_ctas = sm_count();                                 // one CTA per SM at most
+    const int per_cta = (tiles + max_ctas - 1) / max_ctas;           // tiles per CTA, evenly spread
     const int grid = (tiles + per_cta - 1) / per_cta;
     cudaError_t err = tb_launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, p);
     return err == cudaSuccess ? tb_launch_status() : (int)err;
@@ -346,16 +373,8 @@ int launch_tiles(const LinearParams& p, cudaStream_t stream) {
 
 template <int MT, int PRO, int EPI>
 int launch(const LinearParams& p, cudaStream_t stream) {
-    // 32-feature tiles when there are enough of them to give every SM work, else 16-feature tiles
-    if (p.N % 32 == 0 && p.N / 32 >= 148) return launch_tiles<MT, PRO, EPI, 2, false>(p, stream);
-    static int sms = 0;
-    if (sms == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
-    }
-    if (p.N / 16 <= sms) return launch_tiles<MT, PRO, EPI, 1, true>(p, stream);   // one CTA per SM at most
-    return launch_tiles<MT, PRO, EPI, 1, false>(p, stream);
+    if (wide_tiles(p.N)) return launch_tiles<MT, PRO, EPI, 2>(p, stream);
+    return launch_tiles<MT, PRO, EPI, 1>(p, stream);
 }
 
 template <int MT>
@@ -380,8 +399,7 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
 // 1 if the sizes are ones this kernel takes, else 0 (the caller then uses the general path).
 TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
     if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < 32 || K % 32 != 0) return 0;
-    if (prologue != PRO_NONE && (size_t)(M <= 8 ? 8 : 16) * (K + 32) * 2 > 96 * 1024) return 0;
-    return 1;
+    return smem_bytes(M <= 8 ? 1 : 2, prologue != PRO_NONE, wide_tiles(N) ? 2 : 1, K) <= kMaxSmem;
 }
 
 // x: PRO_NONE only.  res/upd/norm_w/res_out: see LinearParams.  out_stride in elements of the output type.
