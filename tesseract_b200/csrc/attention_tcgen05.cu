@@ -133,11 +133,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Blackwell's packed 32-bit pairs (one instruction for two lanes of a 64-bit register pair) and three-input
+// maximum: the softmax loop is bound by the number of instructions it issues per score.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {   // each lane: fmaf(a, b, c)
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+
 __global__ void __launch_bounds__(kThreads, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
-    // barriers: kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full, s_free
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    // barriers: k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full, p_ready, o_full, s_free.
+    // Keys and values have rings of their own: a key block's stage is free again as soon as its scores are
+    // computed, a whole block before its value stage is.
+    __shared__ __align__(8) uint64_t bars[4 * STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -159,8 +188,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const uint32_t q_tile = smem_u32(smem);
     const uint32_t p_tile = q_tile + kTileBytes;                // two 16 KiB halves (keys 0..63 | 64..127)
     const uint32_t kv_tiles = p_tile + 2 * kTileBytes;          // [stage][K | V]
-    const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[STAGES]);
-    const uint32_t s_full = smem_u32(&bars[2 * STAGES]), p_ready = s_full + 8, o_full = s_full + 16;
+    const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[STAGES]);
+    const uint32_t v_full = smem_u32(&bars[2 * STAGES]), v_empty = smem_u32(&bars[3 * STAGES]);
+    const uint32_t s_full = smem_u32(&bars[4 * STAGES]), p_ready = s_full + 8, o_full = s_full + 16;
     const uint32_t s_free = s_full + 24;
 
     const int last_row = min(n_rows, r0 + BM) - 1;
@@ -172,8 +202,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(kv_full + 8 * s, 1);
-            mbar_init(kv_empty + 8 * s, 1);
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
         }
         mbar_init(s_full, 1);
         mbar_init(p_ready, BM);
@@ -209,32 +241,40 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
 
     if (warp == 5) {
         // ------------------------------------------------------------ TMA producer: K and V blocks, page by page
-        if (lane == 0) {
-            const int rows_per_copy = min(p.page_size, BN);          // keys one bulk copy brings
-            const int copies = BN / rows_per_copy;
-            const int last_page = key_hi >> p.page_shift;            // pages past it hold nothing of this sequence
-            bool ok = true;
-            for (int it = 0; it < n_blocks; ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(kv_empty + 8 * s, ((it / STAGES) & 1) ^ 1, &abort_flag)) { ok = false; break; }
-                const uint32_t dst = kv_tiles + s * 2 * kTileBytes;
-                const int key0 = (kb_first + it) * BN;
-                mbar_expect_tx(kv_full + 8 * s, 2 * kTileBytes);
-                for (int c = 0; c < copies; ++c) {
-                    const int key = key0 + c * rows_per_copy;
-                    const int logical = key >> p.page_shift;
-                    // keys past the sequence come from the scratch page: finite values that the mask removes
-                    const int page = logical <= last_page ? table[logical] : 0;
-                    const int in_page = key & (p.page_size - 1);
-                    const uint32_t at = dst + (uint32_t)(c * rows_per_copy) * 128;
-                    tma_load_kv(at, &cache_map, kv_full + 8 * s, in_page, kv_head, 0, page);
-                    tma_load_kv(at + kTileBytes, &cache_map, kv_full + 8 * s, in_page, kv_head, 1, page);
+        // Lane c brings page c of a block (its table entry, one copy); lane 0 waits for the stage and announces
+        // the bytes.  Order: K_0 V_0 K_1 V_1 ... (K_{j+STAGES} becomes possible before V_{j+STAGES} does).
+        const int rows_per_copy = min(p.page_size, BN);          // keys one bulk copy brings
+        const int copies = BN / rows_per_copy;                   // at most 16 (pages of 8 keys or more)
+        const int last_page = key_hi >> p.page_shift;            // pages past it hold nothing of this sequence
+        bool ok = true;
+        for (int it = 0; it < n_blocks && ok; ++it) {
+            const int s = it % STAGES;
+            const int key0 = (kb_first + it) * BN;
+            int page = 0, in_page = 0;
+            if (lane < copies) {
+                const int key = key0 + lane * rows_per_copy;
+                const int logical = key >> p.page_shift;
+                // keys past the sequence come from the scratch page: finite values that the mask removes
+                page = logical <= last_page ? table[logical] : 0;
+                in_page = key & (p.page_size - 1);
+            }
+            const uint32_t dst = kv_tiles + s * 2 * kTileBytes + (uint32_t)(lane * rows_per_copy) * 128;
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                const uint32_t full = (which ? v_full : k_full) + 8 * s, empty = (which ? v_empty : k_empty) + 8 * s;
+                int go = 1;
+                if (lane == 0) {
+                    go = mbar_wait(empty, ((it / STAGES) & 1) ^ 1, &abort_flag) ? 1 : 0;
+                    if (go) mbar_expect_tx(full, kTileBytes);
                 }
+                go = __shfl_sync(0xffffffffu, go, 0);            // also orders the announcement before the copies
+                if (!go) { ok = false; break; }
+                if (lane < copies) tma_load_kv(dst + which * kTileBytes, &cache_map, full, in_page, kv_head, which, page);
             }
-            if (!ok) {
-                abort_flag = 1;
-                atomicExch(p.error, 10);
-            }
+        }
+        if (!ok && lane == 0) {
+            abort_flag = 1;
+            atomicExch(p.error, 10);
         }
     } else if (warp == 4) {
         // ------------------------------------------------------------ the issuer: one lane feeds the tensor core
@@ -243,13 +283,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             constexpr uint32_t idesc_pv = idesc_bf16(BM, D, 1);
             auto issue_qk = [&](int j) {
                 const int s = j % STAGES;
-                if (!mbar_wait(kv_full + 8 * s, (j / STAGES) & 1, &abort_flag)) return false;
+                if (!mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t k_tile = kv_tiles + s * 2 * kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
                     umma(tmem_s, desc_sw128(q_tile + kk * 32, 1), desc_sw128(k_tile + kk * 32, 1), idesc_qk, kk != 0);
                 umma_commit(s_full);
+                umma_commit(k_empty + 8 * s);     // the key stage may be refilled once these products are done
                 return true;
             };
             bool ok = issue_qk(0);
@@ -262,6 +303,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 }
                 // P_j is in shared memory (and O has been rescaled if the maximum jumped): O += P_j V_j
                 if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kTileBytes + kTileBytes;
 #pragma unroll
@@ -269,7 +311,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                     umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
                          desc_sw128(v_tile + kk * 2048, 1024 >> 4), idesc_pv, (j | kk) != 0);
                 umma_commit(o_full);
-                umma_commit(kv_empty + 8 * (j % STAGES));
+                umma_commit(v_empty + 8 * (j % STAGES));
             }
             if (!ok) {
                 abort_flag = 1;
@@ -307,7 +349,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             auto reduce_max = [&](const uint32_t (&chunk)[32], int c) {
                 if (full) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(chunk[i]));
+                    for (int i = 0; i < 32; i += 2)
+                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
@@ -351,16 +394,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 }
             }
             // Pass 2: probabilities, their 32-bit sum (four partial sums), and the bfloat16 P tile.
-            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint64_t ls[4] = {0, 0, 0, 0};   // four pairs of partial sums (0 is the bit pattern of (0.0f, 0.0f))
             auto emit = [&](const uint32_t (&chunk)[32], int c) {
                 uint32_t packed[16];
                 const float neg_m = -m;
                 if (full) {
+                    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(neg_m, neg_m);
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(chunk[i]), p.scale_log2, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(chunk[i + 1]), p.scale_log2, neg_m));
-                        ls[(i >> 1) & 3] += p0 + p1;
+                        float t0, t1;
+                        unpack2(fma2(pack2(__uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1])), scale2, neg_m2),
+                                t0, t1);
+                        const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                        ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
                         packed[i >> 1] = pack_bf16(p0, p1);
                     }
                 } else {
@@ -372,7 +418,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                             const bool valid = c * 32 + i + e >= lo_col && c * 32 + i + e <= hi_col;
                             pr[e] = valid ? fast_exp2(fmaf(__uint_as_float(chunk[i + e]), p.scale_log2, neg_m)) : 0.0f;
                         }
-                        ls[(i >> 1) & 3] += pr[0] + pr[1];
+                        ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(pr[0], pr[1]));
                         packed[i >> 1] = pack_bf16(pr[0], pr[1]);
                     }
                 }
@@ -396,7 +442,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             tc_fence_before();
             mbar_arrive(s_free);                       // S has been read: the issuer may start the next block's scores
             emit(cb, 3);
-            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            {
+                float lo, hi;
+                unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), lo, hi);
+                l += lo + hi;
+            }
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(p_ready);

@@ -115,7 +115,7 @@ int launch(void* qkv, int64_t qkv_stride, const int* positions, const int* seq_o
                      (((uintptr_t)qkv | (uintptr_t)cache) % 16 == 0);
     const int work = (num_heads + num_kv_heads) * (vec ? half / Packet<T>::N : half);
     int threads = 32;
-    while (threads < 512 && threads < work) threads <<= 1;
+    while (threads < 128 && threads < work) threads <<= 1;   // small blocks: many rows in flight per SM
     const size_t smem = (size_t)head_dim * sizeof(float);
     cudaError_t err;
     if (vec)
