@@ -457,6 +457,33 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     return out
 
 
+def skinny_gemm_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    """Whether the weight-streaming tcgen05 product takes these sizes (at most 128 rows)."""
+    if epilogue not in (EPI_BF16, EPI_SWIGLU):
+        return False
+    return bool(load_library("skinny_gemm").tb_skinny_gemm_supported(_i32(rows), _i32(out_features),
+                                                                    _i32(in_features), _i32(epilogue)))
+
+
+def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16) -> torch.Tensor:
+    """``out = x @ weight^T`` for at most 128 rows on the tcgen05 tensor cores, the weights streamed once
+    (bfloat16 in and out, 32-bit accumulation, K split over a thread-block cluster for narrow outputs).
+
+    ``EPI_BF16`` stores ``[M, N]``; ``EPI_SWIGLU`` takes a weight whose rows interleave eight gate rows and their
+    eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``."""
+    _cuda(x, weight, out)
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(x.dtype == weight.dtype == out.dtype == torch.bfloat16, "skinny_gemm takes bfloat16")
+    _need(weight.shape[1] == k and x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1, "gemm layout")
+    _need(out.shape == (m, n // 2 if epilogue == EPI_SWIGLU else n), "skinny_gemm out shape")
+    lib = load_library("skinny_gemm")
+    _check(lib.tb_skinny_gemm(_ptr(x), _i64(x.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
+                              _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
+                              _ptr(_error_word(x.device)), _stream()), "skinny_gemm")
+    return out
+
+
 def tcgen05_error(device=None) -> int:
     """Non-zero if a bounded wait inside a tcgen05 kernel ran out since the last call (synchronises)."""
     total = 0
