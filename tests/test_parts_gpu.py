@@ -272,6 +272,102 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     torch.testing.assert_close(again[0], plain["q"][19], rtol=2e-5, atol=2e-5)
 
 
+def windowed_spec(hidden=32, vocab=61, window=20):
+    """Two attention layers with different cache needs: layer 0 sees all keys, layer 1 the last `window` only."""
+    from tesseract_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    def norm(name):
+        return PartSpec.make("rms_norm", {"size": hidden, "eps": 1e-5}, {"weight": name})
+
+    def layer(i, win):
+        mixer = PartSpec.make("attention", {"hidden_size": hidden, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                            "window": win, "scale": None},
+                              {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"},
+                              {"position": PartSpec.make("rotary", {"head_dim": 16, "theta": 1000.0, "scaling": None})})
+        ffn = PartSpec.make("swiglu", {"hidden_size": hidden, "intermediate_size": 48},
+                            {"gate": f"l{i}.g", "up": f"l{i}.u", "down": f"l{i}.d"})
+        return LayerSpec.make("pre_norm", mixer, ffn, {"input": norm(f"l{i}.n1"), "post_mixer": norm(f"l{i}.n2")})
+
+    sizes = {"vocab_size": vocab, "hidden_size": hidden}
+    return ModelSpec(architecture="WindowedForTests", hidden_size=hidden, vocab_size=vocab, max_positions=512,
+                     embedding=PartSpec.make("token_embedding", sizes, {"table": "emb"}),
+                     layers=(layer(0, None), layer(1, window)), run_order=(RunEntry(0), RunEntry(1)),
+                     final_norm=norm("fn"), head=PartSpec.make("lm_head", sizes, {"weight": "head"}))
+
+
+def windowed_plain(tensors, tokens, window):
+    w = {k: v.double() for k, v in tensors.items()}
+    T = len(tokens)
+    cos, sin = llama.rope_tables(range(T), llama.rope_inverse_frequencies(16, 1000.0, None))
+    h = llama.embed(tokens, w["emb"])
+    for i, win in ((0, None), (1, window)):
+        x = llama.rms_norm(h, w[f"l{i}.n1"], 1e-5)
+        q = llama.rotate_half((x @ w[f"l{i}.q"].T).view(T, 4, 16), cos, sin)
+        k = llama.rotate_half((x @ w[f"l{i}.k"].T).view(T, 2, 16), cos, sin)
+        v = (x @ w[f"l{i}.v"].T).view(T, 2, 16)
+        h = h + llama.attention(q, k, v, 0.25, win).reshape(T, 64) @ w[f"l{i}.o"].T
+        m = llama.rms_norm(h, w[f"l{i}.n2"], 1e-5)
+        h = h + llama.swiglu(m, w[f"l{i}.g"], w[f"l{i}.u"], w[f"l{i}.d"])
+    return llama.rms_norm(h, w["fn"], 1e-5) @ w["head"].T
+
+
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 3e-5), (torch.bfloat16, 3e-2)])
+def test_layers_with_and_without_a_window_keep_pages_of_their_own(dtype, tol):
+    """One model, two cache groups: the windowed layer's pages go back as the window passes them and are used
+    again, the other layer keeps every page; portions and decoded tokens of three requests share the steps."""
+    from tesseract_b200.engine import StepEntry, make_stepper
+    from tesseract_b200.models import DecoderModel, tensor_roles
+
+    window = 20
+    spec = windowed_spec(window=window)
+    g = torch.Generator().manual_seed(4)
+    tensors = {name: cls.random_tensor(part, role, tuple(want.shape), g) * (4 if role in "qk" else 1)
+               for cls, part, role, name, want in tensor_roles(spec)}
+    model = DecoderModel(spec, {k: v.to(dtype) if v.dtype != torch.float32 or k.endswith((".q", ".k", ".v", ".o", ".g",
+                                ".u", ".d", "emb", "head")) else v for k, v in tensors.items()}, runtime(dtype))
+    # 11 pages of 16 tokens per group: two live requests fill the full layer's pool, the third uses pages again
+    stepper = make_stepper(model, capacity_tokens=176, max_requests=3, max_step_tokens=32)
+    cache = stepper.cache
+    assert len(cache.groups) == 2
+    windowed = [i for i, grp in enumerate(cache.groups) if grp.need.window][0]
+    rng = np.random.default_rng(7)
+    seqs = {"a": rng.integers(0, 61, 90).tolist(), "b": rng.integers(0, 61, 70).tolist(),
+            "c": rng.integers(0, 61, 78).tolist()}
+    rounded = {k: v.to(dtype).float() for k, v in tensors.items()}
+    plain = {r: windowed_plain(rounded, t, window) for r, t in seqs.items()}
+    got = {r: [] for r in seqs}
+    at = {r: 0 for r in seqs}
+    sizes = [16, 7, 2, 5, 1, 1, 23, 1, 3]
+    live, waiting, step = [], ["a", "b", "c"], 0
+    peak_windowed = 0
+    while live or waiting:
+        while waiting and len(live) < 2 and cache.admit(waiting[0], None):
+            live.append(waiting.pop(0))
+        entries = []
+        for j, r in enumerate(live):
+            n = min(sizes[(step + 3 * j) % len(sizes)], len(seqs[r]) - at[r])
+            entries.append(StepEntry(r, seqs[r][at[r]:at[r] + n], list(range(n))))
+            at[r] += n
+        logits = stepper.step(entries).cpu().double()
+        k = 0
+        for e in entries:
+            got[e.request].append(logits[k:k + len(e.tokens)])
+            k += len(e.tokens)
+        cache.check()
+        for r in live:
+            held = len(cache.pages_of(r, windowed))
+            peak_windowed = max(peak_windowed, held)
+            assert len(cache.pages_of(r, 1 - windowed)) == -(-at[r] // 16)          # the full layer keeps every page
+        for r in [r for r in live if at[r] == len(seqs[r])]:
+            cache.release(r)
+            live.remove(r)
+        step += 1
+    assert peak_windowed <= -(-(window - 1 + 32) // 16) + 1                          # the window bounds what is held
+    assert cache.pages_reused > 0 and cache.used_pages() == 0
+    for r in seqs:
+        torch.testing.assert_close(torch.cat(got[r]), plain[r], rtol=tol, atol=tol)
+
+
 def test_attention_part_with_the_tcgen05_prompt_kernel():
     """The same mixer with prompt portions on the tcgen05 kernel: portions, decode rows beside them, page reuse."""
     from tesseract_b200 import kernels
