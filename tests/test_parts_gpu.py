@@ -272,6 +272,131 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     torch.testing.assert_close(again[0], plain["q"][19], rtol=2e-5, atol=2e-5)
 
 
+def register_toy_routing_and_position():
+    """A feed-forward that routes each row to one of its experts, and a position encoding that rotates adjacent
+    pairs: two more kinds that the framework has never seen (written with torch operations; they are toys)."""
+    from tesseract_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding
+    from tesseract_b200.weights.loader import ExpectedTensor
+
+    if "toy_top1" in FEED_FORWARDS.kinds():
+        return
+
+    @FEED_FORWARDS.register("toy_top1")
+    class ToyTop1(FeedForward):
+        """y = relu(x W1[e]^T) W2[e]^T with e = argmax(x R^T) (router logits in 32-bit, lowest index on ties)."""
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.router = tensors["router"].to(device=runtime.device, dtype=torch.float32)
+            self.w1 = tensors["w1"].to(device=runtime.device, dtype=torch.float32)
+            self.w2 = tensors["w2"].to(device=runtime.device, dtype=torch.float32)
+
+        @classmethod
+        def expected_tensors(cls, spec):
+            p, w = spec.params, spec.weights
+            e, h, i = int(p["experts"]), int(p["hidden_size"]), int(p["intermediate_size"])
+            return {w["router"]: ExpectedTensor((e, h)), w["w1"]: ExpectedTensor((e, i, h)),
+                    w["w2"]: ExpectedTensor((e, h, i))}
+
+        @classmethod
+        def random_tensor(cls, spec, role, shape, generator):
+            return torch.randn(shape, generator=generator) * (1.0 if role == "router" else 0.2)
+
+        def forward(self, x, ctx):
+            rows = x.float()
+            expert = (rows @ self.router.T).argmax(dim=1)
+            hidden = torch.relu(torch.einsum("th,tih->ti", rows, self.w1[expert]))
+            return torch.einsum("ti,thi->th", hidden, self.w2[expert]).to(x.dtype)
+
+    @POSITION_ENCODINGS.register("toy_adjacent_pairs")
+    class ToyAdjacentPairs(PositionEncoding):
+        """(x[2i], x[2i+1]) rotated by position * theta^(-2i/d): no inverse-frequency table for the kernels, so the
+        mixer calls ``apply`` on its query and key views."""
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            d = int(spec.params["head_dim"])
+            self.freq = torch.tensor([float(spec.params["theta"]) ** (-2.0 * i / d) for i in range(d // 2)],
+                                     dtype=torch.float32, device=runtime.device)
+
+        def apply(self, q, k, positions):
+            angle = positions.to(torch.float32)[:, None] * self.freq[None, :]
+            cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            for x in (q, k):
+                even, odd = x[..., 0::2].float(), x[..., 1::2].float()
+                new_even, new_odd = even * cos - odd * sin, odd * cos + even * sin   # both before either is stored
+                x[..., 0::2] = new_even.to(x.dtype)
+                x[..., 1::2] = new_odd.to(x.dtype)
+
+
+def test_toy_routed_feed_forward_and_position_encoding_build_and_step():
+    from tesseract_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from tesseract_b200.engine import StepEntry, make_stepper
+    from tesseract_b200.models import DecoderModel, tensor_roles
+
+    register_toy_routing_and_position()
+    hidden, vocab, d = 32, 47, 16
+
+    def norm(name):
+        return PartSpec.make("rms_norm", {"size": hidden, "eps": 1e-5}, {"weight": name})
+
+    def layer(i):
+        mixer = PartSpec.make("attention", {"hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": d,
+                                            "window": None, "scale": None},
+                              {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"},
+                              {"position": PartSpec.make("toy_adjacent_pairs", {"head_dim": d, "theta": 50.0})})
+        ffn = PartSpec.make("toy_top1", {"experts": 3, "hidden_size": hidden, "intermediate_size": 24},
+                            {"router": f"l{i}.r", "w1": f"l{i}.w1", "w2": f"l{i}.w2"})
+        return LayerSpec.make("pre_norm", mixer, ffn, {"input": norm(f"l{i}.n1"), "post_mixer": norm(f"l{i}.n2")})
+
+    sizes = {"vocab_size": vocab, "hidden_size": hidden}
+    spec = ModelSpec(architecture="RoutedForTests", hidden_size=hidden, vocab_size=vocab, max_positions=128,
+                     embedding=PartSpec.make("token_embedding", sizes, {"table": "emb"}),
+                     layers=(layer(0), layer(1)), run_order=(RunEntry(0), RunEntry(1)),
+                     final_norm=norm("fn"), head=PartSpec.make("lm_head", sizes, {"weight": "head"}))
+    g = torch.Generator().manual_seed(11)
+    tensors = {name: cls.random_tensor(part, role, tuple(want.shape), g) * (4 if role in "qk" else 1)
+               for cls, part, role, name, want in tensor_roles(spec)}
+    model = DecoderModel(spec, tensors, runtime(torch.float32))
+    stepper = make_stepper(model, capacity_tokens=128, max_requests=2)
+
+    def plain(tokens):
+        w = {k: v.double() for k, v in tensors.items()}
+        T = len(tokens)
+        freq = torch.tensor([50.0 ** (-2.0 * i / d) for i in range(d // 2)], dtype=torch.float32)
+        angle = (torch.arange(T, dtype=torch.float32)[:, None] * freq[None, :]).double()
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+
+        def rotate(x):
+            out = torch.empty_like(x)
+            out[..., 0::2] = x[..., 0::2] * cos - x[..., 1::2] * sin
+            out[..., 1::2] = x[..., 1::2] * cos + x[..., 0::2] * sin
+            return out
+
+        h = llama.embed(tokens, w["emb"])
+        for i in range(2):
+            x = llama.rms_norm(h, w[f"l{i}.n1"], 1e-5)
+            q, k = rotate((x @ w[f"l{i}.q"].T).view(T, 2, d)), rotate((x @ w[f"l{i}.k"].T).view(T, 1, d))
+            v = (x @ w[f"l{i}.v"].T).view(T, 1, d)
+            h = h + llama.attention(q, k, v, 0.25).reshape(T, 2 * d) @ w[f"l{i}.o"].T
+            m = llama.rms_norm(h, w[f"l{i}.n2"], 1e-5)
+            expert = (m @ w[f"l{i}.r"].T).argmax(dim=1)
+            hid = torch.relu(torch.einsum("th,tih->ti", m, w[f"l{i}.w1"][expert]))
+            h = h + torch.einsum("ti,thi->th", hid, w[f"l{i}.w2"][expert])
+        return llama.rms_norm(h, w["fn"], 1e-5) @ w["head"].T
+
+    rng = np.random.default_rng(3)
+    tokens = rng.integers(0, vocab, 41).tolist()
+    want = plain(tokens)
+    assert stepper.cache.admit("r")
+    got, at = [], 0
+    for n in (17, 2, 1, 1, 9, 1, 10):                       # a portion, tiny portions, decoded tokens
+        got.append(stepper.step([StepEntry("r", tokens[at:at + n], list(range(n)))]).cpu().double())
+        at += n
+    # a routed layer can flip an expert on a near tie; with these seeds no row is that close
+    torch.testing.assert_close(torch.cat(got), want, rtol=5e-5, atol=5e-5)
+
+
 def windowed_spec(hidden=32, vocab=61, window=20):
     """Two attention layers with different cache needs: layer 0 sees all keys, layer 1 the last `window` only."""
     from tesseract_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
