@@ -1,6 +1,7 @@
 // bfloat16 matrix product on the fifth-generation tensor cores: C[M,N] = A[M,K] . W[N,K]^T, 32-bit accumulation.
 //
-// The Blackwell-native path for prompt-sized batches.  One CTA computes a 128 x 256 tile of C:
+// The Blackwell-native path for prompt-sized batches.  A persistent CTA per SM computes 128 x 256 tiles of C, two
+// accumulators in tensor memory so that one tile's epilogue runs under the next tile's products:
 //   * warp 0, one elected lane: TMA producer.  Tiles of A (128 x 64) and W (256 x 64) are brought into a
 //     four-stage ring in shared memory by cp.async.bulk.tensor with the 128-byte swizzle; completion is
 //     signalled on an mbarrier per stage (no multicast: every CTA issues its own loads).
@@ -24,7 +25,7 @@ constexpr int kThreads = 256;
 constexpr uint32_t kATileBytes = BM * BK * 2;   // 16 KiB
 constexpr uint32_t kBTileBytes = BN * BK * 2;   // 32 KiB
 constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
-constexpr uint32_t kTmemColumns = 256;
+constexpr uint32_t kTmemColumns = 512;   // two accumulators of BN columns
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -33,6 +34,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -104,6 +108,47 @@ struct GemmParams {
     int* error;
 };
 
+// One 32-column chunk of an accumulator row: to memory as the epilogue asks.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&acc)[32]) {
+    if (row >= p.M || col0 >= p.N) return;
+    if (EPI == EPI_F32) {
+        float* dst = reinterpret_cast<float*>(p.out) + (int64_t)row * p.out_stride + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            if (col0 + j < p.N)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
+                                                                  __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+    } else if (EPI == EPI_BF16) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            if (col0 + j >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j + e]);
+            Packet<__nv_bfloat16>::store(dst + j, v);
+        }
+    } else {
+        // columns come in blocks of sixteen: eight gates, then their eight up projections
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0 / 2;
+#pragma unroll
+        for (int j = 0; j < 32; j += 16) {
+            if (col0 + j >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float gate = __uint_as_float(acc[j + e]), up = __uint_as_float(acc[j + 8 + e]);
+                v[e] = gate * __fdividef(1.0f, 1.0f + __expf(-gate)) * up;   // 32-bit, fast reciprocal and exponential
+            }
+            Packet<__nv_bfloat16>::store(dst + j / 2, v);
+        }
+    }
+}
+
+// Persistent: a CTA per SM walks over the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tiles that are
+// neighbours in time share a panel of W and the rows of A, which then come from L2).  Two accumulators of 256
+// columns in tensor memory: while the epilogue warps drain one tile, the products of the next fill the other.
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -111,14 +156,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int k_blocks = (p.K + BK - 1) / BK;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), done_bar = smem_u32(&bars[2 * STAGES]);
+    const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = acc_full0 + 16;
     const uint32_t tiles = smem_u32(smem);
 
     if (threadIdx.x == 0) {
@@ -127,7 +175,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(done_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);      // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -144,92 +195,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
-        for (int kb = 0; kb < k_blocks; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t parity = ((kb / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
-            if (!mbar_wait(empty0 + 8 * s, parity, &abort_flag)) {
-                abort_flag = 1;
-                atomicExch(p.error, 1);
-                break;
+        int g = 0;                                               // k blocks issued so far, over all tiles
+        for (int t = blockIdx.x; t < total_tiles && !abort_flag; t += gridDim.x) {
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+            for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                const int s = g % STAGES;
+                if (!mbar_wait(empty0 + 8 * s, ((g / STAGES) & 1) ^ 1, &abort_flag)) {   // fresh barriers pass parity 1
+                    abort_flag = 1;
+                    atomicExch(p.error, 1);
+                    break;
+                }
+                mbar_expect_tx(full0 + 8 * s, kStageBytes);
+                const uint32_t a_dst = tiles + s * kStageBytes;
+                tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
+                tma_load_2d(a_dst + kATileBytes, &map_b, full0 + 8 * s, kb * BK, n0);
             }
-            mbar_expect_tx(full0 + 8 * s, kStageBytes);
-            const uint32_t a_dst = tiles + s * kStageBytes;
-            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
-            tma_load_2d(a_dst + kATileBytes, &map_b, full0 + 8 * s, kb * BK, n0);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        int g = 0, i = 0;
         bool ok = true;
-        for (int kb = 0; kb < k_blocks && ok; ++kb) {
-            const int s = kb % STAGES;
-            if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, &abort_flag)) {
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            // the epilogue must have drained this accumulator's previous tile
+            if (!mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_flag)) {
                 abort_flag = 1;
-                atomicExch(p.error, 2);
+                atomicExch(p.error, 4);
                 ok = false;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = tiles + s * kStageBytes, b_addr = a_addr + kATileBytes;
+            const uint32_t acc = tmem_base + buf * BN;
+            for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                const int s = g % STAGES;
+                if (!mbar_wait(full0 + 8 * s, (g / STAGES) & 1, &abort_flag)) {
+                    abort_flag = 1;
+                    atomicExch(p.error, 2);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = tiles + s * kStageBytes, b_addr = a_addr + kATileBytes;
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk) {
-                // inside the 128-byte swizzle atom a step of 16 elements along K is 32 bytes of start address
-                umma_bf16(tmem_base, umma_desc_k_sw128(a_addr + kk * 32), umma_desc_k_sw128(b_addr + kk * 32), idesc,
-                          (kb | kk) != 0);
+                for (int kk = 0; kk < BK / 16; ++kk) {
+                    // inside the 128-byte swizzle atom a step of 16 elements along K is 32 bytes of start address
+                    umma_bf16(acc, umma_desc_k_sw128(a_addr + kk * 32), umma_desc_k_sw128(b_addr + kk * 32), idesc,
+                              (kb | kk) != 0);
+                }
+                umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
             }
-            umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+            if (ok) umma_commit(acc_full0 + 8 * buf); // the accumulator is complete once all products are done
         }
-        if (ok) umma_commit(done_bar);            // the accumulator is complete once all products are done
     } else if (warp >= 4) {
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;             // a warp may touch tensor-memory lanes 32*(warp % 4) .. +31
-        const int row = m0 + quarter * 32 + lane;
-        if (mbar_wait(done_bar, 0, &abort_flag)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t acc[32];
-                tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, acc);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col0 = n0 + c * 32;
-                if (row >= p.M || col0 >= p.N) continue;
-                if (EPI == EPI_F32) {
-                    float* dst = reinterpret_cast<float*>(p.out) + (int64_t)row * p.out_stride + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        if (col0 + j < p.N)
-                            *reinterpret_cast<float4*>(dst + j) =
-                                make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
-                                            __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
-                } else if (EPI == EPI_BF16) {
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (col0 + j >= p.N) break;
-                        float v[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j + e]);
-                        Packet<__nv_bfloat16>::store(dst + j, v);
-                    }
-                } else {
-                    // columns come in blocks of sixteen: eight gates, then their eight up projections
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.out_stride + col0 / 2;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 16) {
-                        if (col0 + j >= p.N) break;
-                        float v[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float gate = __uint_as_float(acc[j + e]), up = __uint_as_float(acc[j + 8 + e]);
-                            v[e] = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                        }
-                        Packet<__nv_bfloat16>::store(dst + j / 2, v);
-                    }
-                }
+        int i = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            if (!mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, &abort_flag)) {
+                abort_flag = 1;
+                atomicExch(p.error, 3);
+                break;
             }
-        } else {
-            abort_flag = 1;
-            atomicExch(p.error, 3);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lanes = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                uint32_t acc0[32], acc1[32];      // two chunks in flight: the second loads while the first is stored
+                tmem_load_32(lanes + c * 32, acc0);
+                tmem_load_32(lanes + c * 32 + 32, acc1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                store_chunk<EPI>(p, row, n0 + c * 32, acc0);
+                store_chunk<EPI>(p, row, n0 + c * 32 + 32, acc1);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -299,7 +343,14 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
     p.K = K;
     p.error = error;
     const size_t smem = (size_t)STAGES * kStageBytes + 1024;
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    const int total_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
+    }
+    dim3 grid(total_tiles < sms ? total_tiles : sms);
 #define TB_LAUNCH(E)                                                                                          \
     {                                                                                                         \
         cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \

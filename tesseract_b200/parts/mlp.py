@@ -71,5 +71,9 @@ class SwiGLU(FeedForward):
         if (self.interleaved and not self.runtime.is_float32 and rows <= 8
                 and kernels.decode_linear_supported(rows, proj.out_features, proj.in_features)):
             return kernels.decode_linear(proj.weight, activated, x=x, epilogue=kernels.EPI_SWIGLU)
+        if (self.interleaved and not self.runtime.is_float32 and rows >= kernels.FUSED_GATE_UP_MIN_ROWS
+                and kernels.gemm_tcgen05_supported(rows, proj.out_features, proj.in_features, kernels.EPI_SWIGLU)):
+            # prompt portions: both projections on the tcgen05 tensor cores, the activation in the epilogue
+            return kernels.gemm_tcgen05(x, proj.weight, activated, epilogue=kernels.EPI_SWIGLU)
         gate_up = proj.forward(x)
         return kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)
