@@ -186,6 +186,17 @@ def run_ours(args):
             last.append(int(rng.integers(0, cfg["vocab_size"])))
         greedy, ones = [0.0] * batch, [1.0] * batch
 
+        entries = [StepEntry(rid, [0], [0]) for rid in ids]
+        all_fed = [True] * batch
+
+        def launch(previous, tokens):
+            # as the scheduler does while every request decodes: the step is launched before the tokens of the
+            # step before have been read; they reach it on the device
+            if previous is None:
+                first = [StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)]
+                return stepper.launch_decode(first, greedy, greedy) if stepper.graphs else None
+            return stepper.launch_decode(entries, greedy, greedy, previous, all_fed)
+
         def one_step(tokens):
             return stepper.step_and_sample([StepEntry(rid, [t], [0]) for rid, t in zip(ids, tokens)],
                                            greedy, ones, greedy)
@@ -200,8 +211,16 @@ def run_ours(args):
         launches = launched()
         t0 = time.time()
         start.record()
-        for _ in range(steps):
-            last = one_step(last)
+        if stepper.graphs is not None:
+            inflight = launch(None, last)
+            for _ in range(steps - 1):
+                following = launch(inflight, None)
+                last = inflight.tokens()                  # host tokens out, one step behind the launches
+                inflight = following
+            last = inflight.tokens()
+        else:
+            for _ in range(steps):
+                last = one_step(last)
         stop.record()
         torch.cuda.synchronize()
         windows.append((t0, time.time()))

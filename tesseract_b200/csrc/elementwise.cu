@@ -126,3 +126,26 @@ TB_EXPORT int tb_silu_mul(const void* gu, void* out, int rows, int inter, int in
         return TB_ERR_BAD_DTYPE;
     return tb_launch_status();
 }
+
+namespace {
+
+// out[i] = feed[i] >= 0 ? previous[feed[i]] : tokens[i]: a decode step takes the token of a sequence either from
+// the host (its first decoded token) or straight from the row of the previous step's sampler output.
+__global__ void select_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ feed,
+                                     const int* __restrict__ previous, int* __restrict__ out, int n, int vocab) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int token = tokens[i];
+    const int from = feed[i];
+    if (from >= 0) token = previous[from];
+    out[i] = (token >= 0 && token < vocab) ? token : 0;   // never index the embedding table out of range
+}
+
+}  // namespace
+
+TB_EXPORT int tb_select_tokens(const int* tokens, const int* feed, const int* previous, int* out, int n, int vocab,
+                               cudaStream_t stream) {
+    if (n <= 0) return 0;
+    select_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, feed, previous, out, n, vocab);
+    return tb_launch_status();
+}

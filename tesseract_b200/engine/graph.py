@@ -15,6 +15,7 @@ at the scratch page and the scratch state slot, so they disturb nothing.
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -32,26 +33,30 @@ def _next_pow2(n: int) -> int:
     return p
 
 
+HOST_RING = 3          # pinned copies of a graph's metadata: a launch may be prepared while two are still in flight
+
+
 class _Graph:
     """Persistent buffers and the captured graph for one (batch bucket, table width)."""
 
-    def __init__(self, stepper: Stepper, batch: int, columns: int):
+    def __init__(self, stepper: Stepper, batch: int, columns: int, sampled: torch.Tensor):
         cache, device = stepper.cache, stepper.runtime.device
         self.batch, self.columns = batch, columns
         self.paged = [i for i, g in enumerate(cache.groups) if g.pool is not None]
-        ints = 3 * batch + len(self.paged) * batch * columns
+        ints = 4 * batch + len(self.paged) * batch * columns
         ints = (ints + 1) // 2 * 2                                  # keep the float64 block 8-byte aligned
         self.nbytes = ints * 4 + batch * 4 + (batch % 2) * 4 + batch * 8
-        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=True)
+        self.hosts = [torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=True) for _ in range(HOST_RING)]
+        self.host_events: List[Optional[torch.cuda.Event]] = [None] * HOST_RING
+        self.next_host = 0
         self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
 
         def carve(buffer):
             at = 0
             out = {}
-            for name, count, dtype, width in (("tokens", batch, torch.int32, 4), ("positions", batch, torch.int32, 4),
-                                              ("slots", batch, torch.int32, 4)):
-                out[name] = buffer[at:at + count * width].view(dtype)
-                at += count * width
+            for name in ("tokens", "feed", "positions", "slots"):
+                out[name] = buffer[at:at + batch * 4].view(torch.int32)
+                at += batch * 4
             out["tables"] = []
             for _ in self.paged:
                 out["tables"].append(buffer[at:at + batch * columns * 4].view(torch.int32).view(batch, columns))
@@ -62,19 +67,24 @@ class _Graph:
             out["uniform"] = buffer[at:at + batch * 8].view(torch.float64)
             return out
 
-        self.h = carve(self.host)
         self.d = carve(self.dev)
-        self.h_np = {k: (v.numpy() if not isinstance(v, list) else [t.numpy() for t in v]) for k, v in self.h.items()}
-        self.h_np["slots"][:] = cache.scratch_slot
-        self.dev.copy_(self.host)
+        self.h_np = []
+        for host in self.hosts:
+            views = carve(host)
+            arrays = {k: (v.numpy() if not isinstance(v, list) else [t.numpy() for t in v]) for k, v in views.items()}
+            arrays["slots"][:] = cache.scratch_slot
+            arrays["feed"][:] = -1
+            self.h_np.append(arrays)
+        self.dev.copy_(self.hosts[0])
         arange = torch.arange(batch + 1, dtype=torch.int32, device=device)
-        self.out_tokens = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.sampled = sampled                       # shared by all graphs: row i holds the last token of row i
+        self.tokens = torch.zeros(batch, dtype=torch.int32, device=device)   # this step's token ids, chosen on the device
         groups: List[GroupView] = []
         tables = dict(zip(self.paged, self.d["tables"]))
         for index, g in enumerate(cache.groups):
             groups.append(GroupView(tables.get(index), cache.page_size if g.pool is not None else 0))
         self.ctx = StepContext(
-            num_rows=batch, num_seqs=batch, token_ids=self.d["tokens"], positions=self.d["positions"],
+            num_rows=batch, num_seqs=batch, token_ids=self.tokens, positions=self.d["positions"],
             seq_of_row=arange[:batch], row_start=arange, seq_begin=self.d["positions"], state_slots=self.d["slots"],
             groups=groups, host_new=[1] * batch, host_begin=(), host_slots=(), max_new=1,
             max_context=columns * cache.page_size)
@@ -83,13 +93,26 @@ class _Graph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._capture(stepper)
 
+    def host_arrays(self) -> Tuple[int, dict]:
+        """The next pinned metadata block of the ring, once the copy that last read it is done."""
+        index = self.next_host
+        self.next_host = (index + 1) % HOST_RING
+        event = self.host_events[index]
+        if event is not None:
+            event.synchronize()
+        return index, self.h_np[index]
+
     def _run(self, stepper: Stepper) -> torch.Tensor:
+        # a row's token comes from the host or, for a sequence that decoded in the step before, from that step's
+        # sampler output, which never leaves the device
+        kernels.select_tokens(self.d["tokens"], self.d["feed"], self.sampled, self.tokens, stepper.vocab_size)
         logits = stepper.model.forward(self.ctx, stepper.cache.bindings, self.want_rows)
-        kernels.sample(logits, self.d["temps"], self.d["uniform"], self.out_tokens)
+        kernels.sample(logits, self.d["temps"], self.d["uniform"], self.sampled[:self.batch])
         return logits
 
     def _capture(self, stepper: Stepper) -> None:
         torch.cuda.synchronize()
+        kept = self.sampled.clone()                 # the step before may be feeding its tokens to this one
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -97,13 +120,39 @@ class _Graph:
                 self._run(stepper)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        self.sampled.copy_(kept)
         graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count
-        with torch.cuda.graph(graph):
-            self.logits = self._run(stepper)
+        # No destructor may run while the stream is capturing: a dead graph of an earlier engine that the cycle
+        # collector happened to free right then would make a CUDA call that invalidates the capture.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = self._run(stepper)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels_per_replay = kernels.launch_count - before     # this package's kernels inside the graph
         self.graph = graph
         torch.cuda.synchronize()
+
+
+class DecodeLaunch:
+    """A decode step that has been launched: where each request's row is, and where its tokens will arrive."""
+
+    def __init__(self, rows: Dict, count: int, host_tokens: torch.Tensor, done: torch.cuda.Event, graph: _Graph):
+        self.rows = rows                  # request -> row of this step
+        self.count = count
+        self.host_tokens = host_tokens    # pinned int32, filled by an asynchronous copy
+        self.done = done
+        self.graph = graph
+
+    def tokens(self) -> List[int]:
+        """Wait for the step and return its sampled tokens, one per row, in row order."""
+        self.done.synchronize()
+        return self.host_tokens[:self.count].tolist()
 
 
 class DecodeGraphs:
@@ -117,14 +166,21 @@ class DecodeGraphs:
         self.captures = 0
         self.kernels_replayed = 0
         self.safe = all(getattr(block.mixer, "graph_safe", False) for block in stepper.model.layers)
+        widest = max(_next_pow2(max_batch), max_batch)
+        self.sampled = torch.zeros(widest, dtype=torch.int32, device=stepper.runtime.device)
+        self._token_ring = [torch.zeros(widest, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
+        self._token_events: List[Optional[torch.cuda.Event]] = [None] * HOST_RING
+        self._next_tokens = 0
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         return (self.safe and len(entries) <= self.max_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
-    def step(self, entries: Sequence[StepEntry], temperatures: Sequence[float], draws: Sequence[float]
-             ) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Run one pure-decode step; returns (tokens int32 [B] on the device, logits [B, vocab])."""
+    def launch(self, entries: Sequence[StepEntry], temperatures: Sequence[float], draws: Sequence[float],
+               previous: Optional[DecodeLaunch] = None, fed: Optional[Sequence[bool]] = None) -> DecodeLaunch:
+        """Enqueue one pure-decode step and return at once.  ``fed[i]`` says that entry i's token is whatever
+        ``previous`` sampled for the same request (the entry's own token is then ignored): the step can be
+        launched before the host has seen that token."""
         stepper, cache = self.stepper, self.stepper.cache
         stepper._validate(entries)
         for entry in entries:
@@ -135,18 +191,25 @@ class DecodeGraphs:
         key = (min(_next_pow2(count), max(self.max_batch, count)), max(8, _next_pow2(pages)))
         graph = self.graphs.get(key)
         if graph is None:
-            graph = _Graph(stepper, *key)
+            graph = _Graph(stepper, *key, self.sampled)
             self.graphs[key] = graph
             self.captures += 1
-        h = graph.h_np
+        slot_index, h = graph.host_arrays()
         slots = [cache.slot(e.request) for e in entries]
         h["tokens"][:count] = [int(e.tokens[0]) for e in entries]
+        feed = [-1] * count
+        if previous is not None and fed is not None:
+            for i, entry in enumerate(entries):
+                if fed[i]:
+                    feed[i] = previous.rows[entry.request]
+        h["feed"][:count] = feed
         h["positions"][:count] = lengths
         h["slots"][:count] = slots
         h["temps"][:count] = temperatures
         h["uniform"][:count] = draws
         if count < graph.batch:
             h["tokens"][count:] = 0
+            h["feed"][count:] = -1
             h["positions"][count:] = 0
             h["slots"][count:] = cache.scratch_slot
             h["temps"][count:] = 0.0
@@ -154,11 +217,29 @@ class DecodeGraphs:
             table[:count] = cache.block_table_rows(group_index, slots, graph.columns)
             if count < graph.batch:
                 table[count:] = 0
-        graph.dev.copy_(graph.host, non_blocking=True)
+        graph.dev.copy_(graph.hosts[slot_index], non_blocking=True)
+        copied = torch.cuda.Event()
+        copied.record()
+        graph.host_events[slot_index] = copied
         graph.graph.replay()
+        # the sampled tokens go to pinned memory at once: the next launch may overwrite the sampler's rows
+        ring = self._next_tokens
+        self._next_tokens = (ring + 1) % HOST_RING
+        if self._token_events[ring] is not None:
+            self._token_events[ring].synchronize()
+        self._token_ring[ring][:count].copy_(self.sampled[:count], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self._token_events[ring] = done
         for entry in entries:
             cache.commit(entry.request, 1)
         stepper.steps_run += 1
         self.replays += 1
         self.kernels_replayed += graph.kernels_per_replay
-        return graph.out_tokens[:count], graph.logits[:count]
+        return DecodeLaunch({e.request: i for i, e in enumerate(entries)}, count, self._token_ring[ring], done, graph)
+
+    def step(self, entries: Sequence[StepEntry], temperatures: Sequence[float], draws: Sequence[float]
+             ) -> Tuple[List[int], torch.Tensor]:
+        """Run one pure-decode step and wait for it; returns (tokens, logits [B, vocab] on the device)."""
+        launch = self.launch(entries, temperatures, draws)
+        return launch.tokens(), launch.graph.logits[:launch.count]

@@ -60,7 +60,9 @@ class LLM:
                                    eos_token_ids=self.model.spec.eos_token_ids,
                                    max_positions=self.model.spec.max_positions,
                                    capacity_tokens=self.stepper.cache.num_pages * page_size,
-                                   run_and_sample=self.stepper.step_and_sample)
+                                   run_and_sample=self.stepper.step_and_sample,
+                                   launch_decode=self.stepper.launch_decode if cuda_graphs else None,
+                                   can_launch_decode=self.stepper.can_launch_decode if cuda_graphs else None)
         self.tokenizer = self._load_tokenizer(model_path)
 
     @staticmethod

@@ -20,6 +20,13 @@ Behaviour follows the reference's engine thread (src/engine/scheduler.rs):
 * ``apply`` (:724-833) appends sampled tokens and finishes on a stop token, an
   end-of-sequence id or ``max_tokens``; a failed step fails the requests of its batch,
   frees what they held and leaves the engine serving (:495-505).
+
+Not in the reference: while every running request is decoding, steps are launched one ahead
+of the read-back of their tokens.  The step function takes a sequence's token from the
+previous step's sampler output on the device, so the host builds and launches step k + 1
+while step k runs and only then looks at step k's tokens (stop tokens, end of sequence).
+A request that turns out to have ended at step k has one row of step k + 1 computed in
+vain; its token is dropped.  The tokens each request receives are the same either way.
 """
 
 from __future__ import annotations
@@ -83,6 +90,7 @@ class ScheduledSequence:
     tokens: List[int]
     samples: bool
     draw: float = 0.0
+    slot: int = -1          # launched ahead: index in ``request.generated`` that this step's token will fill
 
     @property
     def is_decode(self) -> bool:
@@ -105,13 +113,19 @@ class Scheduler:
 
     def __init__(self, config: EngineConfig, cache, run_step: Callable, sample: Callable, *, eos_token_ids=(),
                  max_positions: Optional[int] = None, capacity_tokens: Optional[int] = None,
-                 run_and_sample: Optional[Callable] = None):
+                 run_and_sample: Optional[Callable] = None, launch_decode: Optional[Callable] = None,
+                 can_launch_decode: Optional[Callable] = None):
         config.validate()
         self.config = config
         self.cache = cache
         self.run_step = run_step
         self.sample = sample
         self.run_and_sample = run_and_sample    # (entries, temperatures, top_ps, draws) -> tokens, in one call
+        # launch_decode(entries, temperatures, draws, previous, fed) -> launch with .tokens(); can_launch_decode(
+        # number of rows, top_ps) says whether a pure decode batch may go that way.  Both or neither.
+        self.launch_decode = launch_decode
+        self.can_launch_decode = can_launch_decode
+        self._inflight: Optional[Tuple[List[ScheduledSequence], object]] = None   # launched, tokens not read yet
         self.eos_token_ids = frozenset(int(t) for t in eos_token_ids)
         self.max_positions = max_positions
         self.capacity_tokens = capacity_tokens if capacity_tokens is not None else config.kv_capacity_tokens
@@ -181,6 +195,8 @@ class Scheduler:
                 remaining = request.target_tokens - request.computed_tokens
                 if remaining <= 0:
                     continue
+                if is_decode and len(request.generated) >= request.params.max_tokens:
+                    continue    # its last token is in flight (steps launched ahead): nothing more to compute
                 limit = 1 if is_decode else self.config.prefill_chunk_tokens
                 count = min(remaining, limit, budget)
                 begin = request.computed_tokens
@@ -199,9 +215,12 @@ class Scheduler:
     def step(self) -> StepResult:
         """Admit, build one batch, run it, sample, apply.  Returns what happened."""
         self.admit_waiting()
+        if self._may_launch_ahead():
+            return self._step_launched_ahead()
+        drained = self._drain()
         batch = self.build_batch()
         if not batch:
-            return StepResult([], {}, [])
+            return drained or StepResult([], {}, [])
         self.steps += 1
         entries = [StepEntry(s.request.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
         sampled = [s for s in batch if s.samples]
@@ -217,12 +236,101 @@ class Scheduler:
             if len(tokens) != len(sampled):
                 raise RuntimeError("the sampler returned a wrong number of tokens")
         except Exception as exc:  # noqa: BLE001 - a failed step fails its batch, the engine keeps serving
-            finished = []
-            for s in batch:
+            result = self._fail(batch, exc)
+        else:
+            result = self._apply(batch, sampled, tokens)
+        if drained is not None:
+            result.new_tokens.update(drained.new_tokens)
+            result.finished[:0] = drained.finished
+        return result
+
+    def _fail(self, batch, exc) -> StepResult:
+        finished = []
+        for s in batch:
+            if s.request.finish_reason is None:
                 s.request.error = f"{type(exc).__name__}: {exc}"
                 finished.append(self._finish(s.request.id, FINISH_ERROR))
-            return StepResult(batch, {}, [r for r in finished if r is not None])
-        return self._apply(batch, sampled, tokens)
+        return StepResult(batch, {}, [r for r in finished if r is not None])
+
+    # ------------------------------------------------------------------ steps launched ahead of their read-back
+    def _may_launch_ahead(self) -> bool:
+        if self.launch_decode is None or not self.running:
+            return False
+        requests = [self.requests[i] for i in self.running]
+        if any(r.computed_tokens < len(r.prompt) for r in requests):
+            return False                                  # prompt portions: those steps run the ordinary way
+        return bool(self.can_launch_decode(len(requests), [r.params.top_p for r in requests]))
+
+    def _step_launched_ahead(self) -> StepResult:
+        previous = self._inflight
+        batch = self.build_batch()
+        if not batch:                                     # every running request waits for a token in flight
+            return self._drain() or StepResult([], {}, [])
+        self.steps += 1
+        fed = [s.tokens[0] is None for s in batch]        # the token is still on the device: feed it from there
+        entries = [StepEntry(s.request.id, [0 if f else s.tokens[0]], [0]) for s, f in zip(batch, fed)]
+        try:
+            launch = self.launch_decode(entries, [s.request.params.temperature for s in batch],
+                                        [s.draw for s in batch], previous[1] if previous else None, fed)
+        except Exception as exc:  # noqa: BLE001
+            self._inflight = None
+            result = self._fail(batch, exc)
+            if previous is not None:
+                earlier = self._collect(previous)
+                result.new_tokens.update(earlier.new_tokens)
+                result.finished[:0] = earlier.finished
+            return result
+        for s in batch:
+            s.request.computed_tokens += 1
+            s.slot = len(s.request.generated)
+            s.request.generated.append(None)              # filled when the launch is read back
+        self._inflight = (batch, launch)
+        if previous is None:
+            return StepResult(batch, {}, [])
+        result = self._collect(previous)
+        return StepResult(batch, result.new_tokens, result.finished)
+
+    def _drain(self) -> Optional[StepResult]:
+        """Read back the step that is in flight, if any."""
+        if self._inflight is None:
+            return None
+        inflight, self._inflight = self._inflight, None
+        return self._collect(inflight)
+
+    def _collect(self, inflight) -> StepResult:
+        batch, launch = inflight
+        try:
+            tokens = launch.tokens()
+            if len(tokens) != len(batch):
+                raise RuntimeError("the sampler returned a wrong number of tokens")
+        except Exception as exc:  # noqa: BLE001
+            return self._fail(batch, exc)
+        new_tokens: Dict[Hashable, int] = {}
+        finished: List[Request] = []
+        for s, token in zip(batch, tokens):
+            request = s.request
+            if request.finish_reason is not None:
+                continue                                  # ended meanwhile: this row was computed in vain
+            token = int(token)
+            request.generated[s.slot] = token
+            new_tokens[request.id] = token
+            reason = self._stop_reason(request, token, s.slot + 1)
+            if reason is not None:
+                del request.generated[s.slot + 1:]        # a token launched after the last one is dropped
+                request.computed_tokens = min(request.computed_tokens, len(request.prompt) + s.slot)
+                done = self._finish(request.id, reason)
+                if done is not None:
+                    finished.append(done)
+        return StepResult(batch, new_tokens, finished)
+
+    def _stop_reason(self, request: Request, token: int, generated: int) -> Optional[str]:
+        if token in request.params.stop_token_ids:
+            return FINISH_STOP
+        if token in self.eos_token_ids and not request.params.ignore_eos:
+            return FINISH_STOP
+        if generated >= request.params.max_tokens:
+            return FINISH_LENGTH
+        return None
 
     def _apply(self, batch, sampled, tokens) -> StepResult:
         new_tokens: Dict[Hashable, int] = {}
@@ -234,13 +342,7 @@ class Scheduler:
             token = int(token)
             request.generated.append(token)
             new_tokens[request.id] = token
-            reason = None
-            if token in request.params.stop_token_ids:
-                reason = FINISH_STOP
-            elif token in self.eos_token_ids and not request.params.ignore_eos:
-                reason = FINISH_STOP
-            elif len(request.generated) >= request.params.max_tokens:
-                reason = FINISH_LENGTH
+            reason = self._stop_reason(request, token, len(request.generated))
             if reason is not None:
                 done = self._finish(request.id, reason)
                 if done is not None:
@@ -252,6 +354,7 @@ class Scheduler:
         if request is None:
             return None
         request.finish_reason = reason
+        request.generated = [t for t in request.generated if t is not None]   # a token still in flight is dropped
         try:
             self.waiting.remove(request_id)
         except ValueError:

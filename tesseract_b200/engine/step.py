@@ -177,11 +177,22 @@ class Stepper:
             self.step(entries)
             return []
         if self.graphs is not None and wanted == len(entries) and self.graphs.eligible(entries):
-            tokens, logits = self.graphs.step(entries, temperatures, draws)
-            out = tokens.cpu().tolist()
+            out, logits = self.graphs.step(entries, temperatures, draws)
             for i, (t, p) in enumerate(zip(temperatures, top_ps)):
                 if t > 0.0 and p < 1.0:
                     out[i] = sample_top_p_host(logits[i].cpu().numpy(), t, p, draws[i])
             return out
         logits = self.step(entries)
         return self._sampler.sample(logits, temperatures, top_ps, draws)
+
+    def can_launch_decode(self, rows: int, top_ps: Sequence[float]) -> bool:
+        """Whether :meth:`launch_decode` takes a batch of ``rows`` single-token rows with these top-p values: a
+        graph-replayed decode step, sampled on the device."""
+        return (self.graphs is not None and self.graphs.safe and 0 < rows <= self.graphs.max_batch
+                and all(p >= 1.0 for p in top_ps))
+
+    def launch_decode(self, entries: Sequence[StepEntry], temperatures: Sequence[float], draws: Sequence[float],
+                      previous=None, fed: Optional[Sequence[bool]] = None):
+        """Enqueue a decode step without waiting for it; ``launch.tokens()`` waits and returns its tokens.  Entries
+        marked in ``fed`` take their token from ``previous`` (the launch before) on the device."""
+        return self.graphs.launch(entries, temperatures, draws, previous, fed)

@@ -101,6 +101,21 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> t
     return out
 
 
+def select_tokens(tokens: torch.Tensor, feed: torch.Tensor, previous: torch.Tensor, out: torch.Tensor,
+                  vocab_size: int) -> torch.Tensor:
+    """``out[i] = previous[feed[i]] if feed[i] >= 0 else tokens[i]`` (all int32): token ids that stay on the device
+    from one decode step to the next."""
+    _cuda(tokens, feed, previous, out)
+    n = out.numel()
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (tokens, feed, previous, out)),
+          "select_tokens takes contiguous int32 tensors")
+    _need(tokens.numel() >= n and feed.numel() >= n, "select_tokens: tokens and feed must cover out")
+    lib = load_library("elementwise")
+    _check(lib.tb_select_tokens(_ptr(tokens), _ptr(feed), _ptr(previous), _ptr(out), _i32(n), _i32(vocab_size),
+                                _stream()), "select_tokens")
+    return out
+
+
 def gather_rows(rows_index: torch.Tensor, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[s] = src[rows_index[s]]``."""
     _cuda(rows_index, src, out)

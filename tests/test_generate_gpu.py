@@ -43,7 +43,7 @@ def test_greedy_generation_matches_plain(model_folders, name, lengths, steps, dt
               max_batch_tokens=48)
     outs = llm.generate(prompts, SamplingParams(max_tokens=steps, temperature=0.0, ignore_eos=True))
     for prompt, out in zip(prompts, outs):
-        assert len(out.token_ids) == steps and out.finish_reason == "length"
+        assert len(out.token_ids) == steps and out.finish_reason == "length", out.error
         check_greedy(config, tensors, prompt, out.token_ids, margin)
     assert llm.stepper.cache.used_pages() == 0
     llm.stepper.cache.check()
@@ -146,3 +146,30 @@ def test_graph_replay_decodes_like_the_eager_path(model_folders, dtype, margin):
         assert outs[True] == outs[False]
     for k in (0, 2):
         check_greedy(config, tensors, prompts[k], outs[True][k], margin)
+
+
+def test_steps_launched_ahead_give_the_same_tokens_as_ordinary_steps(model_folders):
+    """With CUDA graphs the scheduler launches decode steps before it has read the tokens of the step before
+    (they reach the next step on the device); without graphs every step waits.  Same tokens, with requests that
+    end at different times, stop tokens, temperature rows, and a request that arrives while others decode."""
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("c")
+    config, _ = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], n, seed=90 + n) for n in (3, 30, 70, 12, 45)]
+    first = LLM(folder, dtype="float32", kv_capacity_tokens=2048, max_running=3, prefill_chunk_tokens=32,
+                cuda_graphs=False)
+    greedy = first.generate(prompts[:1], SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True))[0].token_ids
+    params = [SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True, stop_token_ids=[greedy[6]]),
+              SamplingParams(max_tokens=31, temperature=0.9, seed=7, ignore_eos=True),
+              SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True),
+              SamplingParams(max_tokens=40, temperature=0.4, seed=8, ignore_eos=True),
+              SamplingParams(max_tokens=17, temperature=0.0, ignore_eos=True)]
+    want = [(o.token_ids, o.finish_reason) for o in first.generate(prompts, params)]
+    ahead = LLM(folder, dtype="float32", kv_capacity_tokens=2048, max_running=3, prefill_chunk_tokens=32)
+    got = [(o.token_ids, o.finish_reason) for o in ahead.generate(prompts, params)]
+    assert got == want
+    assert want[0][1] == "stop" and want[0][0][-1] == greedy[6]
+    assert ahead.stepper.graphs.replays > 20
+    assert ahead.stepper.cache.used_pages() == 0
+    ahead.stepper.cache.check()

@@ -218,3 +218,130 @@ def test_scheduler_state_machine(data):
             assert want in ([], [len(tokens) - 1])
     s.cache.check()
     assert s.cache.used_pages() == 0 and s.cache.slots.free_slots == max_running
+
+
+# ----------------------------------------------------------------------------- steps launched ahead of their read-back
+
+
+class FakeLaunch:
+    def __init__(self, rows, tokens):
+        self.rows, self._tokens, self.read = rows, tokens, False
+
+    def tokens(self):
+        self.read = True
+        return list(self._tokens)
+
+
+class FakeAheadEngine(FakeEngine):
+    """The fake with a device-like decode path: a launch returns at once, its tokens are read later, and a row
+    may take its token from the launch before (by that launch's row of the same request)."""
+
+    def __init__(self, config, fail_launch=None, **kw):
+        super().__init__(config, **kw)
+        self.launches = []
+        self.unread_at_launch = []
+        self.fail_launch = fail_launch
+
+    def can_launch_decode(self, rows, top_ps):
+        return 0 < rows <= 4 and all(p >= 1.0 for p in top_ps)
+
+    def launch_decode(self, entries, temperatures, draws, previous, fed):
+        if self.fail_launch is not None and len(self.launches) == self.fail_launch:
+            self.launches.append("failed")
+            raise RuntimeError("injected launch failure")
+        self.unread_at_launch.append(previous is not None and not previous.read)
+        tokens = []
+        for e, from_device in zip(entries, fed):
+            last = previous._tokens[previous.rows[e.request]] if from_device else e.tokens[0]
+            assert from_device or last is not None
+            self.cache.extend(e.request, 1)
+            self.cache.commit(e.request, 1)
+            tokens.append(1000 if last < 1000 else last + 1)
+        self.draws.extend(draws)
+        launch = FakeLaunch({e.request: i for i, e in enumerate(entries)}, tokens)
+        self.launches.append(launch)
+        return launch
+
+
+def make_ahead(**kw):
+    config = EngineConfig(max_queue=8, max_running=4, max_batch_tokens=32, prefill_chunk_tokens=8,
+                          kv_capacity_tokens=512, max_sequence_length=512)
+    fake = FakeAheadEngine(config, **kw)
+    scheduler = Scheduler(config, fake.cache, fake.run_step, fake.sample, eos_token_ids=[1003], max_positions=400,
+                          launch_decode=fake.launch_decode, can_launch_decode=fake.can_launch_decode)
+    return scheduler, fake
+
+
+def workload(scheduler, arrivals):
+    """Requests arrive at given iterations; returns {prompt length: (tokens, reason)} when all are done."""
+    finished, step = [], 0
+    pending = sorted(arrivals, key=lambda a: a[0])
+    while pending or scheduler.has_work():
+        while pending and pending[0][0] <= step:
+            _, prompt, params = pending.pop(0)
+            scheduler.add_request(prompt, params)
+        finished += scheduler.step().finished
+        step += 1
+        assert step < 10_000
+    return {len(r.prompt): (r.generated, r.finish_reason) for r in finished}
+
+
+ARRIVALS = [
+    (0, list(range(5)), SamplingParams(max_tokens=9, ignore_eos=True, temperature=0.0)),
+    (0, list(range(11)), SamplingParams(max_tokens=30, temperature=0.0)),                    # ends at 1003
+    (3, list(range(21)), SamplingParams(max_tokens=4, ignore_eos=True, temperature=0.7, seed=5)),
+    (9, list(range(3)), SamplingParams(max_tokens=12, stop_token_ids=[1006], ignore_eos=True, temperature=0.0)),
+    (30, list(range(7)), SamplingParams(max_tokens=1, ignore_eos=True, temperature=0.0)),
+]
+
+
+def test_launching_ahead_gives_every_request_the_same_tokens():
+    plain, _ = make()
+    ahead, fake = make_ahead()
+    want = workload(plain, list(ARRIVALS))
+    got = workload(ahead, list(ARRIVALS))
+    assert got == want
+    assert got[11] == ([1000, 1001, 1002, 1003], FINISH_STOP) and got[3][0][-1] == 1006
+    assert any(fake.unread_at_launch)                    # steps really were launched before the one before was read
+    assert fake.cache.used_pages() == 0
+    fake.cache.check()
+
+
+def test_a_row_launched_after_its_request_ended_is_dropped():
+    s, fake = make_ahead()
+    s.add_request(list(range(4)), SamplingParams(max_tokens=30, temperature=0.0))            # ends at 1003 (eos)
+    done = run_all(s)
+    assert done[0].generated == [1000, 1001, 1002, 1003] and done[0].finish_reason == FINISH_STOP
+    # the step after the one that sampled 1003 had been launched already; its token never shows
+    assert [l._tokens for l in fake.launches][-1] == [1004]
+    assert s.cache.used_pages() == 0 and not s.has_work()
+
+
+def test_top_p_and_prompts_fall_back_to_ordinary_steps():
+    s, fake = make_ahead()
+    s.add_request(list(range(4)), SamplingParams(max_tokens=5, ignore_eos=True, temperature=0.8, top_p=0.5, seed=1))
+    done = run_all(s)
+    assert not fake.launches and len(done[0].generated) == 5
+
+
+def test_cancelling_a_request_with_a_token_in_flight():
+    s, fake = make_ahead()
+    a = s.add_request(list(range(4)), SamplingParams(max_tokens=50, ignore_eos=True, temperature=0.0))
+    b = s.add_request(list(range(6)), SamplingParams(max_tokens=6, ignore_eos=True, temperature=0.0))
+    for _ in range(5):
+        s.step()
+    s.cancel(a)
+    done = run_all(s)
+    assert [r.id for r in done] == [b] and done[0].generated == [1000 + i for i in range(6)]
+    assert s.cache.used_pages() == 0
+
+
+def test_a_failed_launch_fails_its_batch_and_the_engine_goes_on():
+    s, fake = make_ahead(fail_launch=2)
+    s.add_request(list(range(4)), SamplingParams(max_tokens=10, ignore_eos=True, temperature=0.0))
+    done = run_all(s)
+    assert done[0].finish_reason == FINISH_ERROR and "injected" in done[0].error
+    assert all(t is not None for t in done[0].generated)
+    s.add_request(list(range(4)), SamplingParams(max_tokens=3, ignore_eos=True, temperature=0.0))
+    assert run_all(s)[0].generated == [1000, 1001, 1002]
+    assert s.cache.used_pages() == 0
