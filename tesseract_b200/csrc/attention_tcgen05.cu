@@ -176,9 +176,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
     const int n_tiles = (n_rows + BM - 1) / BM;
-    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) return;     // short sequences belong to the decode kernel
+    pdl_trigger();
+    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) {           // short sequences belong to the decode kernel
+        pdl_wait();                                             // (no thread leaves before the kernel in front is done)
+        return;
+    }
     if (smem_u32(smem) & 1023u) {                               // never expected: refuse rather than compute garbage
         if (threadIdx.x == 0) atomicExch(p.error, 99);
+        pdl_wait();
         return;
     }
     const int r0 = (n_tiles - 1 - blockIdx.x) * BM;             // heavy tiles first
@@ -218,6 +223,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // barriers and tensor memory are set up while the kernel before this one drains; its results (the rotated
+    // queries, this step's keys and values) are read from here on
+    pdl_wait();
     // the Q tile: every thread copies its share of the 128 rows x 8 chunks, swizzled like the K/V tiles
     for (int idx = threadIdx.x; idx < BM * 8; idx += kThreads) {
         const int r = idx >> 3, c = idx & 7;
@@ -535,6 +543,7 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     if (err != cudaSuccess) return (int)err;
     const int max_folded = max_rows_per_seq * p.group;
     dim3 grid((max_folded + BM - 1) / BM, num_kv_heads, num_seqs);
-    attention_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(*map, p);
+    if (cudaError_t err = tb_launch_pdl(attention_tcgen05_kernel, grid, dim3(kThreads), smem, stream, *map, p))
+        return (int)err;
     return tb_launch_status();
 }

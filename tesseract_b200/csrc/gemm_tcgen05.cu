@@ -161,6 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.K + BK - 1) / BK;
     const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -192,6 +193,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    // barriers and tensor memory were set up while the kernel before this one drained; its results (the rows of
+    // A) are read from here on
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -356,7 +360,8 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
         cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                                (int)smem);                                                    \
         if (err != cudaSuccess) return (int)err;                                                              \
-        gemm_tcgen05_kernel<E><<<grid, kThreads, smem, stream>>>(map_a, map_b, p);                           \
+        err = tb_launch_pdl(gemm_tcgen05_kernel<E>, grid, dim3(kThreads), smem, stream, map_a, map_b, p);     \
+        if (err != cudaSuccess) return (int)err;                                                              \
     }
     if (epilogue == EPI_BF16) TB_LAUNCH(EPI_BF16)
     else if (epilogue == EPI_SWIGLU) TB_LAUNCH(EPI_SWIGLU)

@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(256) rms_norm_warp_kernel(const T* __restrict_
                                                             const float* __restrict__ w, T* __restrict__ y,
                                                             T* __restrict__ res_out, int rows, int width, float eps) {
     constexpr int N = Packet<T>::N;
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -128,10 +130,11 @@ template <typename T, bool ADD, int PACKETS>
 int launch_warp_kernel(const void* x, const void* upd, const float* w, void* y, void* res_out, int rows, int width,
                        float eps, cudaStream_t stream) {
     const int rows_per_block = 8;
-    rms_norm_warp_kernel<T, ADD, PACKETS><<<(rows + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0,
-                                            stream>>>((const T*)x, (const T*)upd, w, (T*)y, (T*)res_out, rows, width,
-                                                      eps);
-    return tb_launch_status();
+    // programmatic dependent launch: the kernel behind this one may set itself up while this one runs
+    cudaError_t err = tb_launch_pdl(rms_norm_warp_kernel<T, ADD, PACKETS>, dim3((rows + rows_per_block - 1) / rows_per_block),
+                                    dim3(rows_per_block * 32), 0, stream, (const T*)x, (const T*)upd, w, (T*)y,
+                                    (T*)res_out, rows, width, eps);
+    return err == cudaSuccess ? tb_launch_status() : (int)err;
 }
 
 template <typename T, bool ADD, bool VEC>
