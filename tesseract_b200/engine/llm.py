@@ -83,6 +83,17 @@ class LLM:
             return list(self.tokenizer.encode(prompt).ids)
         return [int(t) for t in prompt]
 
+    @staticmethod
+    def _check_device_waits() -> None:
+        """Every wait inside the tcgen05 kernels is bounded; one that ran out leaves a code on the device and the
+        results of that launch are not to be trusted.  Fail loudly rather than return them."""
+        from .. import kernels
+
+        code = kernels.tcgen05_error()
+        if code:
+            raise RuntimeError(f"a bounded wait inside a tcgen05 kernel ran out (code {code}); the generated "
+                               f"tokens of this call are unreliable")
+
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:
         """Generate for every prompt under continuous batching; outputs in the order of the prompts."""
@@ -104,6 +115,7 @@ class LLM:
             result = self.scheduler.step()
             for request in result.finished:
                 done[ids.pop(request.id)] = request
+        self._check_device_waits()
         outputs = []
         for index in range(len(prompts)):
             request = done[index]
