@@ -171,13 +171,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.z, kv_head = blockIdx.y;
+    // blockIdx.x runs over (tile rank, kv head) with the kv head fastest: CTAs start in the order of their index,
+    // so the heavy tiles (late rows see the most keys) of ALL heads start first and the light ones fill the gaps
+    const int seq = blockIdx.z, kv_head = blockIdx.x % p.num_kv_heads, tile_rank = blockIdx.x / p.num_kv_heads;
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
     const int n_tiles = (n_rows + BM - 1) / BM;
     pdl_trigger();
-    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) {           // short sequences belong to the decode kernel
+    if (n_rows <= 16 || tile_rank >= n_tiles) {           // short sequences belong to the decode kernel
         pdl_wait();                                             // (no thread leaves before the kernel in front is done)
         return;
     }
@@ -186,7 +188,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         pdl_wait();
         return;
     }
-    const int r0 = (n_tiles - 1 - blockIdx.x) * BM;             // heavy tiles first
+    const int r0 = (n_tiles - 1 - tile_rank) * BM;              // heavy tiles first
     const int begin = p.seq_begin[seq];
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
 
@@ -542,7 +544,7 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
                                            (int)smem);
     if (err != cudaSuccess) return (int)err;
     const int max_folded = max_rows_per_seq * p.group;
-    dim3 grid((max_folded + BM - 1) / BM, num_kv_heads, num_seqs);
+    dim3 grid(((max_folded + BM - 1) / BM) * num_kv_heads, 1, num_seqs);
     if (cudaError_t err = tb_launch_pdl(attention_tcgen05_kernel, grid, dim3(kThreads), smem, stream, *map, p))
         return (int)err;
     return tb_launch_status();
