@@ -25,11 +25,17 @@ using namespace tbtma;
 
 constexpr int D = 64;            // head_dim this kernel is built for
 constexpr int BM = 128;          // folded query rows per CTA
-constexpr int BN = 128;          // keys per block
+#ifndef TB_ATTN_BN
+#define TB_ATTN_BN 128
+#endif
+constexpr int BN = TB_ATTN_BN;   // keys per block: 128 (two CTAs per SM) or 64 (three)
 constexpr int STAGES = 2;        // K/V ring depth
 constexpr int kThreads = 192;         // warps 0..3 softmax, warp 4 issuer, warp 5 TMA producer
-constexpr uint32_t kTileBytes = BN * D * 2;           // 16 KiB: one K or V block, also the Q tile and half a P tile
-constexpr uint32_t kTmemColumns = 256;                // S: columns 0..127, O_blk: columns 128..191
+constexpr uint32_t kTileBytes = BM * D * 2;           // 16 KiB: the Q tile, and the P tile of 64 keys (128 rows x 128 bytes)
+constexpr uint32_t kKVTileBytes = BN * D * 2;         // one K or V block
+constexpr int kPTiles = BN / 64;                      // P tiles of 64 keys per block
+constexpr int kCtasPerSm = BN == 128 ? 2 : 3;
+constexpr uint32_t kTmemColumns = BN == 128 ? 256 : 128;   // S: columns 0..BN-1, O: the 64 columns after them
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
 
@@ -160,7 +166,7 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 }
 
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
     // barriers: k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full, p_ready, o_full, s_free.
@@ -193,8 +199,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
 
     const uint32_t q_tile = smem_u32(smem);
-    const uint32_t p_tile = q_tile + kTileBytes;                // two 16 KiB halves (keys 0..63 | 64..127)
-    const uint32_t kv_tiles = p_tile + 2 * kTileBytes;          // [stage][K | V]
+    const uint32_t p_tile = q_tile + kTileBytes;                // kPTiles tiles of 16 KiB (keys 0..63 | 64..127)
+    const uint32_t kv_tiles = p_tile + kPTiles * kTileBytes;    // [stage][K | V]
     const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[STAGES]);
     const uint32_t v_full = smem_u32(&bars[2 * STAGES]), v_empty = smem_u32(&bars[3 * STAGES]);
     const uint32_t s_full = smem_u32(&bars[4 * STAGES]), p_ready = s_full + 8, o_full = s_full + 16;
@@ -268,18 +274,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 page = logical <= last_page ? table[logical] : 0;
                 in_page = key & (p.page_size - 1);
             }
-            const uint32_t dst = kv_tiles + s * 2 * kTileBytes + (uint32_t)(lane * rows_per_copy) * 128;
+            const uint32_t dst = kv_tiles + s * 2 * kKVTileBytes + (uint32_t)(lane * rows_per_copy) * 128;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
                 const uint32_t full = (which ? v_full : k_full) + 8 * s, empty = (which ? v_empty : k_empty) + 8 * s;
                 int go = 1;
                 if (lane == 0) {
                     go = mbar_wait(empty, ((it / STAGES) & 1) ^ 1, &abort_flag) ? 1 : 0;
-                    if (go) mbar_expect_tx(full, kTileBytes);
+                    if (go) mbar_expect_tx(full, kKVTileBytes);
                 }
                 go = __shfl_sync(0xffffffffu, go, 0);            // also orders the announcement before the copies
                 if (!go) { ok = false; break; }
-                if (lane < copies) tma_load_kv(dst + which * kTileBytes, &cache_map, full, in_page, kv_head, which, page);
+                if (lane < copies) tma_load_kv(dst + which * kKVTileBytes, &cache_map, full, in_page, kv_head, which, page);
             }
         }
         if (!ok && lane == 0) {
@@ -295,7 +301,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 const int s = j % STAGES;
                 if (!mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t k_tile = kv_tiles + s * 2 * kTileBytes;
+                const uint32_t k_tile = kv_tiles + s * 2 * kKVTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
                     umma(tmem_s, desc_sw128(q_tile + kk * 32, 1), desc_sw128(k_tile + kk * 32, 1), idesc_qk, kk != 0);
@@ -315,7 +321,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kTileBytes + kTileBytes;
+                const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kKVTileBytes + kKVTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
                     umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
@@ -374,13 +380,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             tmem_load_32_nowait(tmem_s + lane_base + 32, cb);
             reduce_max(ca, 0);
             tmem_wait_ld();
-            tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
-            reduce_max(cb, 1);
-            tmem_wait_ld();
-            tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
-            reduce_max(ca, 2);
-            tmem_wait_ld();
-            reduce_max(cb, 3);
+            if (BN == 128) {
+                tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
+                reduce_max(cb, 1);
+                tmem_wait_ld();
+                tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
+                reduce_max(ca, 2);
+                tmem_wait_ld();
+                reduce_max(cb, 3);
+            } else {
+                reduce_max(cb, 1);
+            }
             const float raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             const float block_max = raw_max > 0.5f * kMasked ? raw_max * p.scale_log2 : kMasked;
             // P_{j-1} V_{j-1} must be complete before the P tile is overwritten (and before O is rescaled)
@@ -443,15 +453,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             tmem_load_32_nowait(tmem_s + lane_base + 32, cb);
             emit(ca, 0);
             tmem_wait_ld();
-            tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
-            emit(cb, 1);
-            tmem_wait_ld();
-            tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
-            emit(ca, 2);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(s_free);                       // S has been read: the issuer may start the next block's scores
-            emit(cb, 3);
+            if (BN == 128) {
+                tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
+                emit(cb, 1);
+                tmem_wait_ld();
+                tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
+                emit(ca, 2);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(s_free);                   // S has been read: the issuer may start the next block's scores
+                emit(cb, 3);
+            } else {
+                tc_fence_before();
+                mbar_arrive(s_free);
+                emit(cb, 1);
+            }
             {
                 float lo, hi;
                 unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), lo, hi);
@@ -539,7 +555,7 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.scale_log2 = scale * kLog2e;
-    const size_t smem = (size_t)(1 + 2 + 2 * STAGES) * kTileBytes;
+    const size_t smem = (size_t)(1 + kPTiles) * kTileBytes + (size_t)2 * STAGES * kKVTileBytes;
     cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)smem);
     if (err != cudaSuccess) return (int)err;
