@@ -261,14 +261,15 @@ __global__ void __launch_bounds__(WARPS * 32, (D <= 64 ? 2 : 1)) attention_tiles
     constexpr int NT = WARPS * 32;
     constexpr bool QREG = D <= 128;  // Q fragments live in registers unless the head is very wide
     extern __shared__ __align__(128) unsigned char smem[];
-    const int seq = blockIdx.z, kv_head = blockIdx.y;
+    // blockIdx.x runs over (tile rank, kv head), the kv head fastest: CTAs start in index order, so the heavy
+    // tiles (late rows see the most keys) of all heads start first and the light ones fill the gaps
+    const int seq = blockIdx.z, kv_head = blockIdx.x % p.num_kv_heads, tile_rank = blockIdx.x / p.num_kv_heads;
     const int first_row = p.row_start[seq];
     const int q_len = p.row_start[seq + 1] - first_row;
     const int n_rows = q_len * p.group;
-    // heavy tiles (late rows see the most keys) are scheduled first
     const int n_tiles = (n_rows + BM - 1) / BM;
-    if (n_rows <= 16 || (int)blockIdx.x >= n_tiles) return;  // short sequences belong to the decode kernel
-    const int r0 = (n_tiles - 1 - blockIdx.x) * BM;
+    if (n_rows <= 16 || tile_rank >= n_tiles) return;  // short sequences belong to the decode kernel
+    const int r0 = (n_tiles - 1 - tile_rank) * BM;
     const int begin = p.seq_begin[seq];
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -758,7 +759,7 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
             cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess) return (int)err;
         }
-        dim3 grid((max_rows_per_seq + BM - 1) / BM, p.num_kv_heads, num_seqs);
+        dim3 grid(((max_rows_per_seq + BM - 1) / BM) * p.num_kv_heads, 1, num_seqs);
         kernel<<<grid, WARPS * 32, smem, stream>>>(p);
         if (int status = tb_launch_status()) return status;
     }
