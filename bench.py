@@ -275,7 +275,8 @@ def run_ours(args):
                    "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
                    "decode_context": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (2.47 GB of weights read every step)"},
+                   "l2": "inputs larger than L2 (2.47 GB of weights read every step)",
+                   "decode_steps": "CUDA graph per step, launched one ahead of the token read-back"},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "of": pk["source"]},
