@@ -125,8 +125,9 @@ def swiglu(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Te
 
 
 def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=torch.float64,
-            round_to: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence (layer order of src/cuda/dense_decoder.rs:644-831)."""
+            round_to: Optional[torch.dtype] = None, head_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence (layer order of src/cuda/dense_decoder.rs:644-831); with
+    ``head_rows`` only those rows go through the final norm and the head (src/cuda/dense_decoder.rs:784-823)."""
     w = {name: t.to(dtype) for name, t in tensors.items()}
     nh, nkv = config["num_attention_heads"], config.get("num_key_value_heads") or config["num_attention_heads"]
     d = config.get("head_dim") or config["hidden_size"] // nh
@@ -154,6 +155,8 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int
         pending = swiglu(m, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"],
                          w[f"{p}.mlp.down_proj.weight"], round_to)
     h = h if pending is None else h + pending
+    if head_rows is not None:
+        h = h[list(head_rows)]
     final = rms_norm(h, w["model.norm.weight"], eps, round_to)
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
     return final @ head.T

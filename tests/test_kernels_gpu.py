@@ -446,7 +446,8 @@ def test_silu_mul_interleaved_layout():
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n, k", [(16, 32), (48, 96), (160, 64), (2048, 2048), (384, 320), (1024, 4096)])
+@pytest.mark.parametrize("n, k", [(16, 32), (48, 96), (160, 64), (2048, 2048), (384, 320), (1024, 4096),
+                                  (16384, 256), (5024, 96)])       # the last two: 32-feature tiles, several per CTA
 def test_decode_linear_plain_and_f32(m, n, k):
     from tesseract_b200 import kernels
 
@@ -471,7 +472,7 @@ def test_decode_linear_plain_and_f32(m, n, k):
     assert torch.equal(alone[0], out32[m - 1])
 
 
-@pytest.mark.parametrize("m, n, k, eps", [(1, 64, 64, 1e-5), (7, 160, 96, 1e-6), (8, 3072, 2048, 1e-5),
+@pytest.mark.parametrize("m, n, k, eps", [(1, 64, 64, 1e-5), (7, 160, 96, 1e-6), (8, 3072, 2048, 1e-5), (6, 16384, 2048, 1e-5),
                                           (13, 512, 1024, 1e-3), (16, 256, 2048, 1e-5), (5, 64, 4096, 1e-5)])
 def test_decode_linear_fused_norm_and_swiglu(m, n, k, eps):
     from tesseract_b200 import kernels

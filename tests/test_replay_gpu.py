@@ -151,3 +151,41 @@ def test_first_tokens(engines, plains, dtype):
                 steps[-1] = (steps[-1][0], [rid])
         got = replay(engines(name, dtype), steps)
         compare(got, plains(name), REL[dtype], f"{name}/{dtype}/first-tokens")
+
+
+def test_one_layer_of_the_1b_sizes_in_bfloat16(tmp_path):
+    """The kernels that only the full-size model reaches (tcgen05 attention at head size 64, the tcgen05 gate/up
+    product, 32-feature decode tiles, the 128,256-wide head) inside the engine: a one-layer model with the layer
+    sizes of Llama 3.2 1B, a prompt in one step, then decoded tokens, against the plain model."""
+    from tests.helpers import make_model_folder
+    from tests.plain import llama
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    config = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+        "num_hidden_layers": 1, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
+        "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "max_position_embeddings": 131072,
+        "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "bos_token_id": 128000, "eos_token_id": [128001],
+    }
+    folder = make_model_folder(str(tmp_path / "one_layer_1b"), config, "bfloat16", 3)
+    plain_config, tensors = llama.load_folder(folder)
+    tokens = random_tokens(config["vocab_size"], 300, seed=17)
+    want_rows = [270, 299, 300, 301, 302]                       # the prompt's last rows, then decoded positions
+    prompt = 300
+    tokens = tokens + random_tokens(config["vocab_size"], 3, seed=18)
+    hidden = llama.forward(plain_config, tensors, tokens, head_rows=want_rows)
+    model = load_model(folder, dtype="bfloat16")
+    stepper = make_stepper(model, capacity_tokens=512, max_requests=2)
+    assert stepper.cache.admit("r")
+    got = [stepper.step([StepEntry("r", tokens[:prompt], [270, 299])]).float().cpu()]
+    for t in range(prompt, prompt + 3):
+        got.append(stepper.step([StepEntry("r", tokens[t:t + 1], [0])]).float().cpu())
+    got = torch.cat(got)
+    from tesseract_b200 import kernels
+    assert kernels.tcgen05_error() == 0
+    scale = float(hidden.abs().max())
+    assert float((got.double() - hidden).abs().max()) <= 3e-2 * max(1.0, scale)
+    assert (got.argmax(dim=1) == hidden.argmax(dim=1)).float().mean() >= 0.6   # random weights: many near ties
