@@ -243,3 +243,124 @@ class DecodeGraphs:
         """Run one pure-decode step and wait for it; returns (tokens, logits [B, vocab] on the device)."""
         launch = self.launch(entries, temperatures, draws)
         return launch.tokens(), launch.graph.logits[:launch.count]
+
+
+class _ChunkGraph:
+    """Buffers and the captured graph for steps in which one sequence brings ``rows`` prompt tokens."""
+
+    def __init__(self, stepper: Stepper, rows: int, wants_last: bool, columns: int):
+        cache, device = stepper.cache, stepper.runtime.device
+        self.rows, self.columns = rows, columns
+        self.paged = [i for i, g in enumerate(cache.groups) if g.pool is not None]
+        # int32 block: tokens[rows] positions[rows] begin[1] slot[1] tables[paged][columns]
+        self.ints = 2 * rows + 2 + len(self.paged) * columns
+        self.hosts = [torch.zeros(self.ints, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
+        self.host_events: List[Optional[torch.cuda.Event]] = [None] * HOST_RING
+        self.next_host = 0
+        self.dev = torch.zeros(self.ints, dtype=torch.int32, device=device)
+        d = self.dev
+        tables = {}
+        at = 2 * rows + 2
+        for index in self.paged:
+            tables[index] = d[at:at + columns].view(1, columns)
+            at += columns
+        groups = [GroupView(tables.get(index), cache.page_size if g.pool is not None else 0)
+                  for index, g in enumerate(cache.groups)]
+        self.ctx = StepContext(
+            num_rows=rows, num_seqs=1, token_ids=d[:rows], positions=d[rows:2 * rows],
+            seq_of_row=torch.zeros(rows, dtype=torch.int32, device=device),
+            row_start=torch.tensor([0, rows], dtype=torch.int32, device=device), seq_begin=d[2 * rows:2 * rows + 1],
+            state_slots=d[2 * rows + 1:2 * rows + 2], groups=groups, host_new=[rows], host_begin=(), host_slots=(),
+            max_new=rows, max_context=columns * cache.page_size)
+        self.want_rows = torch.tensor([rows - 1], dtype=torch.int32, device=device) if wants_last else None
+        # capture on harmless metadata: position 0.., the scratch slot, the scratch page
+        host = self.hosts[0].numpy()
+        host[rows:2 * rows] = np.arange(rows, dtype=np.int32)
+        host[2 * rows + 1] = cache.scratch_slot
+        self.dev.copy_(self.hosts[0])
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                stepper.model.forward(self.ctx, cache.bindings, self.want_rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = kernels.launch_count
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()                                 # see _Graph._capture
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = stepper.model.forward(self.ctx, cache.bindings, self.want_rows)
+        finally:
+            if collecting:
+                gc.enable()
+        self.kernels_per_replay = kernels.launch_count - before
+        self.graph = graph
+        torch.cuda.synchronize()
+
+
+class ChunkGraphs:
+    """CUDA-graph replay of prompt portions: a step in which a single sequence brings exactly ``rows`` tokens
+    (the configured portion size) and wants nothing or its last place.  Between two such steps only device
+    metadata differs (token ids, positions, the block table), so the launches of the whole model are replayed
+    instead of issued one by one; at 2,048 rows of the 1B sizes that takes the step from 4.6 to 3.9 ms."""
+
+    def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int):
+        self.stepper = stepper
+        self.rows = rows
+        page = stepper.cache.page_size
+        self.columns = max(1, -(-min(max_sequence_length, stepper.max_positions) // page))
+        self.graphs: Dict[bool, _ChunkGraph] = {}
+        self.replays = 0
+        self.kernels_replayed = 0
+        self.safe = all(getattr(block.mixer, "graph_safe", False) for block in stepper.model.layers)
+
+    def eligible(self, entries: Sequence[StepEntry]) -> bool:
+        if not self.safe or len(entries) != 1:
+            return False
+        entry = entries[0]
+        if len(entry.tokens) != self.rows or list(entry.want) not in ([], [self.rows - 1]):
+            return False
+        cache = self.stepper.cache
+        return cache.is_live(entry.request) and cache.length(entry.request) + self.rows <= self.columns * cache.page_size
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        stepper, cache = self.stepper, self.stepper.cache
+        stepper._validate(entries)
+        entry = entries[0]
+        rows = self.rows
+        wants_last = bool(entry.want)
+        graph = self.graphs.get(wants_last)
+        if graph is None:
+            graph = _ChunkGraph(stepper, rows, wants_last, self.columns)
+            self.graphs[wants_last] = graph
+        begin = cache.length(entry.request)
+        cache.extend(entry.request, rows)
+        index = graph.next_host
+        graph.next_host = (index + 1) % HOST_RING
+        if graph.host_events[index] is not None:
+            graph.host_events[index].synchronize()
+        host = graph.hosts[index].numpy()
+        host[:rows] = np.asarray(entry.tokens, dtype=np.int32)
+        host[rows:2 * rows] = np.arange(begin, begin + rows, dtype=np.int32)
+        host[2 * rows] = begin
+        slot = cache.slot(entry.request)
+        host[2 * rows + 1] = slot
+        used = -(-(begin + rows) // cache.page_size)              # pages this step can touch
+        at = 2 * rows + 2
+        for group_index in graph.paged:
+            host[at:at + used] = cache.block_table_rows(group_index, [slot], used)[0]
+            at += graph.columns
+        graph.dev.copy_(graph.hosts[index], non_blocking=True)
+        copied = torch.cuda.Event()
+        copied.record()
+        graph.host_events[index] = copied
+        graph.graph.replay()
+        cache.commit(entry.request, rows)
+        stepper.steps_run += 1
+        self.replays += 1
+        self.kernels_replayed += graph.kernels_per_replay
+        return graph.logits

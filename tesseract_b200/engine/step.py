@@ -82,6 +82,7 @@ class Stepper:
         self._staging = _Staging(self.runtime.device)
         self.steps_run = 0
         self.graphs = None          # set by enable_graphs()
+        self.chunk_graphs = None    # set by enable_graphs(chunk_rows=...)
         self._sampler = None
 
     # ------------------------------------------------------------------ validation
@@ -98,10 +99,13 @@ class Stepper:
             count = len(entry.tokens)
             if count == 0:
                 raise StepError(f"request {entry.request!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < self.vocab_size:
-                    raise StepError(f"token id {token} of request {entry.request!r} is outside the vocabulary "
-                                    f"of {self.vocab_size}")
+            ids = np.asarray(entry.tokens)
+            if ids.dtype.kind not in "iu" or ids.ndim != 1:
+                raise StepError(f"the tokens of request {entry.request!r} are not a list of integers")
+            low, high = int(ids.min()), int(ids.max())
+            if low < 0 or high >= self.vocab_size:
+                raise StepError(f"token id {low if low < 0 else high} of request {entry.request!r} is outside the "
+                                f"vocabulary of {self.vocab_size}")
             for place in entry.want:
                 if not 0 <= int(place) < count:
                     raise StepError(f"wanted place {place} of request {entry.request!r} is outside its "
@@ -144,7 +148,10 @@ class Stepper:
         return ctx, (device[6] if want_rows.size else None), int(want_rows.size)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run one batch; return float32 logits ``[wanted, vocab]`` on the device, or ``None``."""
+        """Run one batch; return float32 logits ``[wanted, vocab]`` on the device, or ``None``.  (A replayed
+        prompt portion returns a buffer that the next such step overwrites: read it before that.)"""
+        if self.chunk_graphs is not None and self.chunk_graphs.eligible(entries):
+            return self.chunk_graphs.step(entries)
         self._validate(entries)
         for entry in entries:
             self.cache.extend(entry.request, len(entry.tokens))
@@ -156,11 +163,15 @@ class Stepper:
         return logits
 
     # ------------------------------------------------------------------ step + sampling
-    def enable_graphs(self, max_batch: int) -> None:
-        """Replay pure decode steps as CUDA graphs from now on (if every mixer allows it)."""
-        from .graph import DecodeGraphs
+    def enable_graphs(self, max_batch: int, chunk_rows: Optional[int] = None,
+                      max_sequence_length: Optional[int] = None) -> None:
+        """Replay pure decode steps as CUDA graphs from now on (if every mixer allows it), and, with
+        ``chunk_rows``, steps in which a single sequence brings exactly that many prompt tokens."""
+        from .graph import ChunkGraphs, DecodeGraphs
 
         self.graphs = DecodeGraphs(self, max_batch)
+        if chunk_rows is not None and chunk_rows > 16:
+            self.chunk_graphs = ChunkGraphs(self, chunk_rows, max_sequence_length or self.max_positions)
 
     def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float], top_ps: Sequence[float],
                         draws: Sequence[float]) -> List[int]:

@@ -189,3 +189,41 @@ def test_one_layer_of_the_1b_sizes_in_bfloat16(tmp_path):
     scale = float(hidden.abs().max())
     assert float((got.double() - hidden).abs().max()) <= 3e-2 * max(1.0, scale)
     assert (got.argmax(dim=1) == hidden.argmax(dim=1)).float().mean() >= 0.6   # random weights: many near ties
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_prompt_portions_equal_ordinary_steps(model_folders, dtype):
+    """A prompt fed in portions of the configured size goes through a captured CUDA graph (only device metadata
+    changes between such steps); the logits are those of the same portions run launch by launch, bit for bit,
+    for two requests whose portions interleave (different pages, different positions, the same graph)."""
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    folder = model_folders("c")
+    config, _ = llama.load_folder(folder) if False else (TINY["c"], None)
+    model = load_model(folder, dtype=dtype)
+    chunk = 24
+    tokens = {"p": random_tokens(config["vocab_size"], 3 * chunk + 5, seed=31),
+              "q": random_tokens(config["vocab_size"], 2 * chunk, seed=32)}
+
+    def run(graphs):
+        stepper = make_stepper(model, capacity_tokens=512, max_requests=2)
+        if graphs:
+            stepper.enable_graphs(2, chunk_rows=chunk, max_sequence_length=256)
+        out = []
+        for r in tokens:
+            assert stepper.cache.admit(r)
+        at = {"p": 0, "q": 0}
+        for r in ("p", "q", "p", "q", "p", "p"):                 # portions of the two requests in turn
+            n = min(chunk, len(tokens[r]) - at[r])
+            want = [n - 1] if at[r] + n >= len(tokens[r]) or r == "q" else []
+            logits = stepper.step([StepEntry(r, tokens[r][at[r]:at[r] + n], want)])
+            at[r] += n
+            if logits is not None:
+                out.append(logits.clone())
+        return torch.cat(out), stepper
+
+    want, _ = run(False)
+    got, stepper = run(True)
+    assert stepper.chunk_graphs.replays == 5 and len(stepper.chunk_graphs.graphs) == 2   # the 5-token tail ran eagerly
+    assert torch.equal(got, want)
+    stepper.cache.check()
