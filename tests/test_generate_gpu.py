@@ -173,3 +173,38 @@ def test_steps_launched_ahead_give_the_same_tokens_as_ordinary_steps(model_folde
     assert ahead.stepper.graphs.replays > 20
     assert ahead.stepper.cache.used_pages() == 0
     ahead.stepper.cache.check()
+
+
+def test_many_requests_under_load_get_the_same_tokens_with_and_without_graphs(model_folders):
+    """Forty requests of random lengths and options through a small cache (requests wait for pages, portions
+    replay as graphs, decode steps are launched ahead, batches change shape all the time) against the same
+    requests with every step run launch by launch: the same tokens and finish reasons, and every page returned."""
+    import random
+
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders("b")
+    config, _ = llama.load_folder(folder)
+    rng = random.Random(5)
+    prompts, params = [], []
+    for i in range(40):
+        prompts.append([rng.randrange(config["vocab_size"]) for _ in range(rng.choice([1, 2, 7, 31, 32, 33, 64, 90, 120]))])
+        greedy = rng.random() < 0.5
+        params.append(SamplingParams(max_tokens=rng.choice([1, 2, 5, 17, 40]), temperature=0.0 if greedy else 0.8,
+                                     seed=100 + i, ignore_eos=rng.random() < 0.7,
+                                     stop_token_ids=[rng.randrange(config["vocab_size"])] if rng.random() < 0.3 else []))
+    results = []
+    for graphs in (False, True):
+        llm = LLM(folder, dtype="float32", kv_capacity_tokens=640, max_running=6, max_queue=64,
+                  prefill_chunk_tokens=32, max_batch_tokens=96, max_sequence_length=256, cuda_graphs=graphs)
+        alone = [rng2.randrange(config["vocab_size"]) for rng2 in [random.Random(9)] for _ in range(100)]
+        outs = llm.generate([alone], SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))   # portions replay
+        outs += llm.generate(prompts, params)
+        results.append([(o.token_ids, o.finish_reason) for o in outs])
+        assert llm.stepper.cache.used_pages() == 0
+        llm.stepper.cache.check()
+        if graphs:
+            counts = (llm.stepper.graphs.replays, llm.stepper.chunk_graphs.replays, llm.stepper.steps_run)
+            assert counts[0] > 10 and counts[1] >= 1, counts
+    assert results[0] == results[1]
+    assert {reason for _, reason in results[0]} >= {"length"}
