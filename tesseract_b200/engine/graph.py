@@ -246,37 +246,43 @@ class DecodeGraphs:
 
 
 class _ChunkGraph:
-    """Buffers and the captured graph for steps in which one sequence brings ``rows`` prompt tokens."""
+    """Buffers and the captured graph for steps in which one sequence brings ``rows`` prompt tokens and up to
+    ``decodes`` others one decoded token each (rows ``rows`` .. ``rows + decodes - 1``, all wanted)."""
 
-    def __init__(self, stepper: Stepper, rows: int, wants_last: bool, columns: int):
+    def __init__(self, stepper: Stepper, rows: int, decodes: int, wants_last: bool, columns: int):
         cache, device = stepper.cache, stepper.runtime.device
-        self.rows, self.columns = rows, columns
+        self.rows, self.decodes, self.columns = rows, decodes, columns
+        total, seqs = rows + decodes, 1 + decodes
         self.paged = [i for i, g in enumerate(cache.groups) if g.pool is not None]
-        # int32 block: tokens[rows] positions[rows] begin[1] slot[1] tables[paged][columns]
-        self.ints = 2 * rows + 2 + len(self.paged) * columns
+        # int32 block: tokens[total] positions[total] begin[seqs] slot[seqs]; block tables apart (only the columns
+        # in use are copied)
+        self.ints = 2 * total + 2 * seqs
         self.hosts = [torch.zeros(self.ints, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
+        self.host_tables = [[torch.zeros((seqs, columns), dtype=torch.int32, pin_memory=True) for _ in self.paged]
+                            for _ in range(HOST_RING)]
         self.host_events: List[Optional[torch.cuda.Event]] = [None] * HOST_RING
         self.next_host = 0
         self.dev = torch.zeros(self.ints, dtype=torch.int32, device=device)
+        self.dev_tables = [torch.zeros((seqs, columns), dtype=torch.int32, device=device) for _ in self.paged]
         d = self.dev
-        tables = {}
-        at = 2 * rows + 2
-        for index in self.paged:
-            tables[index] = d[at:at + columns].view(1, columns)
-            at += columns
+        tables = dict(zip(self.paged, self.dev_tables))
         groups = [GroupView(tables.get(index), cache.page_size if g.pool is not None else 0)
                   for index, g in enumerate(cache.groups)]
+        seq_of_row = torch.cat([torch.zeros(rows, dtype=torch.int32),
+                                torch.arange(1, seqs, dtype=torch.int32)]).to(device)
+        row_start = torch.cat([torch.zeros(1, dtype=torch.int32),
+                               torch.arange(rows, total + 1, dtype=torch.int32)]).to(device)
         self.ctx = StepContext(
-            num_rows=rows, num_seqs=1, token_ids=d[:rows], positions=d[rows:2 * rows],
-            seq_of_row=torch.zeros(rows, dtype=torch.int32, device=device),
-            row_start=torch.tensor([0, rows], dtype=torch.int32, device=device), seq_begin=d[2 * rows:2 * rows + 1],
-            state_slots=d[2 * rows + 1:2 * rows + 2], groups=groups, host_new=[rows], host_begin=(), host_slots=(),
-            max_new=rows, max_context=columns * cache.page_size)
-        self.want_rows = torch.tensor([rows - 1], dtype=torch.int32, device=device) if wants_last else None
-        # capture on harmless metadata: position 0.., the scratch slot, the scratch page
+            num_rows=total, num_seqs=seqs, token_ids=d[:total], positions=d[total:2 * total], seq_of_row=seq_of_row,
+            row_start=row_start, seq_begin=d[2 * total:2 * total + seqs],
+            state_slots=d[2 * total + seqs:2 * total + 2 * seqs], groups=groups, host_new=[rows] + [1] * decodes,
+            host_begin=(), host_slots=(), max_new=rows, max_context=columns * cache.page_size)
+        wanted = ([rows - 1] if wants_last else []) + list(range(rows, total))
+        self.want_rows = torch.tensor(wanted, dtype=torch.int32, device=device) if wanted else None
+        # capture on harmless metadata: positions 0.., the scratch slot, the scratch page
         host = self.hosts[0].numpy()
-        host[rows:2 * rows] = np.arange(rows, dtype=np.int32)
-        host[2 * rows + 1] = cache.scratch_slot
+        host[total:total + rows] = np.arange(rows, dtype=np.int32)
+        host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
         self.dev.copy_(self.hosts[0])
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
@@ -303,64 +309,83 @@ class _ChunkGraph:
 
 
 class ChunkGraphs:
-    """CUDA-graph replay of prompt portions: a step in which a single sequence brings exactly ``rows`` tokens
-    (the configured portion size) and wants nothing or its last place.  Between two such steps only device
-    metadata differs (token ids, positions, the block table), so the launches of the whole model are replayed
-    instead of issued one by one; at 2,048 rows of the 1B sizes that takes the step from 4.6 to 3.9 ms."""
+    """CUDA-graph replay of steps with a prompt portion: the first sequence brings exactly ``rows`` tokens (the
+    configured portion size) and wants nothing or its last place; every other sequence brings one decoded token
+    and wants it.  Between two such steps only device metadata differs (token ids, positions, block tables), so
+    the launches of the whole model are replayed instead of issued one by one; at 2,048 rows of the 1B sizes that
+    takes the step from 4.6 to 3.9 ms.  One graph per (decode rows rounded up to a power of two, wants-last);
+    rows that pad the decode part point at the scratch page and the scratch state slot."""
 
-    def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int):
+    def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int, max_decodes: int):
         self.stepper = stepper
         self.rows = rows
+        self.max_decodes = max_decodes
         page = stepper.cache.page_size
         self.columns = max(1, -(-min(max_sequence_length, stepper.max_positions) // page))
-        self.graphs: Dict[bool, _ChunkGraph] = {}
+        self.graphs: Dict[Tuple[int, bool], _ChunkGraph] = {}
         self.replays = 0
         self.kernels_replayed = 0
         self.safe = all(getattr(block.mixer, "graph_safe", False) for block in stepper.model.layers)
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
-        if not self.safe or len(entries) != 1:
+        if not self.safe or not entries or len(entries) - 1 > self.max_decodes:
             return False
-        entry = entries[0]
-        if len(entry.tokens) != self.rows or list(entry.want) not in ([], [self.rows - 1]):
+        first = entries[0]
+        if len(first.tokens) != self.rows or list(first.want) not in ([], [self.rows - 1]):
+            return False
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries[1:]):
             return False
         cache = self.stepper.cache
-        return cache.is_live(entry.request) and cache.length(entry.request) + self.rows <= self.columns * cache.page_size
+        limit = self.columns * cache.page_size
+        return all(cache.is_live(e.request) and cache.length(e.request) + len(e.tokens) <= limit for e in entries)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         stepper, cache = self.stepper, self.stepper.cache
         stepper._validate(entries)
-        entry = entries[0]
-        rows = self.rows
-        wants_last = bool(entry.want)
-        graph = self.graphs.get(wants_last)
+        rows, decodes = self.rows, len(entries) - 1
+        wants_last = bool(entries[0].want)
+        bucket = 0 if decodes == 0 else min(_next_pow2(decodes), max(self.max_decodes, decodes))
+        graph = self.graphs.get((bucket, wants_last))
         if graph is None:
-            graph = _ChunkGraph(stepper, rows, wants_last, self.columns)
-            self.graphs[wants_last] = graph
-        begin = cache.length(entry.request)
-        cache.extend(entry.request, rows)
+            graph = _ChunkGraph(stepper, rows, bucket, wants_last, self.columns)
+            self.graphs[(bucket, wants_last)] = graph
+        total, seqs = rows + bucket, 1 + bucket
+        begins = [cache.length(e.request) for e in entries]
+        for entry in entries:
+            cache.extend(entry.request, len(entry.tokens))
         index = graph.next_host
         graph.next_host = (index + 1) % HOST_RING
         if graph.host_events[index] is not None:
             graph.host_events[index].synchronize()
         host = graph.hosts[index].numpy()
-        host[:rows] = np.asarray(entry.tokens, dtype=np.int32)
-        host[rows:2 * rows] = np.arange(begin, begin + rows, dtype=np.int32)
-        host[2 * rows] = begin
-        slot = cache.slot(entry.request)
-        host[2 * rows + 1] = slot
-        used = -(-(begin + rows) // cache.page_size)              # pages this step can touch
-        at = 2 * rows + 2
-        for group_index in graph.paged:
-            host[at:at + used] = cache.block_table_rows(group_index, [slot], used)[0]
-            at += graph.columns
+        slots = [cache.slot(e.request) for e in entries]
+        host[:rows] = np.asarray(entries[0].tokens, dtype=np.int32)
+        host[total:total + rows] = np.arange(begins[0], begins[0] + rows, dtype=np.int32)
+        host[rows:total] = 0
+        host[total + rows:2 * total] = 0
+        host[2 * total:2 * total + seqs] = 0
+        host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
+        if decodes:
+            host[rows:rows + decodes] = [int(e.tokens[0]) for e in entries[1:]]
+            host[total + rows:total + rows + decodes] = begins[1:]
+        host[2 * total:2 * total + 1 + decodes] = begins
+        host[2 * total + seqs:2 * total + seqs + 1 + decodes] = slots
+        used = min(graph.columns, -(-max(b + len(e.tokens) for b, e in zip(begins, entries)) // cache.page_size))
         graph.dev.copy_(graph.hosts[index], non_blocking=True)
+        for k, group_index in enumerate(graph.paged):
+            table = graph.host_tables[index][k].numpy()
+            table[:1 + decodes, :used] = cache.block_table_rows(group_index, slots, used)
+            table[1 + decodes:, :used] = 0
+            graph.dev_tables[k][:, :used].copy_(graph.host_tables[index][k][:, :used], non_blocking=True)
         copied = torch.cuda.Event()
         copied.record()
         graph.host_events[index] = copied
         graph.graph.replay()
-        cache.commit(entry.request, rows)
+        for entry in entries:
+            cache.commit(entry.request, len(entry.tokens))
         stepper.steps_run += 1
         self.replays += 1
         self.kernels_replayed += graph.kernels_per_replay
-        return graph.logits
+        if graph.logits is None:
+            return None
+        return graph.logits[:(1 if wants_last else 0) + decodes]

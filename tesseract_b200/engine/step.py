@@ -171,7 +171,7 @@ class Stepper:
 
         self.graphs = DecodeGraphs(self, max_batch)
         if chunk_rows is not None and chunk_rows > 16:
-            self.chunk_graphs = ChunkGraphs(self, chunk_rows, max_sequence_length or self.max_positions)
+            self.chunk_graphs = ChunkGraphs(self, chunk_rows, max_sequence_length or self.max_positions, max_batch)
 
     def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float], top_ps: Sequence[float],
                         draws: Sequence[float]) -> List[int]:

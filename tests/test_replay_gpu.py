@@ -227,3 +227,43 @@ def test_replayed_prompt_portions_equal_ordinary_steps(model_folders, dtype):
     assert stepper.chunk_graphs.replays == 5 and len(stepper.chunk_graphs.graphs) == 2   # the 5-token tail ran eagerly
     assert torch.equal(got, want)
     stepper.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_portions_beside_decoded_tokens_equal_ordinary_steps(model_folders, dtype):
+    """A prompt portion beside one to three decoded tokens of other requests (the common step of continuous
+    batching) replays as a graph too, padded to a power of two of decode rows; bit-equal to launch by launch."""
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    folder = model_folders("c")
+    config = TINY["c"]
+    model = load_model(folder, dtype=dtype)
+    chunk = 24
+    long_prompt = random_tokens(config["vocab_size"], 4 * chunk, seed=41)
+    others = {name: random_tokens(config["vocab_size"], n, seed=50 + n) for name, n in (("x", 9), ("y", 40), ("z", 17))}
+    feed = {name: random_tokens(config["vocab_size"], 8, seed=60 + len(name) + ord(name)) for name in others}
+
+    def run(graphs):
+        stepper = make_stepper(model, capacity_tokens=512, max_requests=4)
+        if graphs:
+            stepper.enable_graphs(4, chunk_rows=chunk, max_sequence_length=256)
+        for name, prompt in others.items():
+            assert stepper.cache.admit(name)
+            stepper.step([StepEntry(name, prompt, [])])
+        assert stepper.cache.admit("p")
+        out = []
+        live = ["x", "y", "z"]
+        for k in range(4):                                      # portions of p beside 3, 3, 2, 1 decoded tokens
+            entries = [StepEntry("p", long_prompt[k * chunk:(k + 1) * chunk], [chunk - 1] if k == 3 else [])]
+            entries += [StepEntry(name, [feed[name][k]], [0]) for name in live]
+            out.append(stepper.step(entries).clone())
+            if k >= 1:
+                stepper.cache.release(live.pop())
+        return torch.cat(out), stepper
+
+    want, _ = run(False)
+    got, stepper = run(True)
+    assert stepper.chunk_graphs.replays == 4
+    assert sorted(stepper.chunk_graphs.graphs) == [(1, True), (2, False), (4, False)]
+    assert torch.equal(got, want)
+    stepper.cache.check()
