@@ -20,12 +20,17 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int BM = 128, BK = 64;
+// Tiles of 128 x 256 with a four-stage ring; products of at most 128 rows (one row of tiles) take 128 x 128 tiles
+// with six stages instead, so that twice as many SMs stream the weights.
+template <int BN>
+constexpr int kStages = BN == 256 ? 4 : 6;
 constexpr int kThreads = 256;
 constexpr uint32_t kATileBytes = BM * BK * 2;   // 16 KiB
-constexpr uint32_t kBTileBytes = BN * BK * 2;   // 32 KiB
-constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
-constexpr uint32_t kTmemColumns = 512;   // two accumulators of BN columns
+template <int BN>
+constexpr uint32_t kStageBytes = kATileBytes + BN * BK * 2;
+template <int BN>
+constexpr uint32_t kTmemColumns = 2 * BN;   // two accumulators of BN columns
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -149,10 +154,13 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
 // Persistent: a CTA per SM walks over the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tiles that are
 // neighbours in time share a panel of W and the rows of A, which then come from L2).  Two accumulators of 256
 // columns in tensor memory: while the epilogue warps drain one tile, the products of the next fill the other.
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
+    constexpr int STAGES = kStages<BN>;
+    constexpr uint32_t kStageBytes = ::kStageBytes<BN>;
+    constexpr uint32_t kTmemColumns = ::kTmemColumns<BN>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -336,9 +344,11 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
     if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16 != 0 || a_stride % 8 != 0 || w_stride % 8 != 0 ||
         out_stride % 8 != 0)
         return TB_ERR_BAD_ALIGN;
+    // one row of tiles: narrower tiles, so that twice as many SMs stream the weights
+    const int bn = M <= BM ? 128 : 256;
     CUtensorMap map_a, map_b;
     if (int status = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_stride, BM)) return status;
-    if (int status = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, BN)) return status;
+    if (int status = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, bn)) return status;
     GemmParams p;
     p.out = out;
     p.out_stride = out_stride;
@@ -346,8 +356,7 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
     p.N = N;
     p.K = K;
     p.error = error;
-    const size_t smem = (size_t)STAGES * kStageBytes + 1024;
-    const int total_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int total_tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
@@ -355,18 +364,24 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
     }
     dim3 grid(total_tiles < sms ? total_tiles : sms);
+#define TB_LAUNCH_BN(E, W)                                                                                    \
+    {                                                                                                         \
+        const size_t smem = (size_t)kStages<W> * kStageBytes<W> + 1024;                                       \
+        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<E, W>,                                     \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        if (err != cudaSuccess) return (int)err;                                                              \
+        err = tb_launch_pdl(gemm_tcgen05_kernel<E, W>, grid, dim3(kThreads), smem, stream, map_a, map_b, p);  \
+        if (err != cudaSuccess) return (int)err;                                                              \
+    }
 #define TB_LAUNCH(E)                                                                                          \
     {                                                                                                         \
-        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                               (int)smem);                                                    \
-        if (err != cudaSuccess) return (int)err;                                                              \
-        err = tb_launch_pdl(gemm_tcgen05_kernel<E>, grid, dim3(kThreads), smem, stream, map_a, map_b, p);     \
-        if (err != cudaSuccess) return (int)err;                                                              \
+        if (bn == 128) TB_LAUNCH_BN(E, 128) else TB_LAUNCH_BN(E, 256)                                         \
     }
     if (epilogue == EPI_BF16) TB_LAUNCH(EPI_BF16)
     else if (epilogue == EPI_SWIGLU) TB_LAUNCH(EPI_SWIGLU)
     else if (epilogue == EPI_F32) TB_LAUNCH(EPI_F32)
     else return TB_ERR_BAD_SIZE;
 #undef TB_LAUNCH
+#undef TB_LAUNCH_BN
     return tb_launch_status();
 }

@@ -387,9 +387,10 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Ten
 
 PRO_NONE, PRO_NORM, PRO_ADD_NORM = 0, 1, 2
 EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
-# From this many rows on, gate/up + SwiGLU in one tcgen05 GEMM beats the library product plus the activation kernel
-# (measured at 128 rows and more: 20.7 against 23.5 us at 128, 100 against 114 us at 2,048).
-FUSED_GATE_UP_MIN_ROWS = 128
+# From this many rows on (the skinny decode product takes up to 16), gate/up + SwiGLU in one tcgen05 GEMM beats the
+# library product plus the activation kernel: a decode step of 32 rows 1.48 -> 1.42 ms, of 64 rows 1.91 -> 1.89 ms
+# with the 128-wide tiles that products of at most 128 rows get; 100 against 114 us per product at 2,048 rows.
+FUSED_GATE_UP_MIN_ROWS = 17
 
 
 def decode_linear_supported(rows: int, out_features: int, in_features: int, prologue: int = PRO_NONE) -> bool:

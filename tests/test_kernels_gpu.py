@@ -529,7 +529,8 @@ def test_decode_linear_refuses_other_sizes():
 
 
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (1, 256, 64), (130, 264, 72),
-                                     (2048, 3072, 2048), (333, 1000, 520), (77, 16, 8)])
+                                     (2048, 3072, 2048), (333, 1000, 520), (77, 16, 8), (64, 1000, 520),
+                                     (96, 40000, 1024)])
 def test_gemm_tcgen05(m, n, k):
     from tesseract_b200 import kernels
 
