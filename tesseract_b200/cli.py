@@ -51,6 +51,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=None)
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--check-weights", action="store_true",
+                   help="after loading, read the final norm's weight back from the device and compare it with the "
+                        "checkpoint bit by bit (the reference's checkpoint report, src/cuda/dense_decoder.rs:1429-1463)")
     p.add_argument("--json", action="store_true", help="one JSON object per request on standard output")
     return p
 
@@ -80,6 +83,10 @@ def main(argv=None) -> int:
               prefill_chunk_tokens=args.prefill_chunk_tokens, max_sequence_length=args.max_sequence_length,
               kv_capacity_tokens=args.kv_capacity_tokens, page_size=args.page_size,
               cuda_graphs=not args.no_cuda_graphs)
+    if args.check_weights:
+        from .engine.loading import check_upload
+
+        print(f"weights checked: {check_upload(llm.model, model_path)} matches the checkpoint", file=sys.stderr)
     vocab = read_config_json(model_path)["vocab_size"]
     prompts = list(args.prompt)
     prompts += [[int(t) for t in ids.split(",") if t.strip()] for ids in args.prompt_ids]

@@ -48,6 +48,23 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device_index: int = 0) -
     return DecoderModel(spec, tensors, Runtime(parse_dtype(dtype), device))
 
 
+def check_upload(model: DecoderModel, model_dir: str) -> str:
+    """Read the final norm's weight back from the device and compare it bit by bit with the checkpoint, as the
+    reference's checkpoint report does with ``model.norm.weight`` (src/cuda/dense_decoder.rs:1429-1463).
+    Returns the tensor's name; raises ``RuntimeError`` on a difference."""
+    from ..weights.safetensors_io import SafetensorsSource
+
+    name = model.spec.final_norm.weights.get("weight")
+    on_device = getattr(model.final_norm, "weight", None)
+    if name is None or on_device is None:
+        raise RuntimeError("the model's final norm holds no weight to check")
+    stored = SafetensorsSource(model_dir).tensor(name)
+    same = torch.equal(stored.to(torch.float32).view(torch.int32), on_device.cpu().to(torch.float32).view(torch.int32))
+    if not same:
+        raise RuntimeError(f"{name} read back from the device differs from {model_dir}")
+    return name
+
+
 def make_stepper(model: DecoderModel, *, capacity_tokens: int, page_size: int = 16, max_requests: int = 32,
                  max_step_tokens: int = 4096) -> Stepper:
     """A cache sized for ``capacity_tokens`` and the step function over it."""

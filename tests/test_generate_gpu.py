@@ -113,9 +113,10 @@ def test_command_line_generates(model_folders):
     folder = model_folders("a")
     cmd = [sys.executable, os.path.join(ROOT, "bin", "tesseract"), "--model-path", folder, "--prompt-ids", "5,6,7,8",
            "--random-prompt", "11", "--max-tokens", "4", "--temperature", "0", "--ignore-eos", "--json",
-           "--kv-capacity-tokens", "256", "--max-running", "2", "--dtype", "float32"]
+           "--kv-capacity-tokens", "256", "--max-running", "2", "--dtype", "float32", "--check-weights"]
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stderr
+    assert "weights checked: model.norm.weight" in done.stderr
     records = [json.loads(line) for line in done.stdout.strip().splitlines()]
     assert len(records) == 2 and all(len(r["token_ids"]) == 4 and r["finish_reason"] == "length" for r in records)
     config, tensors = llama.load_folder(folder)
