@@ -33,7 +33,7 @@ class Linear:
             return kernels.gemm_f32_nt(x, self.weight, out)
         if not x.is_cuda:
             raise RuntimeError("tesseract_b200 has no CPU path; tensors must be on a CUDA device")
-        if rows <= 8 and x.stride(1) == 1 and kernels.decode_linear_supported(rows, self.out_features,
+        if rows <= kernels.DECODE_LINEAR_MAX_ROWS and x.stride(1) == 1 and kernels.decode_linear_supported(rows, self.out_features,
                                                                                self.in_features):
             # decode-sized batches: the package's own weight-streaming kernel
             if out is None:
@@ -62,7 +62,7 @@ class Linear:
             epilogue = kernels.EPI_F32 if float32_out else kernels.EPI_BF16
         prologue = kernels.PRO_NORM if deferred.update is None else kernels.PRO_ADD_NORM
         fusable = (not self.runtime.is_float32 and isinstance(deferred.norm, RMSNorm) and not deferred.done
-                   and rows <= 8 and deferred.residual.is_contiguous()
+                   and rows <= kernels.DECODE_LINEAR_NORMED_MAX_ROWS and deferred.residual.is_contiguous()
                    and kernels.decode_linear_supported(rows, self.out_features, self.in_features, prologue))
         if not fusable:
             return None

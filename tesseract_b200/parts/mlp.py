@@ -68,7 +68,7 @@ class SwiGLU(FeedForward):
         rows = x.shape[0]
         activated = torch.empty((rows, self.intermediate_size), dtype=x.dtype, device=x.device)
         proj = self.gate_up_proj
-        if (self.interleaved and not self.runtime.is_float32 and rows <= 8
+        if (self.interleaved and not self.runtime.is_float32 and rows <= kernels.DECODE_LINEAR_MAX_ROWS
                 and kernels.decode_linear_supported(rows, proj.out_features, proj.in_features)):
             return kernels.decode_linear(proj.weight, activated, x=x, epilogue=kernels.EPI_SWIGLU)
         if (self.interleaved and not self.runtime.is_float32 and rows >= kernels.FUSED_GATE_UP_MIN_ROWS
