@@ -189,10 +189,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         float ss[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) ss[r] = 0.0f;
-        // With eight rows and K up to four elements per thread the sums stay in registers between the two
-        // passes and the rows are read once; otherwise the second pass reads them again.
-        const bool keep = MT == 1 && K <= kThreads * 4;
-        float kept[8][4];
+        // With K up to four elements per thread the sums stay in registers between the two passes and the rows are
+        // read once (every CTA reads all rows, so a second reading costs the L2 as much again); otherwise the
+        // second pass reads them again.
+        const bool keep = K <= kThreads * 4;
+        float kept[ROWS][4];
         for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         ss[r0 + r] += c[r][e] * c[r][e];
-                        if (MT == 1) kept[r][e] = c[r][e];
+                        kept[r0 + r][e] = c[r][e];
                     }
                 }
             }
@@ -235,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     const float inv = inv_s[r0 + r];
                     float v[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) v[e] = (MT == 1 && keep) ? kept[r][e] : c[r][e];
+                    for (int e = 0; e < 4; ++e) v[e] = keep ? kept[r0 + r][e] : c[r][e];
                     v[0] *= inv * nw.x;
                     v[1] *= inv * nw.y;
                     v[2] *= inv * nw.z;
@@ -311,17 +312,35 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     __float2bfloat16_rn(act);
             }
         } else {
-            for (int idx = threadIdx.x; idx < TF * ROWS; idx += kThreads) {
-                const int m = idx / TF, f = idx - m * TF;  // consecutive threads write consecutive features
+            // A thread sums two neighbouring features of one batch row: consecutive lanes then read consecutive
+            // batch rows of the partial sums (at most two lanes per bank; one feature per lane along the features
+            // would put 8 or 16 lanes on a bank) and store the pair at once.
+            for (int idx = threadIdx.x; idx < (TF / 2) * ROWS; idx += kThreads) {
+                const int f = 2 * (idx / ROWS), m = idx % ROWS;
                 if (m >= p.M) continue;
-                float sum = 0.0f;
+                float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kWarps; ++w) sum += partial[(size_t)w * TF * ROWS + f * ROWS + m];
-                if (EPI == EPI_F32)
-                    reinterpret_cast<float*>(p.out)[(int64_t)m * p.out_stride + n0 + f] = sum;
-                else
-                    reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + n0 + f] =
-                        __float2bfloat16_rn(sum);
+                for (int w = 0; w < kWarps; ++w) {
+                    sum0 += partial[(size_t)w * TF * ROWS + f * ROWS + m];
+                    sum1 += partial[(size_t)w * TF * ROWS + (f + 1) * ROWS + m];
+                }
+                if (EPI == EPI_F32) {
+                    float* o = reinterpret_cast<float*>(p.out) + (int64_t)m * p.out_stride + n0 + f;
+                    if ((uintptr_t)o % 8 == 0) {
+                        *reinterpret_cast<float2*>(o) = make_float2(sum0, sum1);
+                    } else {
+                        o[0] = sum0;
+                        o[1] = sum1;
+                    }
+                } else {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)m * p.out_stride + n0 + f;
+                    if ((uintptr_t)o % 4 == 0) {
+                        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(sum0, sum1);
+                    } else {
+                        o[0] = __float2bfloat16_rn(sum0);
+                        o[1] = __float2bfloat16_rn(sum1);
+                    }
+                }
             }
         }
         __syncthreads();  // the partial sums are reused by the next tile
@@ -340,25 +359,33 @@ int sm_count() {
 
 // 32-feature tiles where that still gives every SM a tile, else 16-feature tiles.
 bool wide_tiles(int N) { return N % 32 == 0 && N / 32 >= sm_count(); }
-// ring depth: deep for up to eight rows; sixteen rows need the room for their activations and partial sums
-constexpr int stages_for(int nh, int rows8) { return rows8 > 1 ? 3 : nh == 2 ? 5 : 6; }
+// Ring depth: five stages of 32-feature tiles or six of 16-feature tiles per warp for up to eight rows; sixteen rows
+// take four or six where the activations and the partial sums leave the room (their size depends on K), else three.
+constexpr int deep_stages(int nh, int rows8) { return rows8 > 1 ? (nh == 2 ? 4 : 6) : (nh == 2 ? 5 : 6); }
+constexpr int kShallowStages = 3;
 
-size_t smem_bytes(int rows8, bool prologue, int nh, int K) {
+size_t smem_bytes(int rows8, bool prologue, int nh, int K, int stages) {
     const int rows = 8 * rows8, tf = 16 * nh;
     const size_t stage = 1024 * nh + (prologue ? 0 : 512 * rows8);
-    size_t smem = (size_t)kWarps * tf * rows * sizeof(float) + (size_t)kWarps * stages_for(nh, rows8) * stage;
+    size_t smem = (size_t)kWarps * tf * rows * sizeof(float) + (size_t)kWarps * stages * stage;
     if (prologue) smem += (size_t)rows * (K + 32) * 2;
     return smem;
 }
 
-constexpr size_t kMaxSmem = 220 * 1024;
+constexpr size_t kMaxSmem = 227 * 1024;
 
-template <int MT, int PRO, int EPI, int NH>
-int launch_tiles(const LinearParams& p, cudaStream_t stream) {
+// the ring depth that these sizes get, or 0 if even the shallow ring does not fit
+int stages_for(int rows8, bool prologue, int nh, int K) {
+    if (smem_bytes(rows8, prologue, nh, K, deep_stages(nh, rows8)) <= kMaxSmem) return deep_stages(nh, rows8);
+    if (rows8 > 1 && smem_bytes(rows8, prologue, nh, K, kShallowStages) <= kMaxSmem) return kShallowStages;
+    return 0;
+}
+
+template <int MT, int PRO, int EPI, int NH, int STAGES>
+int launch_ring(const LinearParams& p, cudaStream_t stream) {
     constexpr int TF = 16 * NH;
-    const size_t smem = smem_bytes(MT, PRO != PRO_NONE, NH, p.K);
-    if (smem > kMaxSmem) return TB_ERR_BAD_SIZE;
-    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, stages_for(NH, MT)>;
+    const size_t smem = smem_bytes(MT, PRO != PRO_NONE, NH, p.K, STAGES);
+    auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, STAGES>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
@@ -369,6 +396,16 @@ int launch_tiles(const LinearParams& p, cudaStream_t stream) {
     const int grid = (tiles + per_cta - 1) / per_cta;
     cudaError_t err = tb_launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, p);
     return err == cudaSuccess ? tb_launch_status() : (int)err;
+}
+
+template <int MT, int PRO, int EPI, int NH>
+int launch_tiles(const LinearParams& p, cudaStream_t stream) {
+    const int stages = stages_for(MT, PRO != PRO_NONE, NH, p.K);
+    if (stages == deep_stages(NH, MT)) return launch_ring<MT, PRO, EPI, NH, deep_stages(NH, MT)>(p, stream);
+    if constexpr (MT > 1) {
+        if (stages == kShallowStages) return launch_ring<MT, PRO, EPI, NH, kShallowStages>(p, stream);
+    }
+    return TB_ERR_BAD_SIZE;
 }
 
 template <int MT, int PRO, int EPI>
@@ -399,7 +436,7 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
 // 1 if the sizes are ones this kernel takes, else 0 (the caller then uses the general path).
 TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
     if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < 32 || K % 32 != 0) return 0;
-    return smem_bytes(M <= 8 ? 1 : 2, prologue != PRO_NONE, wide_tiles(N) ? 2 : 1, K) <= kMaxSmem;
+    return stages_for(M <= 8 ? 1 : 2, prologue != PRO_NONE, wide_tiles(N) ? 2 : 1, K) != 0;
 }
 
 // x: PRO_NONE only.  res/upd/norm_w/res_out: see LinearParams.  out_stride in elements of the output type.
