@@ -49,6 +49,25 @@ def test_greedy_generation_matches_plain(model_folders, name, lengths, steps, dt
     llm.stepper.cache.check()
 
 
+@pytest.mark.parametrize("name, count", [("a", 13), ("b", 16), ("b", 21)])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_wider_decode_batches_match_plain(model_folders, name, count, graphs):
+    """Thirteen and sixteen decode rows take the sixteen-row form of the weight-streaming products (norm and SwiGLU
+    folded in), twenty-one the products for more rows: each against the plain model, request by request."""
+    from tesseract_b200 import LLM, SamplingParams
+
+    folder = model_folders(name)
+    config, tensors = llama.load_folder(folder)
+    prompts = [random_tokens(config["vocab_size"], 3 + (5 * k) % 11, seed=100 + k) for k in range(count)]
+    llm = LLM(folder, dtype="bfloat16", kv_capacity_tokens=2048, max_running=count, prefill_chunk_tokens=64,
+              max_batch_tokens=256, cuda_graphs=graphs)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))
+    for prompt, out in zip(prompts, outs):
+        assert len(out.token_ids) == 5 and out.finish_reason == "length", out.error
+        check_greedy(config, tensors, prompt, out.token_ids, 3e-2)
+    assert llm.stepper.cache.used_pages() == 0
+
+
 def test_temperature_sampling_is_reproducible_and_follows_the_draws(model_folders):
     from tesseract_b200 import LLM, SamplingParams
 
