@@ -1,8 +1,9 @@
-// Prompt-portion attention on the fifth-generation tensor cores (bfloat16, head_dim 64), over cache pages.
+// Prompt-portion attention on the fifth-generation tensor cores (bfloat16, head_dim 64 or 128), over cache pages.
 //
 // Same mathematics and the same folding of grouped query heads into tile rows as attention_mma.cu (which see):
 // one CTA owns 128 folded rows (query position x head of the group) of one sequence and one kv head, and
-// walks over the sequence's keys in blocks of 128.  Per block:
+// walks over the sequence's keys in blocks of BN (128 for head_dim 64, 64 for head_dim 128).  Per block, for
+// head_dim 64 (head_dim 128: N64 x K128 and N128 x K64, operands cut into 64-element slices along the head size):
 //   S = Q . K^T        tcgen05.mma, M128 x N128 x K64, both operands in shared memory (K-major, 128-byte swizzle),
 //                      accumulator in tensor memory (128 columns)
 //   softmax            four warps, one thread per row: tcgen05.ld of the row, scale, mask, running maximum,
@@ -15,7 +16,7 @@
 // cp.async.bulk.tensor over a five-dimensional tensor map of the cache (no multicast); one lane of warp 4 issues
 // the tensor-core instructions.  Roles meet on mbarriers; every wait is bounded, and a wait that
 // runs out sets *error, stops the other roles, and the CTA still frees its tensor memory.
-// Two CTAs fit on an SM (about 100 KiB of shared memory and 256 tensor-memory columns each), so one CTA's softmax
+// Two CTAs fit on an SM (112 KiB of shared memory and 256 tensor-memory columns each), so one CTA's softmax
 // overlaps the other's products.
 #include "tma.cuh"
 
@@ -23,19 +24,29 @@ namespace {
 
 using namespace tbtma;
 
-constexpr int D = 64;            // head_dim this kernel is built for
 constexpr int BM = 128;          // folded query rows per CTA
 #ifndef TB_ATTN_BN
 #define TB_ATTN_BN 128
 #endif
-constexpr int BN = TB_ATTN_BN;   // keys per block: 128 (two CTAs per SM) or 64 (three)
+// Keys per block for head_dim 64: 128 (two CTAs per SM) or 64 (three).  head_dim 128 takes 64 keys per block, which
+// lets two CTAs share an SM (112 KiB of shared memory and 256 tensor-memory columns each).
+constexpr int kBlockKeys64 = TB_ATTN_BN;
 constexpr int STAGES = 2;        // K/V ring depth
 constexpr int kThreads = 192;         // warps 0..3 softmax, warp 4 issuer, warp 5 TMA producer
-constexpr uint32_t kTileBytes = BM * D * 2;           // 16 KiB: the Q tile, and the P tile of 64 keys (128 rows x 128 bytes)
-constexpr uint32_t kKVTileBytes = BN * D * 2;         // one K or V block
-constexpr int kPTiles = BN / 64;                      // P tiles of 64 keys per block
-constexpr int kCtasPerSm = BN == 128 ? 2 : 3;
-constexpr uint32_t kTmemColumns = BN == 128 ? 256 : 128;   // S: columns 0..BN-1, O: the 64 columns after them
+// A swizzled tile of 128 rows x 64 bfloat16 (128 bytes a row): the unit that Q, P, K and V tiles are made of.  A Q
+// tile is D / 64 of them side by side (dims 0..63 | 64..127), a P tile BN / 64 (keys 0..63 | 64..127); K and V
+// blocks are D / 64 tiles of BN rows each.
+constexpr uint32_t kTileBytes = BM * 128;
+template <int D, int BN>
+struct Shape {
+    static constexpr uint32_t kQBytes = (D / 64) * kTileBytes;
+    static constexpr int kPTiles = BN / 64;
+    static constexpr uint32_t kKVHalfBytes = BN * 128;               // one 64-dim slice of a K or V block
+    static constexpr uint32_t kKVTileBytes = (D / 64) * kKVHalfBytes;   // one K or V block
+    static constexpr int kCtasPerSm = D == 64 && BN == 64 ? 3 : 2;
+    static constexpr uint32_t kTmemColumns = BN + D <= 128 ? 128 : 256;   // S: columns 0..BN-1, O: the D columns after them
+    static constexpr size_t kSmemBytes = (size_t)kQBytes + (size_t)kPTiles * kTileBytes + (size_t)2 * STAGES * kKVTileBytes;
+};
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
 
@@ -166,8 +177,12 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 }
 
 
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+template <int D, int BN>
+__global__ void __launch_bounds__(kThreads, (Shape<D, BN>::kCtasPerSm))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
+    using S = Shape<D, BN>;
+    constexpr uint32_t kKVTileBytes = S::kKVTileBytes, kKVHalfBytes = S::kKVHalfBytes, kTmemColumns = S::kTmemColumns;
+    constexpr int kPTiles = S::kPTiles;
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
     // barriers: k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full, p_ready, o_full, s_free.
     // Keys and values have rings of their own: a key block's stage is free again as soon as its scores are
@@ -199,7 +214,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
 
     const uint32_t q_tile = smem_u32(smem);
-    const uint32_t p_tile = q_tile + kTileBytes;                // kPTiles tiles of 16 KiB (keys 0..63 | 64..127)
+    const uint32_t p_tile = q_tile + S::kQBytes;                // kPTiles tiles of 16 KiB (keys 0..63 | 64..127)
     const uint32_t kv_tiles = p_tile + kPTiles * kTileBytes;    // [stage][K | V]
     const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[STAGES]);
     const uint32_t v_full = smem_u32(&bars[2 * STAGES]), v_empty = smem_u32(&bars[3 * STAGES]);
@@ -234,9 +249,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     // barriers and tensor memory are set up while the kernel before this one drains; its results (the rotated
     // queries, this step's keys and values) are read from here on
     pdl_wait();
-    // the Q tile: every thread copies its share of the 128 rows x 8 chunks, swizzled like the K/V tiles
-    for (int idx = threadIdx.x; idx < BM * 8; idx += kThreads) {
-        const int r = idx >> 3, c = idx & 7;
+    // the Q tile: every thread copies its share of the 128 rows x D / 8 chunks, swizzled like the K/V tiles
+    constexpr int kChunks = D / 8;
+    for (int idx = threadIdx.x; idx < BM * kChunks; idx += kThreads) {
+        const int r = idx / kChunks, c = idx % kChunks;
         const int fr = r0 + r;
         const bool ok = fr < n_rows;
         const __nv_bfloat16* src = p.q;
@@ -244,7 +260,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             const int qpos = fr / p.group, g = fr - qpos * p.group;
             src = p.q + (int64_t)(first_row + qpos) * p.q_stride + (int64_t)(kv_head * p.group + g) * D + c * 8;
         }
-        cp_async16(q_tile + sw128(r, c), src, ok);
+        cp_async16(q_tile + (c >> 3) * kTileBytes + sw128(r, c & 7), src, ok);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -285,7 +301,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 }
                 go = __shfl_sync(0xffffffffu, go, 0);            // also orders the announcement before the copies
                 if (!go) { ok = false; break; }
-                if (lane < copies) tma_load_kv(dst + which * kKVTileBytes, &cache_map, full, in_page, kv_head, which, page);
+                if (lane < copies) {
+#pragma unroll
+                    for (int h = 0; h < D / 64; ++h)
+                        tma_load_kv(dst + which * kKVTileBytes + h * kKVHalfBytes, &cache_map, full, h * 64, in_page,
+                                    kv_head, which, page);
+                }
             }
         }
         if (!ok && lane == 0) {
@@ -304,7 +325,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 const uint32_t k_tile = kv_tiles + s * 2 * kKVTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
-                    umma(tmem_s, desc_sw128(q_tile + kk * 32, 1), desc_sw128(k_tile + kk * 32, 1), idesc_qk, kk != 0);
+                    umma(tmem_s, desc_sw128(q_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
+                         desc_sw128(k_tile + (kk >> 2) * kKVHalfBytes + (kk & 3) * 32, 1), idesc_qk, kk != 0);
                 umma_commit(s_full);
                 umma_commit(k_empty + 8 * s);     // the key stage may be refilled once these products are done
                 return true;
@@ -325,7 +347,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
                     umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
-                         desc_sw128(v_tile + kk * 2048, 1024 >> 4), idesc_pv, (j | kk) != 0);
+                         desc_sw128(v_tile + kk * 2048, kKVHalfBytes >> 4), idesc_pv, (j | kk) != 0);
                 umma_commit(o_full);
                 umma_commit(v_empty + 8 * (j % STAGES));
             }
@@ -442,7 +464,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                         packed[i >> 1] = pack_bf16(pr[0], pr[1]);
                     }
                 }
-                unsigned char* dst = smem + kTileBytes + (c >> 1) * kTileBytes;
+                unsigned char* dst = smem + S::kQBytes + (c >> 1) * kTileBytes;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                     *reinterpret_cast<uint4*>(dst + sw128(r, (c & 1) * 4 + q4)) =
@@ -516,11 +538,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
 
 // 1 if this kernel takes the sizes (else the caller uses the mma.sync kernel).
 TB_EXPORT int tb_attention_tcgen05_supported(int num_heads, int num_kv_heads, int head_dim, int page_size) {
-    if (head_dim != D) return 0;
+    if (head_dim != 64 && head_dim != 128) return 0;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return 0;
     if (page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
     return 1;
 }
+
+namespace {
+
+template <int D, int BN>
+int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_rows_per_seq, const TcAttnParams& p,
+                     cudaStream_t stream) {
+    const CUtensorMap* map = cache_map_for(cache, cache_pages, p.num_kv_heads, p.page_size, BN, D);
+    if (map == nullptr) return TB_ERR_BAD_SIZE;
+    auto kernel = attention_tcgen05_kernel<D, BN>;
+    const size_t smem = Shape<D, BN>::kSmemBytes;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    const int max_folded = max_rows_per_seq * p.group;
+    dim3 grid(((max_folded + BM - 1) / BM) * p.num_kv_heads, 1, num_seqs);
+    if (cudaError_t launch = tb_launch_pdl(kernel, grid, dim3(kThreads), smem, stream, *map, p)) return (int)launch;
+    return tb_launch_status();
+}
+
+}  // namespace
 
 // Attention of the sequences with more than 16 folded rows of a packed batch (the others are left to the split
 // decode kernel).  Arguments as tb_attention_mma; error: device int, set non-zero if a bounded wait ran out.
@@ -534,8 +575,6 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
         return TB_ERR_BAD_ALIGN;
     if (num_seqs > 65535 || num_kv_heads > 65535) return TB_ERR_BAD_SIZE;
-    const CUtensorMap* map = cache_map_for(cache, cache_pages, num_kv_heads, page_size, BN);
-    if (map == nullptr) return TB_ERR_BAD_SIZE;
     TcAttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.out = (__nv_bfloat16*)out;
@@ -555,13 +594,6 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.scale_log2 = scale * kLog2e;
-    const size_t smem = (size_t)(1 + kPTiles) * kTileBytes + (size_t)2 * STAGES * kKVTileBytes;
-    cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    const int max_folded = max_rows_per_seq * p.group;
-    dim3 grid(((max_folded + BM - 1) / BM) * num_kv_heads, 1, num_seqs);
-    if (cudaError_t err = tb_launch_pdl(attention_tcgen05_kernel, grid, dim3(kThreads), smem, stream, *map, p))
-        return (int)err;
-    return tb_launch_status();
+    if (head_dim == 128) return launch_attention<128, 64>(cache, cache_pages, num_seqs, max_rows_per_seq, p, stream);
+    return launch_attention<64, kBlockKeys64>(cache, cache_pages, num_seqs, max_rows_per_seq, p, stream);
 }

@@ -48,12 +48,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-// One box of the cache tensor: keys key_in_page.. of `page`, head `kv_head`, K (which = 0) or V (which = 1).
-__device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map, uint32_t bar, int key_in_page,
-                                            int kv_head, int which, int page) {
+// One box of the cache tensor: dims dim0..dim0+63 (dim0 a multiple of 64, so the copy starts on a 16-byte boundary)
+// of keys key_in_page.. of `page`, head `kv_head`, K (which = 0) or V (which = 1).
+__device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map, uint32_t bar, int dim0,
+                                            int key_in_page, int kv_head, int which, int page) {
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
+        ::"r"(dst), "l"(map), "r"(bar), "r"(dim0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -72,20 +73,23 @@ inline EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// Tensor map of one cache entry with head_dim 64, boxes of min(page_size, max_rows) keys of one head.  Maps are
-// kept per (pointer, geometry): a cache entry lives as long as its model.
-inline const CUtensorMap* cache_map_for(const void* cache, int pages, int num_kv_heads, int page_size, int max_rows) {
+// Tensor map of one cache entry [pages][K|V][kv head][key][head_dim] (head_dim a multiple of 64), boxes of 64 dims
+// of min(page_size, max_rows) keys of one head.  Maps are kept per (pointer, geometry): a cache entry lives as long
+// as its model.
+inline const CUtensorMap* cache_map_for(const void* cache, int pages, int num_kv_heads, int page_size, int max_rows,
+                                        int head_dim) {
     static std::mutex lock;
-    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> maps;
+    static std::map<std::tuple<const void*, int, int, int, int, int>, CUtensorMap> maps;
     std::lock_guard<std::mutex> guard(lock);
-    const auto key = std::make_tuple(cache, pages, num_kv_heads, page_size, max_rows);
+    const auto key = std::make_tuple(cache, pages, num_kv_heads, page_size, max_rows, head_dim);
     auto found = maps.find(key);
     if (found != maps.end()) return &found->second;
     EncodeTiledFn fn = encode_tiled();
     if (fn == nullptr) return nullptr;
     CUtensorMap map;
-    const cuuint64_t dims[5] = {64, (cuuint64_t)page_size, (cuuint64_t)num_kv_heads, 2, (cuuint64_t)pages};
-    const cuuint64_t row = 64 * 2;
+    const cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)num_kv_heads, 2,
+                                (cuuint64_t)pages};
+    const cuuint64_t row = (cuuint64_t)head_dim * 2;
     const cuuint64_t strides[4] = {row, row * page_size, row * page_size * num_kv_heads,
                                    row * page_size * num_kv_heads * 2};
     const cuuint32_t box[5] = {64, (cuuint32_t)(page_size < max_rows ? page_size : max_rows), 1, 1, 1};

@@ -600,10 +600,10 @@ def test_skinny_gemm(m, n, k):
     ([600, 90], [260, 90], 4, 2, 16, 100),                      # sliding window
     ([300], [17], 16, 1, 16, 0),                                # a group of 16: two tokens fill a tile row block
 ])
-def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window):
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
     from tesseract_b200 import kernels
 
-    d = 64
     case = paged_case(torch.bfloat16, lengths, new, nh, nkv, d, page_size, seed=sum(lengths))
     scale = 1.0 / math.sqrt(d)
     rows = case["q"].shape[0]
