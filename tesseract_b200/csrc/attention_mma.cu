@@ -27,13 +27,17 @@ constexpr int kThreads = 128;
 constexpr int kWarps = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
-// split decode kernel: keys per warp tile, depth of each warp's ring, warps per CTA (eight while three stages of
-// every warp fit shared memory twice over or, for wide heads, once)
+// split decode kernel: keys per warp tile, warps per CTA and depth of each warp's ring, chosen so that two CTAs
+// share an SM up to a padded head size of 128: eight warps of three stages at 64 (96 KiB), six warps of two stages
+// at 128 (96 KiB; at batch 64 that reads keys and values at 6.0 TB/s, eight warps of three stages, one CTA per SM,
+// at 4.1), four warps of three stages above (192 KiB, one CTA per SM).  Deeper rings measured no faster: a lone
+// warp is bound by its own instruction chain.
 constexpr int kDecodeKeys = 16;
 template <int D>
-constexpr int kDecodeWarps = D <= 128 ? 8 : 4;
+constexpr int kDecodeWarps = D <= 64 ? 8 : D <= 128 ? 6 : 4;
 constexpr int kMaxClusterSplits = 8;  // the portable limit of a thread-block cluster
-constexpr int kDecodeStages = 3;  // deeper rings measured no faster: a lone warp is bound by its own instruction chain
+template <int D>
+constexpr int kDecodeStages = D > 64 && D <= 128 ? 2 : 3;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -546,7 +550,7 @@ __device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, c
 // keeps STAGES - 1 tiles in flight.
 template <int D, int WARPS, int NK>
 __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p) {
-    constexpr int STAGES = kDecodeStages;
+    constexpr int STAGES = kDecodeStages<D>;
     constexpr bool QREG = D <= 128;
     constexpr uint32_t kTileBytes = NK * D * 2;
     constexpr uint32_t kStageBytes = 2 * kTileBytes;
@@ -768,7 +772,7 @@ int launch_all(const AttnParams& p, int num_seqs, int max_rows_per_seq, int run_
         const size_t merge_a = (size_t)(2 * warps * 16 + warps * 16 * D + 32 + 16 * D) * sizeof(float);
         const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
         const size_t merge = merge_a > merge_b ? merge_a : merge_b;
-        const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages * 2 * kDecodeKeys * D * 2 +
+        const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages<D> * 2 * kDecodeKeys * D * 2 +
                              (size_t)D * sizeof(float) + (size_t)2 * D * 2;   // + rotation angles, staged new key/value
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = attention_decode_kernel<D, warps, kDecodeKeys>;

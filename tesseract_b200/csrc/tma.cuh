@@ -1,6 +1,6 @@
 // Bulk tensor copies (TMA) and mbarriers, shared by the kernels that stream cache pages.
 //
-// A cache entry [pages][K|V][kv_heads][page_size][head_dim] (bfloat16, head_dim 64) is described to the TMA unit
+// A cache entry [pages][K|V][kv_heads][page_size][head_dim] (bfloat16, head_dim a multiple of 64) is described to the TMA unit
 // once by a five-dimensional tensor map; a copy then brings min(page_size, max_rows) consecutive keys of one page
 // and one head into shared memory as rows of 128 bytes with the 128-byte swizzle (16-byte chunk index XOR row
 // mod 8), the layout that both ldmatrix-fed mma.sync tiles and tcgen05 matrix descriptors read.  No copy uses

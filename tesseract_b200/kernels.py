@@ -285,20 +285,23 @@ def _counters(device, count: int) -> torch.Tensor:
 def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64) -> int:
     """How many key splits the decode kernel uses.
 
-    A CTA's eight warps (four for head sizes above 128) each stream every eighth tile of 16 keys at about
-    0.65 microseconds a tile; merging splits costs about 2.5 microseconds inside a thread-block cluster (up to
-    8 splits) and 5 through scratch memory; two CTAs fit an SM.  The choice minimises that estimate over the
-    split counts that keep all CTAs resident at once (at most 32: one sequence of 131,072 tokens reads its keys at
-    5.2 TB/s with 32 splits, 4.5 with 16)."""
+    A CTA's warps (eight up to a head size of 64, six up to 128, four above) each stream their share of the tiles
+    of 16 keys at about 0.65 microseconds a tile of 64-wide heads (wider heads in proportion); merging splits
+    costs about 2.5 microseconds inside a thread-block cluster (up to 8 splits) and 5 through scratch memory; two
+    CTAs fit an SM up to a head size of 128, one above.  The choice minimises that estimate over the split counts
+    that keep all CTAs resident at once (at most 32: one sequence of 131,072 tokens reads its keys at 5.2 TB/s
+    with 32 splits, 4.5 with 16)."""
     tiles = -(-max_context // 16)
-    warps = 8 if head_dim <= 128 else 4
+    warps = 8 if head_dim <= 64 else 6 if head_dim <= 128 else 4
     ctas = max(1, num_seqs * num_kv_heads)
-    limit = max(1, min(32, 2 * _SM_COUNT // ctas))
+    per_sm = 2 if head_dim <= 128 else 1
+    tile_cost = 0.65 * max(1.0, head_dim / 64.0)
+    limit = max(1, min(32, per_sm * _SM_COUNT // ctas))
     best, best_cost = 1, float("inf")
     for splits in range(1, limit + 1):
         per_warp = -(-(-(-tiles // splits)) // warps)
         merge = 0.0 if splits == 1 else 2.5 if splits <= 8 else 5.0
-        cost = 0.65 * per_warp + merge + 0.15 * splits
+        cost = tile_cost * per_warp + merge + 0.15 * splits
         if cost < best_cost:
             best, best_cost = splits, cost
     return best

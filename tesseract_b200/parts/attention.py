@@ -52,7 +52,7 @@ class Attention(Mixer):
         self.qkv_proj = Linear(fused, runtime)
         self.o_proj = Linear(tensors["o"], runtime)
         # Which kernel runs prompt portions in bfloat16: "tcgen05" (tensor-memory accumulators, TMA-fed; head_dim 64
-        # only, other sizes fall back) or "mma" (mma.sync tiles, every head size).
+        # or 128, other sizes fall back) or "mma" (mma.sync tiles, every head size).
         self.prompt_kernel = str(p.get("prompt_kernel") or "tcgen05")
         if self.prompt_kernel not in ("mma", "tcgen05"):
             raise ValueError(f"prompt_kernel must be 'mma' or 'tcgen05', got '{self.prompt_kernel}'")

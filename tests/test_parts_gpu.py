@@ -493,7 +493,8 @@ def test_layers_with_and_without_a_window_keep_pages_of_their_own(dtype, tol):
         torch.testing.assert_close(torch.cat(got[r]), plain[r], rtol=tol, atol=tol)
 
 
-def test_attention_part_with_the_tcgen05_prompt_kernel():
+@pytest.mark.parametrize("nh, nkv, d", [(8, 2, 64), (6, 2, 128)])
+def test_attention_part_with_the_tcgen05_prompt_kernel(nh, nkv, d):
     """The same mixer with prompt portions on the tcgen05 kernel: portions, decode rows beside them, page reuse."""
     from tesseract_b200 import kernels
     from tesseract_b200.cache import CacheManager
@@ -502,7 +503,7 @@ def test_attention_part_with_the_tcgen05_prompt_kernel():
 
     torch.manual_seed(3)
     rt = runtime(torch.bfloat16)
-    hidden, nh, nkv, d = 128, 8, 2, 64
+    hidden = 128
     position = PartSpec.make("rotary", {"head_dim": d, "theta": 10000.0, "scaling": None})
     weights = {"q": torch.randn(nh * d, hidden) * 0.1, "k": torch.randn(nkv * d, hidden) * 0.1,
                "v": torch.randn(nkv * d, hidden) * 0.1, "o": torch.randn(hidden, nh * d) * 0.1}
