@@ -36,6 +36,16 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "bos_token_id": 128000, "eos_token_id": [128001],
 }
+# Other layer sizes of the same architecture (--size), to see how the kernels hold up away from the headline model.
+OTHER_SIZES = {
+    "3b": dict(num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8, head_dim=128,
+               intermediate_size=8192),
+    "8b": dict(num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=14336, tie_word_embeddings=False,
+               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192}),
+}
+SIZE_NAMES = {"1b": "Llama-3.2-1B sizes", "3b": "Llama-3.2-3B sizes", "8b": "Llama-3.1-8B sizes"}
 PROMPT_TOKENS = 2048
 CONTEXT = 4096
 PAGE_SIZE = 16
@@ -129,8 +139,9 @@ def run_ours(args):
     from tesseract_b200.engine import StepEntry
     from tesseract_b200.weights.random_init import write_random_model
 
-    layers = args.layers or LLAMA_1B["num_hidden_layers"]
-    cfg = dict(LLAMA_1B, num_hidden_layers=layers)
+    model = dict(LLAMA_1B, **OTHER_SIZES.get(args.size, {}))
+    layers = args.layers or model["num_hidden_layers"]
+    cfg = dict(model, num_hidden_layers=layers)
     pk = peaks()
     rng = np.random.default_rng(0)
     sampler = ClockSampler()
@@ -271,11 +282,13 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
-        "config": {"model": "Llama-3.2-1B sizes", "layers": layers, "layers_of_model": LLAMA_1B["num_hidden_layers"],
-                   "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
+        "config": {"model": SIZE_NAMES[args.size], "layers": layers, "layers_of_model": model["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
                    "decode_context": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (2.47 GB of weights read every step)",
+                   "l2": f"inputs larger than L2 ({numbers['weight_bytes'] / 1e9:.2f} GB of weights read every step)",
                    "decode_steps": "CUDA graph per step, launched one ahead of the token read-back"},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -411,6 +424,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--size", default="1b", choices=["1b", "3b", "8b"],
+                        help="layer sizes: the headline model's (1b) or another Llama's, for a look at other sizes")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
