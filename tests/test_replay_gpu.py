@@ -191,6 +191,43 @@ def test_one_layer_of_the_1b_sizes_in_bfloat16(tmp_path):
     assert (got.argmax(dim=1) == hidden.argmax(dim=1)).float().mean() >= 0.6   # random weights: many near ties
 
 
+def test_long_context_with_wide_heads_in_bfloat16_against_float32(tmp_path):
+    """Head size 128 at a context of six thousand tokens: prompt portions of 2,048 (tcgen05 attention in 64-key
+    blocks over thousands of earlier keys) and decoded tokens (the split decode kernel's six-warp form, many
+    splits), bfloat16 against the engine's own 32-bit path, which other tests hold against the plain model."""
+    from tests.helpers import make_model_folder
+    from tesseract_b200 import kernels
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    config = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+        "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 4, "num_key_value_heads": 2,
+        "head_dim": 128, "intermediate_size": 1024, "vocab_size": 512, "max_position_embeddings": 16384,
+        "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 2048},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "bos_token_id": 1, "eos_token_id": [2],
+    }
+    folder = make_model_folder(str(tmp_path / "wide_heads"), config, "bfloat16", 5)
+    prompt, decoded = 6000, 6
+    tokens = random_tokens(config["vocab_size"], prompt + decoded, seed=23)
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        stepper = make_stepper(load_model(folder, dtype=dtype), capacity_tokens=8192, max_requests=2)
+        assert stepper.cache.admit("r")
+        rows = []
+        for start in range(0, prompt, 2048):
+            stop = min(prompt, start + 2048)
+            want = [0, stop - start - 1]
+            rows.append(stepper.step([StepEntry("r", tokens[start:stop], want)]).float().cpu())
+        for t in range(prompt, prompt + decoded):
+            rows.append(stepper.step([StepEntry("r", tokens[t:t + 1], [0])]).float().cpu())
+        logits[dtype] = torch.cat(rows)
+    assert kernels.tcgen05_error() == 0
+    scale = float(logits["float32"].abs().max())
+    assert float((logits["bfloat16"] - logits["float32"]).abs().max()) <= 3e-2 * max(1.0, scale)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replayed_prompt_portions_equal_ordinary_steps(model_folders, dtype):
     """A prompt fed in portions of the configured size goes through a captured CUDA graph (only device metadata
