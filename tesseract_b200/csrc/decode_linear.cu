@@ -133,9 +133,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
     pdl_trigger();
     float4 nw_first = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // the norm's weights are weights too: fetch them early
     if (PRO != PRO_NONE && (int)threadIdx.x * 4 < K) nw_first = *reinterpret_cast<const float4*>(p.norm_w + threadIdx.x * 4);
+    // Weights do not depend on the kernel before: their first stages go out ahead of the dependency wait.  With a
+    // norm in front, the last POST of them are held back until the rows' own loads are out: those would otherwise
+    // queue behind the whole ring (some microseconds of HBM time), and the memory would then idle while the norm
+    // is computed; held back, they arrive under it (a decode step of eight rows: 0.783 -> 0.772 ms; with sixteen
+    // rows and their shallower rings it cost 2 %, so those keep the whole prefetch in front).
+    constexpr int POST = PRO == PRO_NONE || MT > 1 ? 0 : (NH == 2 ? 2 : 3) < STAGES - 1 ? (NH == 2 ? 2 : 3) : STAGES - 2;
+    constexpr int PRE = STAGES - 1 - POST;
     int early[STAGES - 1];
 #pragma unroll
-    for (int q = 0; q < STAGES - 1; ++q) early[q] = issue(false);   // weights do not depend on the kernel before
+    for (int q = 0; q < PRE; ++q) early[q] = issue(false);
     pdl_wait();                                      // from here on the previous kernel's results are visible
     if (PRO == PRO_NONE) {
         // the activations of the blocks above, a group each: the loop's wait count then covers them as well
@@ -160,14 +167,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         // Eight rows at a time, all their loads issued before the first use (rows beyond M repeat row M - 1, so
         // that no load depends on a branch), four elements per thread and row.
         float* red = partial;  // [kWarps][ROWS] partial sums of squares (the partial-sum area is free until later)
-        auto load_rows = [&](int r0, int j, float (&c)[8][4]) {
-            uint2 a[8], b[8];
+        auto fetch_rows = [&](int r0, int j, uint2 (&a)[8], uint2 (&b)[8]) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
                 const int row = min(r0 + r, p.M - 1);
                 a[r] = *reinterpret_cast<const uint2*>(p.res + (int64_t)row * K + j);
                 if (PRO == PRO_ADD_NORM) b[r] = *reinterpret_cast<const uint2*>(p.upd + (int64_t)row * K + j);
             }
+        };
+        auto sum_rows = [&](const uint2 (&a)[8], const uint2 (&b)[8], float (&c)[8][4]) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
                 c[r][0] = __uint_as_float(a[r].x << 16);
@@ -182,6 +190,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 }
             }
         };
+        auto load_rows = [&](int r0, int j, float (&c)[8][4]) {
+            uint2 a[8], b[8];
+            fetch_rows(r0, j, a, b);
+            sum_rows(a, b, c);
+        };
+        // the first eight rows' first columns go out before the held-back weight stages
+        uint2 first_a[8], first_b[8];
+        const bool has_first = (int)threadIdx.x * 4 < K;
+        if (POST > 0 && has_first) fetch_rows(0, threadIdx.x * 4, first_a, first_b);
+#pragma unroll
+        for (int q = PRE; q < STAGES - 1; ++q) early[q] = issue(false);
         auto pack4 = [](const float (&v)[4]) {
             const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
             return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
@@ -198,7 +217,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
                 float c[8][4];
-                load_rows(r0, j, c);
+                if (POST > 0 && r0 == 0 && j == (int)threadIdx.x * 4) sum_rows(first_a, first_b, c);
+                else load_rows(r0, j, c);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     if (PRO == PRO_ADD_NORM && blockIdx.x == 0 && r0 + r < p.M)
