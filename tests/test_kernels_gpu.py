@@ -336,6 +336,7 @@ def run_attention_mma(case, nh, nkv, d, page_size, window, scale, splits):
     ([90, 41], 5, 5, 256, 16, 0, 2, None, True),                      # the widest head, no grouping
     ([129, 40], 4, 1, 16, 16, 0, 3, "none", True),                    # no rotation at all
     ([129, 40], 8, 2, 64, 16, 0, 3, "llama3", False),                 # reads a cache that another layer wrote
+    ([7 + 5 * k for k in range(40)], 16, 8, 64, 16, 0, 1, "llama3", True),   # 320 CTAs: the four-warp form
 ])
 def test_attention_decode_rope_equals_rope_then_attention(lengths, nh, nkv, d, page_size, window, splits, scaling,
                                                           write_kv):
@@ -393,6 +394,8 @@ def test_attention_decode_rope_equals_rope_then_attention(lengths, nh, nkv, d, p
     ([513], [513], 32, 8, 64, 16, 0, 1),                               # many tiles of one long prompt
     ([90, 5], [2, 1], 32, 2, 96, 16, 0, 2),                            # a group of 16 heads: one token fills a tile
     ([90, 50], [2, 1], 40, 2, 16, 16, 0, 1),                           # a group of 20: decode goes to the tile kernel
+    ([3 + 2 * k for k in range(75)], [1] * 75, 8, 4, 64, 16, 0, 1),   # 300 CTAs without splits: the four-warp form
+    ([1 + 3 * k for k in range(100)], [1] * 100, 6, 3, 32, 16, 0, 1), # the same at a narrower head
 ])
 def test_attention_mma(lengths, new, nh, nkv, d, page_size, window, splits):
     case = paged_case(torch.bfloat16, lengths, new, nh, nkv, d, page_size, seed=sum(lengths) + d)
