@@ -376,10 +376,13 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
                                               float (&l)[2]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // merge the four warps (each saw a quarter of the keys) through shared memory
+    // rows of the accumulators are D + 8 floats apart: the eight rows that a warp's lanes store at once then fall
+    // on different banks (64-bit stores, conflict-free by half-warp)
+    constexpr int P = D + 8;
     float* sm_m = reinterpret_cast<float*>(smem);             // [warps][16]
     float* sm_l = sm_m + WARPS * 16;                         // [warps][16]
-    float* sm_o = sm_l + WARPS * 16;                         // [warps][16][D]
-    float* x_ml = sm_o + WARPS * 16 * D;                     // [2][16]  this split's maximum and sum (cluster merge)
+    float* sm_o = sm_l + WARPS * 16;                         // [warps][16][P]
+    float* x_ml = sm_o + WARPS * 16 * P;                     // [2][16]  this split's maximum and sum (cluster merge)
     float* x_acc = x_ml + 32;                                 // [16][D]  this split's accumulator
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -393,8 +396,7 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
 #pragma unroll
         for (int dt = 0; dt < D / 8; ++dt) {
             const int col = dt * 8 + 2 * (lane & 3);
-            sm_o[(warp * 16 + r) * D + col] = o[dt][2 * i];
-            sm_o[(warp * 16 + r) * D + col + 1] = o[dt][2 * i + 1];
+            *reinterpret_cast<float2*>(sm_o + (warp * 16 + r) * P + col) = make_float2(o[dt][2 * i], o[dt][2 * i + 1]);
         }
     }
     __syncthreads();
@@ -407,7 +409,7 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             const float wgt = exp2f(sm_m[w * 16 + r] - big);
-            acc += wgt * sm_o[(w * 16 + r) * D + col];
+            acc += wgt * sm_o[(w * 16 + r) * P + col];
             sum += wgt * sm_l[w * 16 + r];
         }
         const int qpos = r / p.group, g = r - qpos * p.group;
@@ -439,14 +441,25 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
             for (int idx = threadIdx.x; idx < n_rows * D; idx += (WARPS * 32)) {
                 const int r = idx / D, col = idx - r * D;
                 if (col >= p.head_dim) continue;
+                // every split's maximum, sum and accumulator at once: the remote loads are independent of each
+                // other, so their latencies overlap (one after the other they cost a round trip per split)
+                float m_s[kMaxClusterSplits], l_s[kMaxClusterSplits], a_s[kMaxClusterSplits];
+#pragma unroll
+                for (int s = 0; s < kMaxClusterSplits; ++s) {
+                    const bool have = s < p.splits;
+                    m_s[s] = have ? ld_cluster_f32(x_ml + r, s) : kMasked;
+                    l_s[s] = have ? ld_cluster_f32(x_ml + 16 + r, s) : 0.0f;
+                    a_s[s] = have ? ld_cluster_f32(x_acc + idx, s) : 0.0f;
+                }
                 float big = kMasked;
-                for (int s = 0; s < p.splits; ++s) big = fmaxf(big, ld_cluster_f32(x_ml + r, s));
+#pragma unroll
+                for (int s = 0; s < kMaxClusterSplits; ++s) big = fmaxf(big, m_s[s]);
                 float acc = 0.0f, sum = 0.0f;
-                for (int s = 0; s < p.splits; ++s) {
-                    const float l_s = ld_cluster_f32(x_ml + 16 + r, s);
-                    const float w = l_s > 0.0f ? exp2f(ld_cluster_f32(x_ml + r, s) - big) : 0.0f;
-                    sum += w * l_s;
-                    acc += w * ld_cluster_f32(x_acc + idx, s);
+#pragma unroll
+                for (int s = 0; s < kMaxClusterSplits; ++s) {
+                    const float w = l_s[s] > 0.0f ? exp2f(m_s[s] - big) : 0.0f;
+                    sum += w * l_s[s];
+                    acc += w * a_s[s];
                 }
                 const int qpos = r / p.group, g = r - qpos * p.group;
                 p.out[(int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * p.head_dim + col] =
@@ -514,10 +527,25 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
     }
 }
 
-// One warp copies NK keys of one kv head's K and V (keys key0.. of the sequence) into its own swizzled tiles.
+// One warp copies NK keys of one kv head's K and V (keys key0.. of the sequence) into its own swizzled tiles, in
+// passes of 32 sixteen-byte chunks.  The page of a lane's key in each pass comes from the block table: a load that
+// the copy depends on, so the kernel below looks the pages of a tile up one tile ahead (warp_pages) and copies
+// with them later (warp_copy_kv); warp_load_kv does both at once.
 template <int D, int NK>
-__device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, const AttnParams& p, const int* table,
-                                             int kv_head, int key0, int key_lo, int key_hi) {
+__device__ __forceinline__ void warp_pages(const AttnParams& p, const int* table, int key0, int key_lo, int key_hi,
+                                           int (&pages)[NK * (D / 8) / 32]) {
+    constexpr int CH = D / 8;
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int pass = 0; pass < NK * CH / 32; ++pass) {
+        const int key = key0 + (pass * 32 + lane) / CH;
+        pages[pass] = key >= key_lo && key <= key_hi ? table[key >> p.page_shift] : 0;
+    }
+}
+
+template <int D, int NK>
+__device__ __forceinline__ void warp_copy_kv(uint32_t k_tile, uint32_t v_tile, const AttnParams& p, int kv_head,
+                                             int key0, int key_lo, int key_hi, const int (&pages)[NK * (D / 8) / 32]) {
     constexpr int CH = D / 8;
     static_assert((NK * CH) % 32 == 0, "a warp copies whole passes of 32 chunks");
     const int lane = threadIdx.x & 31;
@@ -532,14 +560,20 @@ __device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, c
         const int key = key0 + r;
         const bool ok = key >= key_lo && key <= key_hi && c * 8 < p.head_dim;
         const __nv_bfloat16* src = base;
-        if (ok) {
-            const int page = table[key >> p.page_shift];
-            src = base + (int64_t)page * page_block + (int64_t)(key & (p.page_size - 1)) * p.head_dim + c * 8;
-        }
+        if (ok)
+            src = base + (int64_t)pages[pass] * page_block + (int64_t)(key & (p.page_size - 1)) * p.head_dim + c * 8;
         const uint32_t offset = tile_offset<D>(r, c);
         cp_async16(k_tile + offset, src, ok);
         cp_async16(v_tile + offset, src + v_offset, ok);
     }
+}
+
+template <int D, int NK>
+__device__ __forceinline__ void warp_load_kv(uint32_t k_tile, uint32_t v_tile, const AttnParams& p, const int* table,
+                                             int kv_head, int key0, int key_lo, int key_hi) {
+    int pages[NK * (D / 8) / 32];
+    warp_pages<D, NK>(p, table, key0, key_lo, key_hi, pages);
+    warp_copy_kv<D, NK>(k_tile, v_tile, p, kv_head, key0, key_lo, key_hi, pages);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -598,6 +632,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
 
     bool waited = false;
+    int next_pages[NK * (D / 8) / 32];
     if (b0 < b1) {
         if (p.qkv != nullptr) {
             // angles of the one new position: angle_i = float(position) * inv_freq[i], 32-bit, accurate functions
@@ -628,6 +663,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
             cp_async_commit();  // one group per stage, empty or not, keeps the wait count fixed
             kb_load += WARPS;
         }
+        // the pages of the tile that the loop fetches first, looked up a tile ahead from here on
+        if (kb_load < b1) warp_pages<D, NK>(p, table, kb_load * NK, key_lo, key_hi, next_pages);
         if (!waited) {
             pdl_wait();
             waited = true;
@@ -714,10 +751,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         for (int kb = b0 + warp; kb < b1; kb += WARPS, ++it) {
             if (kb_load < b1) {
                 const uint32_t dst = ring + ((it + STAGES - 1) % STAGES) * kStageBytes;
-                warp_load_kv<D, NK>(dst, dst + kTileBytes, p, table, kv_head, kb_load * NK, key_lo, key_hi);
+                warp_copy_kv<D, NK>(dst, dst + kTileBytes, p, kv_head, kb_load * NK, key_lo, key_hi, next_pages);
             }
             cp_async_commit();
             kb_load += WARPS;
+            if (kb_load < b1) warp_pages<D, NK>(p, table, kb_load * NK, key_lo, key_hi, next_pages);
             cp_async_wait<STAGES - 1>();
             __syncwarp();
             const uint32_t cur = ring + (it % STAGES) * kStageBytes;
@@ -760,7 +798,7 @@ int sm_count() {
 
 template <int D, int warps>
 int launch_decode(const AttnParams& p, int num_seqs, cudaStream_t stream) {
-    const size_t merge_a = (size_t)(2 * warps * 16 + warps * 16 * D + 32 + 16 * D) * sizeof(float);
+    const size_t merge_a = (size_t)(2 * warps * 16 + warps * 16 * (D + 8) + 32 + 16 * D) * sizeof(float);
     const size_t merge_b = (size_t)(2 * p.splits + 2) * 16 * sizeof(float);
     const size_t merge = merge_a > merge_b ? merge_a : merge_b;
     const size_t tiles = (size_t)16 * D * 2 + (size_t)warps * kDecodeStages<D> * 2 * kDecodeKeys * D * 2 +
