@@ -106,7 +106,7 @@ class _Graph:
         # a row's token comes from the host or, for a sequence that decoded in the step before, from that step's
         # sampler output, which never leaves the device
         kernels.select_tokens(self.d["tokens"], self.d["feed"], self.sampled, self.tokens, stepper.vocab_size)
-        logits = stepper.model.forward(self.ctx, stepper.cache.bindings, self.want_rows)
+        logits = stepper.model.forward(self.ctx, stepper.cache.bindings, self.want_rows, want_every_row=True)
         kernels.sample(logits, self.d["temps"], self.d["uniform"], self.sampled[:self.batch])
         return logits
 

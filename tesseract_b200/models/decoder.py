@@ -108,24 +108,29 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: StepContext, bindings: Sequence[Optional[CacheBinding]],
-                want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-        """Run the step's rows; return float32 logits ``[len(want_rows), vocab]`` or ``None``."""
+                want_rows: Optional[torch.Tensor], want_every_row: bool = False) -> Optional[torch.Tensor]:
+        """Run the step's rows; return float32 logits ``[len(want_rows), vocab]`` or ``None``.
+        ``want_every_row``: the caller knows that ``want_rows`` is ``0 .. num_rows - 1`` (a decode step), so the
+        rows need not be gathered before the head."""
         hidden = self.embedding.forward(ctx.token_ids[:ctx.num_rows])
         stream = ResidualStream(hidden, None)
         for index, entry in enumerate(self.spec.run_order):
             stream = self.layers[entry.layer].forward(stream, ctx, bindings[index])
         if want_rows is None or want_rows.numel() == 0:
             return None
-        return self.logits_at(stream, want_rows)
+        return self.logits_at(stream, want_rows, want_every_row and want_rows.numel() == ctx.num_rows)
 
-    def logits_at(self, stream: ResidualStream, want_rows: torch.Tensor) -> torch.Tensor:
+    def logits_at(self, stream: ResidualStream, want_rows: torch.Tensor, every_row: bool = False) -> torch.Tensor:
         count = want_rows.numel()
         width = stream.residual.shape[1]
-        residual = torch.empty((count, width), dtype=stream.residual.dtype, device=stream.residual.device)
-        kernels.gather_rows(want_rows, stream.residual, residual)
-        update = None
-        if stream.update is not None:
-            update = torch.empty_like(residual)
-            kernels.gather_rows(want_rows, stream.update, update)
+        if every_row:
+            residual, update = stream.residual[:count], None if stream.update is None else stream.update[:count]
+        else:
+            residual = torch.empty((count, width), dtype=stream.residual.dtype, device=stream.residual.device)
+            kernels.gather_rows(want_rows, stream.residual, residual)
+            update = None
+            if stream.update is not None:
+                update = torch.empty_like(residual)
+                kernels.gather_rows(want_rows, stream.update, update)
         final = DeferredNorm(self.final_norm, residual, update)
         return self.head.forward(final if self.head.accepts_deferred_norm else final.materialize())
