@@ -14,6 +14,8 @@ namespace {
 template <int VEC_BYTES>
 __global__ void gather_rows_kernel(const int* __restrict__ index, const char* __restrict__ src,
                                    char* __restrict__ dst, int64_t row_bytes, int num_src_rows) {
+    pdl_trigger();
+    pdl_wait();   // the indices (and often the rows) come from the kernel in front
     const int row = blockIdx.x;
     int from = index[row];
     if (from < 0 || from >= num_src_rows) from = 0;  // host validates; never read out of bounds
@@ -40,13 +42,17 @@ int gather_rows(const int* index, const void* src, void* dst, int rows, int64_t 
     const int64_t row_bytes = width * elem;
     const bool aligned = (row_bytes % 16 == 0) && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0);
     const int threads = 128;
+    cudaError_t launched;
     if (aligned)
-        gather_rows_kernel<16><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
+        launched = tb_launch_pdl(gather_rows_kernel<16>, dim3(rows), dim3(threads), 0, stream, index, (const char*)src,
+                                 (char*)dst, row_bytes, num_src_rows);
     else if (elem == 4)
-        gather_rows_kernel<4><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
+        launched = tb_launch_pdl(gather_rows_kernel<4>, dim3(rows), dim3(threads), 0, stream, index, (const char*)src,
+                                 (char*)dst, row_bytes, num_src_rows);
     else
-        gather_rows_kernel<2><<<rows, threads, 0, stream>>>(index, (const char*)src, (char*)dst, row_bytes, num_src_rows);
-    return tb_launch_status();
+        launched = tb_launch_pdl(gather_rows_kernel<2>, dim3(rows), dim3(threads), 0, stream, index, (const char*)src,
+                                 (char*)dst, row_bytes, num_src_rows);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 template <typename T>
@@ -133,6 +139,8 @@ namespace {
 // the host (its first decoded token) or straight from the row of the previous step's sampler output.
 __global__ void select_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ feed,
                                      const int* __restrict__ previous, int* __restrict__ out, int n, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     int token = tokens[i];
@@ -146,6 +154,7 @@ __global__ void select_tokens_kernel(const int* __restrict__ tokens, const int* 
 TB_EXPORT int tb_select_tokens(const int* tokens, const int* feed, const int* previous, int* out, int n, int vocab,
                                cudaStream_t stream) {
     if (n <= 0) return 0;
-    select_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, feed, previous, out, n, vocab);
-    return tb_launch_status();
+    cudaError_t launched = tb_launch_pdl(select_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, feed,
+                                         previous, out, n, vocab);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }

@@ -141,6 +141,8 @@ argmax_kernel(const float* __restrict__ logits, int64_t stride, int* __restrict_
     __shared__ MaxIdx scratch[kWarps];
     __shared__ float x_value;
     __shared__ int x_index;
+    pdl_trigger();
+    pdl_wait();   // the logits come from the kernel in front
     const int blocks = gridDim.x, block = blockIdx.x, r = blockIdx.y;
     const int first = min(vocab, block * chunk), count = min(vocab, first + chunk) - first;
     const float* row = logits + (int64_t)r * stride;
@@ -160,6 +162,8 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, const float* __r
     __shared__ float x_value;
     __shared__ int x_index;
     __shared__ double x_total;        // this block's mass
+    pdl_trigger();
+    pdl_wait();   // the logits come from the kernel in front
     const int blocks = gridDim.x, block = blockIdx.x, r = blockIdx.y;
     const int first = min(vocab, block * chunk), last = min(vocab, first + chunk);
     const float* row = logits + (int64_t)r * stride;
@@ -274,13 +278,15 @@ int launch_rows(Kernel kernel, int rows, int vocab, cudaStream_t stream, Args...
     config.gridDim = dim3(blocks, rows, 1);
     config.blockDim = dim3(kThreads);
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
+    cudaLaunchAttribute attribute[2];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
     attribute[0].val.clusterDim.x = blocks;
     attribute[0].val.clusterDim.y = 1;
     attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the end of the head
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = 1;
+    config.numAttrs = 2;
     cudaError_t err = cudaLaunchKernelEx(&config, kernel, args..., vocab, chunk);
     return err == cudaSuccess ? tb_launch_status() : (int)err;
 }
