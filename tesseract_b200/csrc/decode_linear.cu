@@ -50,6 +50,32 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Blackwell's packed pairs of 32-bit floats (one instruction for the two halves of a 64-bit register pair): the
+// norm in front of a product is bound by the instructions each CTA issues for it.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
@@ -175,22 +201,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 if (PRO == PRO_ADD_NORM) b[r] = *reinterpret_cast<const uint2*>(p.upd + (int64_t)row * K + j);
             }
         };
-        auto sum_rows = [&](const uint2 (&a)[8], const uint2 (&b)[8], float (&c)[8][4]) {
+        // c[r] = the four sums of a row as two pairs (elements 0,1 | 2,3), each sum exact in 32 bits
+        auto sum_rows = [&](const uint2 (&a)[8], const uint2 (&b)[8], uint64_t (&c)[8][2]) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-                c[r][0] = __uint_as_float(a[r].x << 16);
-                c[r][1] = __uint_as_float(a[r].x & 0xffff0000u);
-                c[r][2] = __uint_as_float(a[r].y << 16);
-                c[r][3] = __uint_as_float(a[r].y & 0xffff0000u);
+                c[r][0] = pack2(__uint_as_float(a[r].x << 16), __uint_as_float(a[r].x & 0xffff0000u));
+                c[r][1] = pack2(__uint_as_float(a[r].y << 16), __uint_as_float(a[r].y & 0xffff0000u));
                 if (PRO == PRO_ADD_NORM) {
-                    c[r][0] += __uint_as_float(b[r].x << 16);
-                    c[r][1] += __uint_as_float(b[r].x & 0xffff0000u);
-                    c[r][2] += __uint_as_float(b[r].y << 16);
-                    c[r][3] += __uint_as_float(b[r].y & 0xffff0000u);
+                    c[r][0] = add2(c[r][0], pack2(__uint_as_float(b[r].x << 16), __uint_as_float(b[r].x & 0xffff0000u)));
+                    c[r][1] = add2(c[r][1], pack2(__uint_as_float(b[r].y << 16), __uint_as_float(b[r].y & 0xffff0000u)));
                 }
             }
         };
-        auto load_rows = [&](int r0, int j, float (&c)[8][4]) {
+        auto load_rows = [&](int r0, int j, uint64_t (&c)[8][2]) {
             uint2 a[8], b[8];
             fetch_rows(r0, j, a, b);
             sum_rows(a, b, c);
@@ -201,40 +224,44 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         if (POST > 0 && has_first) fetch_rows(0, threadIdx.x * 4, first_a, first_b);
 #pragma unroll
         for (int q = PRE; q < STAGES - 1; ++q) early[q] = issue(false);
-        auto pack4 = [](const float (&v)[4]) {
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        auto pack4 = [](uint64_t v01, uint64_t v23) {
+            float v0, v1, v2, v3;
+            unpack2(v01, v0, v1);
+            unpack2(v23, v2, v3);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
             return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
         };
-        float ss[ROWS];
+        uint64_t ss2[ROWS];   // per row a pair of partial sums of squares (even and odd elements)
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) ss[r] = 0.0f;
+        for (int r = 0; r < ROWS; ++r) ss2[r] = 0;   // the bit pattern of (0.0f, 0.0f)
         // With K up to four elements per thread the sums stay in registers between the two passes and the rows are
         // read once (every CTA reads all rows, so a second reading costs the L2 as much again); otherwise the
         // second pass reads them again.
         const bool keep = K <= kThreads * 4;
-        float kept[ROWS][4];
+        uint64_t kept[ROWS][2];
         for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
-                float c[8][4];
+                uint64_t c[8][2];
                 if (POST > 0 && r0 == 0 && j == (int)threadIdx.x * 4) sum_rows(first_a, first_b, c);
                 else load_rows(r0, j, c);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     if (PRO == PRO_ADD_NORM && blockIdx.x == 0 && r0 + r < p.M)
-                        *reinterpret_cast<uint2*>(p.res_out + (int64_t)(r0 + r) * K + j) = pack4(c[r]);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        ss[r0 + r] += c[r][e] * c[r][e];
-                        kept[r0 + r][e] = c[r][e];
-                    }
+                        *reinterpret_cast<uint2*>(p.res_out + (int64_t)(r0 + r) * K + j) = pack4(c[r][0], c[r][1]);
+                    ss2[r0 + r] = fma2(c[r][0], c[r][0], ss2[r0 + r]);
+                    ss2[r0 + r] = fma2(c[r][1], c[r][1], ss2[r0 + r]);
+                    kept[r0 + r][0] = c[r][0];
+                    kept[r0 + r][1] = c[r][1];
                 }
             }
         }
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            ss[r] = warp_sum(ss[r]);
-            if (lane == 0) red[warp * ROWS + r] = ss[r];
+            float even, odd;
+            unpack2(ss2[r], even, odd);
+            const float ss = warp_sum(even + odd);
+            if (lane == 0) red[warp * ROWS + r] = ss;
         }
         __syncthreads();
         float* inv_s = red + kWarps * ROWS;   // [ROWS] reciprocal root mean squares
@@ -247,22 +274,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         __syncthreads();
         for (int j = threadIdx.x * 4; j < K; j += kThreads * 4) {
             const float4 nw = j == (int)threadIdx.x * 4 ? nw_first : *reinterpret_cast<const float4*>(p.norm_w + j);
+            const uint64_t nw01 = pack2(nw.x, nw.y), nw23 = pack2(nw.z, nw.w);
 #pragma unroll
             for (int r0 = 0; r0 < ROWS; r0 += 8) {
-                float c[8][4];
+                uint64_t c[8][2];
                 if (!keep) load_rows(r0, j, c);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     const float inv = inv_s[r0 + r];
-                    float v[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) v[e] = keep ? kept[r0 + r][e] : c[r][e];
-                    v[0] *= inv * nw.x;
-                    v[1] *= inv * nw.y;
-                    v[2] *= inv * nw.z;
-                    v[3] *= inv * nw.w;
-                    if (r0 + r >= p.M) v[0] = v[1] = v[2] = v[3] = 0.0f;
-                    *reinterpret_cast<uint2*>(xs + (size_t)(r0 + r) * x_pitch + j) = pack4(v);
+                    const uint64_t inv2 = pack2(inv, inv);
+                    // element * (inv * weight), as two pairs
+                    uint64_t v01 = mul2(keep ? kept[r0 + r][0] : c[r][0], mul2(inv2, nw01));
+                    uint64_t v23 = mul2(keep ? kept[r0 + r][1] : c[r][1], mul2(inv2, nw23));
+                    if (r0 + r >= p.M) v01 = v23 = 0;
+                    *reinterpret_cast<uint2*>(xs + (size_t)(r0 + r) * x_pitch + j) = pack4(v01, v23);
                 }
             }
         }
