@@ -602,6 +602,8 @@ def test_skinny_gemm(m, n, k):
     ([1000], [200], 4, 1, 64, 0),                               # one kv head, larger pages
     ([600, 90], [260, 90], 4, 2, 16, 100),                      # sliding window
     ([300], [17], 16, 1, 16, 0),                                # a group of 16: two tokens fill a tile row block
+    ([333, 90], [200, 90], 4, 2, 8, 0),                         # the smallest pages: sixteen or eight copies a block
+    ([500], [300], 6, 3, 32, 64),                               # pages of 32 keys, a window
 ])
 @pytest.mark.parametrize("d", [64, 128])
 def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
