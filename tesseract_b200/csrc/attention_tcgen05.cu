@@ -180,9 +180,10 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 template <int D, int BN>
 __global__ void __launch_bounds__(kThreads, (Shape<D, BN>::kCtasPerSm))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
-    using S = Shape<D, BN>;
-    constexpr uint32_t kKVTileBytes = S::kKVTileBytes, kKVHalfBytes = S::kKVHalfBytes, kTmemColumns = S::kTmemColumns;
-    constexpr int kPTiles = S::kPTiles;
+    using Tiles = Shape<D, BN>;
+    constexpr uint32_t kKVTileBytes = Tiles::kKVTileBytes, kKVHalfBytes = Tiles::kKVHalfBytes;
+    constexpr uint32_t kTmemColumns = Tiles::kTmemColumns;
+    constexpr int kPTiles = Tiles::kPTiles;
     extern __shared__ __align__(1024) unsigned char smem[];   // the swizzled tiles need 1024-byte alignment
     // barriers: k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full, p_ready, o_full, s_free.
     // Keys and values have rings of their own: a key block's stage is free again as soon as its scores are
@@ -214,7 +215,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const int* table = p.block_table + (int64_t)seq * p.bt_stride;
 
     const uint32_t q_tile = smem_u32(smem);
-    const uint32_t p_tile = q_tile + S::kQBytes;                // kPTiles tiles of 16 KiB (keys 0..63 | 64..127)
+    const uint32_t p_tile = q_tile + Tiles::kQBytes;                // kPTiles tiles of 16 KiB (keys 0..63 | 64..127)
     const uint32_t kv_tiles = p_tile + kPTiles * kTileBytes;    // [stage][K | V]
     const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[STAGES]);
     const uint32_t v_full = smem_u32(&bars[2 * STAGES]), v_empty = smem_u32(&bars[3 * STAGES]);
@@ -464,7 +465,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                         packed[i >> 1] = pack_bf16(pr[0], pr[1]);
                     }
                 }
-                unsigned char* dst = smem + S::kQBytes + (c >> 1) * kTileBytes;
+                unsigned char* dst = smem + Tiles::kQBytes + (c >> 1) * kTileBytes;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                     *reinterpret_cast<uint4*>(dst + sw128(r, (c & 1) * 4 + q4)) =
