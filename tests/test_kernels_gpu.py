@@ -433,6 +433,46 @@ def test_attention_mma_finds_one_far_key_among_hundreds():
                     torch.testing.assert_close(out[r].cpu().float(), v, rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_tcgen05_and_wide_decode_find_one_far_key_among_hundreds(d):
+    """One key among 1,500 answers the query (its score stands out by construction): prompt rows on the tcgen05
+    kernel and decode rows on the split kernel, at both head sizes, must return that key's value whichever block,
+    page or split it lies in."""
+    from tesseract_b200 import kernels
+
+    nh, nkv, page_size, n = 8, 2, 16, 1500
+    for target in (0, 63, 64, 127, 128, 777, 1471, 1499):
+        for new, splits in ((40, 1), (1, 5)):
+            case = paged_case(torch.bfloat16, [n], [new], nh, nkv, d, page_size, seed=target + new + d)
+            q = torch.zeros(new, nh, d)
+            q[:, :, d - 5] = 60.0
+            case["q"] = q.to(torch.bfloat16)
+            k = case["ks"][0].float()
+            k[:, :, d - 5] = 0.0
+            k[target, :, d - 5] = 8.0
+            case["ks"][0] = k.to(torch.bfloat16)
+            cache = case["cache"].float()
+            for logical in range(-(-n // page_size)):
+                pg = int(case["table"][0, logical])
+                span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+                cache[pg, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+            case["cache"] = cache.to(torch.bfloat16)
+            if new > 1:
+                row_start = torch.tensor([0, new], dtype=torch.int32)
+                seq_begin = torch.tensor([n - new], dtype=torch.int32)
+                out = torch.full((new, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+                kernels.attention_tcgen05(dev(case["q"]).view(new, nh * d), out, dev(case["cache"]), dev(row_start),
+                                          dev(seq_begin), dev(case["table"]), 1, new, nh, nkv, d, page_size, 0, 1.0)
+                assert kernels.tcgen05_error() == 0
+            else:
+                out = run_attention_mma(case, nh, nkv, d, page_size, 0, 1.0, splits)
+            v = case["vs"][0][target].float().repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+            first_pos = n - new
+            for r in range(new):
+                if first_pos + r >= target:
+                    torch.testing.assert_close(out[r].cpu().float(), v, rtol=1e-2, atol=1e-2)
+
+
 def test_silu_mul_interleaved_layout():
     from tesseract_b200 import kernels
 
