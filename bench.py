@@ -265,7 +265,7 @@ def run_ours(args):
     t0 = time.time()
     produced = 0
     for _ in range(args.steps):
-        produced += len(llm.scheduler.step().new_tokens)
+        produced += llm.scheduler.step().token_count()
     torch.cuda.synchronize()
     e2e_seconds = time.time() - t0
     windows.append((t0, time.time()))
@@ -308,7 +308,7 @@ def run_kernels(args):
 
     import torch
 
-    from tesseract_b200 import kernels
+    from tesseract_b200 import kernels, plan
 
     torch.manual_seed(0)
     dev = "cuda"
@@ -364,7 +364,7 @@ def run_kernels(args):
         out = torch.empty_like(q)
         row_start = torch.arange(batch + 1, device=dev, dtype=torch.int32)
         seq_begin = torch.full((batch,), ctx - 1, device=dev, dtype=torch.int32)
-        splits = kernels.attention_splits(batch, nkv, ctx)
+        splits = plan.attention_splits(batch, nkv, ctx)
         us = timed([lambda c=c: kernels.attention_mma(q, out, c, row_start, seq_begin, table, batch, 1, nh, nkv, d, ps, 0,
                                                       0.125, False, True, splits) for c in caches])
         mb = batch * ctx * 2 * nkv * d * 2 / 1e6
@@ -399,18 +399,6 @@ def run_kernels(args):
         t_own = timed([lambda w=w: kernels.gemm_tcgen05(x, w, out) for w in ws], reps=5)
         out_lines[f"gemm_m{tokens}_{name}"] = {"gflop": fl / 1e9, "library_us": t_lib, "library_tflops": fl / t_lib / 1e6,
                                                "tcgen05_us": t_own, "tcgen05_tflops": fl / t_own / 1e6}
-        del ws
-    # the weight-streaming tcgen05 product at a decode batch of 64 rows, against the library
-    rows = 64
-    for name, n, k in (("qkv", 3072, 2048), ("o", 2048, 2048), ("gate_up", 16384, 2048), ("down", 2048, 8192)):
-        ws = [(torch.randn(n, k, device=dev) / math.sqrt(k)).to(torch.bfloat16) for _ in range(16)]
-        x = torch.randn(rows, k, device=dev).to(torch.bfloat16)
-        out = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
-        mb = n * k * 2 / 1e6
-        out_lines[f"skinny_gemm_m{rows}_{name}"] = {
-            "weight_mb": mb, "hbm_floor_us": mb / pk["hbm_gbs"] * 1e3,
-            "library_us": timed([lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]),
-            "skinny_gemm_us": timed([lambda w=w: kernels.skinny_gemm(x, w, out) for w in ws])}
         del ws
     out_lines["tcgen05_wait_timeouts"] = kernels.tcgen05_error()
     print(json.dumps({"only": "kernels", "peaks": pk, "kernels": out_lines}))

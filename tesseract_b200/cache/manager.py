@@ -3,8 +3,9 @@
 Run entries with the same cache need (same kv heads, head size and window; or the same
 fixed-size state) form a *group*.  A paged group has its own page pool and one block
 table per live request, shared by the group's entries (each entry has its own storage
-``[pages + 1, 2, kv_heads, page_size, head_dim]`` addressed by the same page ids; page 0
-is a scratch page that no request owns, for padded rows).  A state group has storage
+``[pages + 1, *need.page_shape(page_size)]`` addressed by the same page ids, for keys and
+values ``[pages + 1, 2, kv_heads, page_size, head_dim]``; page 0 is a scratch page that no
+request owns, for padded rows).  A state group has storage
 ``[entries, slots + 1, *shape]`` addressed by the request's state slot (the last slot is scratch).  Every live request
 holds one state slot whether or not the model has state groups
 (src/engine/recurrent.rs:6-38; groups after src/engine/state.rs:31-132).
@@ -25,7 +26,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import CacheBinding, PagedKVNeed, StateNeed
+from ..parts.base import CacheBinding, PagedNeed, StateNeed
 from .pages import OutOfPages, PagePool, StateSlots
 
 
@@ -76,19 +77,19 @@ class CacheManager:
             self.groups[group].entries.append(entry)
         for group in self.groups:
             need = group.need
-            if isinstance(need, PagedKVNeed):
+            if isinstance(need, PagedNeed):
                 group.pool = PagePool(num_pages, first_page=1)
                 group.tables = np.zeros((max_requests, 8), dtype=np.int32)
-                if allocate_storage:
+                if allocate_storage:      # the need says what a page looks like; page 0 is the scratch page
                     group.storage = torch.zeros(
-                        (len(group.entries), num_pages + 1, 2, need.num_kv_heads, page_size, need.head_dim),
-                        dtype=dtype, device=device)
+                        (len(group.entries), num_pages + 1, *need.page_shape(page_size)),
+                        dtype=need.dtype or dtype, device=device)
             elif isinstance(need, StateNeed):
                 if allocate_storage:
                     group.storage = torch.zeros((len(group.entries), max_requests + 1, *need.shape),
                                                 dtype=need.dtype, device=device)
             else:
-                raise TypeError(f"unknown cache need {need!r}")
+                raise TypeError(f"a cache need is a PagedNeed or a StateNeed, got {need!r}")
         self.bindings: List[Optional[CacheBinding]] = []
         for entry, need in enumerate(needs):
             source = entry if cache_of[entry] is None else cache_of[entry]
@@ -118,8 +119,11 @@ class CacheManager:
         total = 0
         for g in self.groups:
             if g.pool is not None:
-                elem = torch.empty((), dtype=self.dtype).element_size()
-                total += len(g.entries) * 2 * g.need.num_kv_heads * g.need.head_dim * elem
+                elem = torch.empty((), dtype=g.need.dtype or self.dtype).element_size()
+                page = 1
+                for extent in g.need.page_shape(self.page_size):
+                    page *= extent
+                total += len(g.entries) * (page // self.page_size) * elem
         return total
 
     # ------------------------------------------------------------------ lifecycle

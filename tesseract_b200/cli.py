@@ -26,7 +26,7 @@ def _env(name: str, default):
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="tesseract", description="Generate tokens with a Llama model on one B200.")
+    p = argparse.ArgumentParser(prog="tesseract", description="Generate tokens with a model folder (config.json, model.safetensors) on one B200.")
     p.add_argument("--model-path", default=os.environ.get("TESSERACT_MODEL_PATH"),
                    help="folder with config.json and model.safetensors [TESSERACT_MODEL_PATH]")
     p.add_argument("--device", type=int, default=_env("DEVICE", 0))
@@ -43,6 +43,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--config", help="config.json to use with --random-weights")
     p.add_argument("--prompt", action="append", default=[], help="text prompt (needs tokenizer.json); repeatable")
     p.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; repeatable")
+    p.add_argument("--prompt-file", action="append", default=[], metavar="FILE",
+                   help="one prompt per line: token ids separated by commas or blanks (a line that is not all "
+                        "numbers is a text prompt and needs tokenizer.json); repeatable")
     p.add_argument("--random-prompt", type=int, action="append", default=[], metavar="LEN",
                    help="a prompt of LEN random token ids; repeatable")
     p.add_argument("--max-tokens", type=int, default=128)
@@ -55,13 +58,35 @@ def build_parser() -> argparse.ArgumentParser:
                    help="after loading, read the final norm's weight back from the device and compare it with the "
                         "checkpoint bit by bit (the reference's checkpoint report, src/cuda/dense_decoder.rs:1429-1463)")
     p.add_argument("--json", action="store_true", help="one JSON object per request on standard output")
+    p.add_argument("--plugin", action="append", default=[], metavar="MODULE",
+                   help="import MODULE first (it registers parts or an architecture) [TESSERACT_PLUGINS]; repeatable")
+    p.add_argument("--print-plan", action="store_true",
+                   help="print which kernel every operation of this model takes at each row count, then exit")
     return p
+
+
+def read_prompt_file(path: str):
+    """One prompt per non-empty line: a list of token ids, or the line itself as text."""
+    prompts = []
+    with open(path, encoding="utf-8") as handle:
+        for line in handle:
+            line = line.strip()
+            if not line or line.startswith("#"):
+                continue
+            fields = line.replace(",", " ").split()
+            if all(f.lstrip("-").isdigit() for f in fields):
+                prompts.append([int(f) for f in fields])
+            else:
+                prompts.append(line)
+    return prompts
 
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     from . import LLM, SamplingParams
-    from .config import read_config_json
+    from .config import load_plugins
+
+    load_plugins(args.plugin)
 
     model_path = args.model_path
     scratch = None
@@ -83,17 +108,25 @@ def main(argv=None) -> int:
               prefill_chunk_tokens=args.prefill_chunk_tokens, max_sequence_length=args.max_sequence_length,
               kv_capacity_tokens=args.kv_capacity_tokens, page_size=args.page_size,
               cuda_graphs=not args.no_cuda_graphs)
+    if args.print_plan:
+        from . import plan
+
+        print(plan.describe(llm.model, context=min(args.max_sequence_length, llm.model.spec.max_positions),
+                            page_size=args.page_size))
+        return 0
     if args.check_weights:
         from .engine.loading import check_upload
 
         print(f"weights checked: {check_upload(llm.model, model_path)} matches the checkpoint", file=sys.stderr)
-    vocab = read_config_json(model_path)["vocab_size"]
+    vocab = llm.model.spec.vocab_size
     prompts = list(args.prompt)
     prompts += [[int(t) for t in ids.split(",") if t.strip()] for ids in args.prompt_ids]
+    for path in args.prompt_file:
+        prompts += read_prompt_file(path)
     rng = random.Random(args.seed or 0)
     prompts += [[rng.randrange(vocab) for _ in range(n)] for n in args.random_prompt]
     if not prompts:
-        print("no prompt given (--prompt, --prompt-ids or --random-prompt)", file=sys.stderr)
+        print("no prompt given (--prompt, --prompt-ids, --prompt-file or --random-prompt)", file=sys.stderr)
         return 2
     params = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
                             seed=args.seed, ignore_eos=args.ignore_eos)

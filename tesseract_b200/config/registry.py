@@ -9,10 +9,12 @@ shared.
 
 from __future__ import annotations
 
+import importlib
+import os
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, Iterable, List, Mapping, Tuple
+from typing import Any, Callable, Dict, Iterable, List, Mapping, Sequence, Tuple
 
-from .model_config import NoArchitectureError, UnsupportedArchitectureError, read_config_json
+from .reading import NoArchitectureError, UnsupportedArchitectureError, read_config_json
 from .spec import ModelSpec
 
 
@@ -40,11 +42,28 @@ def known_architectures() -> List[str]:
     return sorted(_ARCHITECTURES)
 
 
+PLUGIN_VARIABLE = "TESSERACT_PLUGINS"
+_plugins_loaded: set = set()
+
+
+def load_plugins(modules: Sequence[str] = ()) -> None:
+    """Import the given modules and those named in ``$TESSERACT_PLUGINS`` (comma-separated), once each.  A plug-in
+    is an ordinary Python module that registers parts and architectures when it is imported; this is how a command
+    line or a replay program learns of an architecture that is not part of the package."""
+    named = [m.strip() for m in os.environ.get(PLUGIN_VARIABLE, "").split(",") if m.strip()]
+    for module in list(modules) + named:
+        if module not in _plugins_loaded:
+            importlib.import_module(module)
+            _plugins_loaded.add(module)
+
+
 def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
     names = config.get("architectures") or []
     if not names:
         raise NoArchitectureError("config.json names no architecture ('architectures' is missing or empty)")
     first = names[0]
+    if first not in _ARCHITECTURES:
+        load_plugins()
     if first not in _ARCHITECTURES:
         raise UnsupportedArchitectureError(
             f"unsupported architecture {list(names)} (model_type '{config.get('model_type', '')}'); "

@@ -106,8 +106,8 @@ struct AttnParams {
     const int* row_start;        // [R+1]
     const int* seq_begin;        // [R] position of the sequence's first new row
     const int* block_table;      // [R, bt_stride]
-    float* part_o;               // [splits][rows][num_heads][D]   (decode only)
-    float* part_ml;              // [splits][rows][num_heads][2]
+    float* part_o;               // [splits][num_seqs][num_kv_heads][16 folded rows][D]   (decode, > 8 splits only)
+    float* part_ml;              // [splits][num_seqs][num_kv_heads][16 folded rows][2]
     int* counters;               // [num_seqs][num_kv_heads] arrival counts of the splits; zero between launches
     int64_t q_stride, out_stride;
     int bt_stride, total_rows;
@@ -426,7 +426,9 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
                 x_ml[16 + r] = sum;
             }
         } else {
-            const int64_t slot = ((int64_t)split * p.total_rows + row) * p.num_heads + head;
+            // a slot per (split, sequence, kv head, folded row): the scratch is sized by the sequences of the
+            // step, never by its rows (a prompt portion beside the decode rows costs nothing here)
+            const int64_t slot = ((((int64_t)split * gridDim.z + seq) * p.num_kv_heads + kv_head) << 4) + r;
             p.part_o[slot * D + col] = acc;
             if (col == 0) {
                 p.part_ml[slot * 2] = big;
@@ -490,8 +492,7 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
     float* row_sum = row_big + 16;                            // [16]
     for (int idx = threadIdx.x; idx < p.splits * n_rows; idx += (WARPS * 32)) {
         const int s = idx / n_rows, r = idx - s * n_rows;
-        const int qpos = r / p.group, g = r - qpos * p.group;
-        const int64_t slot = ((int64_t)s * p.total_rows + first_row + qpos) * p.num_heads + kv_head * p.group + g;
+        const int64_t slot = ((((int64_t)s * gridDim.z + seq) * p.num_kv_heads + kv_head) << 4) + r;
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2));
         wgt[s * 16 + r] = ml.y > 0.0f ? ml.x : kMasked;        // the maximum for now
         wgt[(p.splits + 2 + s) * 16 + r] = ml.y;               // the sums, parked behind row_big / row_sum
@@ -517,8 +518,8 @@ __device__ __forceinline__ void decode_finish(const AttnParams& p, unsigned char
         const int qpos = r / p.group, g = r - qpos * p.group;
         const int head = kv_head * p.group + g;
         const int row = first_row + qpos;
-        const float* src = p.part_o + ((int64_t)row * p.num_heads + head) * D + col;
-        const int64_t split_stride = (int64_t)p.total_rows * p.num_heads * D;
+        const float* src = p.part_o + ((((int64_t)seq * p.num_kv_heads + kv_head) << 4) + r) * D + col;
+        const int64_t split_stride = (int64_t)gridDim.z * p.num_kv_heads * 16 * D;
         float acc = 0.0f;
 #pragma unroll 8
         for (int s = 0; s < p.splits; ++s) acc += wgt[s * 16 + r] * __ldcg(src + s * split_stride);
@@ -873,8 +874,9 @@ TB_EXPORT int tb_attention_mma_padded_dim(int head_dim) {
 //   run_tiles  : launch the tile kernel (sequences with more than 16 folded rows)
 //   run_decode : launch the split kernel (sequences with at most 16 folded rows) with `splits` key splits;
 //                2 to 8 splits meet as a thread-block cluster and use no scratch; more than 8 need
-//                part_o float[splits * total_rows * num_heads * padded_dim] and
-//                part_ml float[splits * total_rows * num_heads * 2]; scratch_floats is the capacity of part_o;
+//                part_o float[splits * num_seqs * num_kv_heads * 16 * padded_dim] and
+//                part_ml float[splits * num_seqs * num_kv_heads * 16 * 2] (a slot per folded row of a (split,
+//                sequence, kv head), whatever the step's row count); scratch_floats is the capacity of part_o;
 //                counters int[num_seqs * num_kv_heads], all zero before the first launch (each launch leaves
 //                them zero again).
 static int attention_entry(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
@@ -895,7 +897,7 @@ static int attention_entry(const void* q, int64_t q_stride, void* out, int64_t o
     if (splits < 1) splits = 1;
     const int cluster = splits >= 2 && splits <= kMaxClusterSplits;
     if (run_decode && splits > 1 && !cluster) {
-        const int64_t need = (int64_t)splits * total_rows * num_heads * padded;
+        const int64_t need = (int64_t)splits * num_seqs * num_kv_heads * 16 * padded;
         if (part_o == nullptr || part_ml == nullptr || counters == nullptr || need > scratch_floats) return -5;
     }
     AttnParams p;

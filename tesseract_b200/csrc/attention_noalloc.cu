@@ -41,12 +41,12 @@ int64_t round_up_64(int64_t n) { return (n + 63) / 64 * 64; }
 
 }  // namespace
 
-TB_EXPORT int64_t tb_attention_noalloc_floats_needed(int splits, int total_rows, int num_heads, int head_dim) {
+TB_EXPORT int64_t tb_attention_noalloc_floats_needed(int splits, int num_seqs, int num_kv_heads, int head_dim) {
     const int padded = tb_attention_mma_padded_dim(head_dim);
     if (padded < 0) return padded;
-    if (splits < 1) splits = 1;
-    if (total_rows < 0 || num_heads <= 0) return TB_ERR_BAD_SIZE;
-    const int64_t slots = (int64_t)splits * total_rows * num_heads;
+    if (num_seqs < 0 || num_kv_heads <= 0) return TB_ERR_BAD_SIZE;
+    if (splits <= kMaxClusterSplits) return 0;   // these meet in a thread-block cluster and never touch the array
+    const int64_t slots = (int64_t)splits * num_seqs * num_kv_heads * 16;
     return round_up_64(slots * padded) + slots * 2;
 }
 
@@ -57,10 +57,11 @@ TB_EXPORT const char* tb_attention_noalloc_strerror(int code) {
         case TB_ERR_BAD_SIZE: return "unsupported size (head_dim must be a multiple of 16 up to 256, page_size a "
                                      "power of two, num_heads a multiple of num_kv_heads)";
         case TB_ERR_BAD_ALIGN: return "q, out and cache must be 16-byte aligned and q_stride a multiple of 8";
-        case TB_NOALLOC_TOO_LARGE: return "the call needs more than the 16 MiB static scratch array "
-                                          "(splits * total_rows * num_heads * (padded_head_dim + 2) floats) or "
-                                          "more than 16384 (sequence, kv head) pairs; "
-                                          "use fewer splits or rows, or the entry point that takes scratch buffers";
+        case TB_NOALLOC_TOO_LARGE: return "with more than 8 splits the call needs more than the 16 MiB static scratch "
+                                          "array (splits * num_seqs * num_kv_heads * 16 * (padded_head_dim + 2) "
+                                          "floats) or more than 16384 (sequence, kv head) pairs; use at most 8 "
+                                          "splits (which need no scratch), fewer sequences, or the entry point "
+                                          "that takes scratch buffers";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown refusal code";
     }
 }
@@ -71,17 +72,22 @@ TB_EXPORT int tb_attention_decode_noalloc(const void* q, int64_t q_stride, void*
                                           int max_rows_per_seq, int num_heads, int num_kv_heads, int head_dim,
                                           int page_size, int window, float scale, int splits, cudaStream_t stream) {
     if (splits < 1) splits = 1;
-    const int64_t need = tb_attention_noalloc_floats_needed(splits, total_rows, num_heads, head_dim);
+    const int64_t need = tb_attention_noalloc_floats_needed(splits, num_seqs, num_kv_heads, head_dim);
     if (need < 0) return (int)need;
-    if (need > (int64_t)TB_NOALLOC_SCRATCH_FLOATS) return TB_NOALLOC_TOO_LARGE;
-    if ((int64_t)num_seqs * num_kv_heads > (int64_t)TB_NOALLOC_COUNTERS) return TB_NOALLOC_TOO_LARGE;
-    float* scratch = nullptr;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
     int* counters = nullptr;
-    if (int status = scratch_for_current_device(&scratch, &counters)) return status;
-    const int padded = tb_attention_mma_padded_dim(head_dim);
-    const int64_t part_o_floats = round_up_64((int64_t)splits * total_rows * num_heads * padded);
-    float* part_o = scratch;
-    float* part_ml = scratch + part_o_floats;
+    int64_t part_o_floats = 0;
+    if (splits > kMaxClusterSplits) {      // only these use the array and the counters; the limits are theirs alone
+        if (need > (int64_t)TB_NOALLOC_SCRATCH_FLOATS) return TB_NOALLOC_TOO_LARGE;
+        if ((int64_t)num_seqs * num_kv_heads > (int64_t)TB_NOALLOC_COUNTERS) return TB_NOALLOC_TOO_LARGE;
+        float* scratch = nullptr;
+        if (int status = scratch_for_current_device(&scratch, &counters)) return status;
+        const int padded = tb_attention_mma_padded_dim(head_dim);
+        part_o_floats = round_up_64((int64_t)splits * num_seqs * num_kv_heads * 16 * padded);
+        part_o = scratch;
+        part_ml = scratch + part_o_floats;
+    }
     return tb_attention_mma(q, q_stride, out, out_stride, cache, row_start, seq_begin, block_table, bt_stride,
                             num_seqs, total_rows, max_rows_per_seq, num_heads, num_kv_heads, head_dim, page_size,
                             window, scale, /*run_tiles=*/0, /*run_decode=*/1, splits, part_o, part_ml, part_o_floats,

@@ -13,15 +13,20 @@
 //
 // The limit.  The array holds TB_NOALLOC_SCRATCH_FLOATS 32-bit floats (16 MiB).  Every GPU on
 // which this library is loaded carries that array from load until the process exits, whether the
-// entry point is ever called or not.  A call needs
-//     splits * total_rows * num_heads * (padded_head_dim + 2) floats (+ up to 63 of padding),
-// where padded_head_dim is head_dim rounded up to 32, 64, 128 or 256; a call that needs more, or that
-// has more than TB_NOALLOC_COUNTERS (sequence, kv head) pairs (a second, 64 KiB static array counts the
-// splits that have finished for each pair), is refused with TB_NOALLOC_TOO_LARGE and nothing is launched.
+// entry point is ever called or not.  A call with at most 8 splits needs none of it (its splits meet
+// inside a thread-block cluster), so no limit applies to it, however many rows it has.  A call with
+// more than 8 splits needs
+//     splits * num_seqs * num_kv_heads * 16 * (padded_head_dim + 2) floats (+ up to 63 of padding),
+// where padded_head_dim is head_dim rounded up to 32, 64, 128 or 256: sixteen folded rows for every
+// (split, sequence, kv head), whatever the number of rows.  Such a call that needs more, or that has more
+// than TB_NOALLOC_COUNTERS (sequence, kv head) pairs (a second, 64 KiB static array counts the splits that
+// have finished for each pair), is refused with TB_NOALLOC_TOO_LARGE and nothing is launched.
 //
 // Rules of use.
-//  * The first call on each device looks the array's device address up (once, with that device
-//    current).  Make that first call outside of any stream capture.
+//  * The first call with more than 8 splits on each device looks the array's device address up (once,
+//    with that device current).  Make that first call outside of any stream capture.  Two host threads
+//    that make it at the same moment both look the address up and both store the same value, which is
+//    the only reason the unguarded cache is safe.
 //  * All calls share the arrays, and they keep whatever the last call left in them.  Nothing in the
 //    float array has to start at zero: every slot the merge step reads is written earlier in the same
 //    call.  The counters must be zero when a call starts; they are zero at load, and the split that
@@ -52,8 +57,9 @@ int tb_attention_decode_noalloc(const void* q, int64_t q_stride, void* out, int6
                                 int head_dim, int page_size, int window, float scale, int splits,
                                 cudaStream_t stream);
 
-// How many floats of the array a call with these sizes needs (negative: the sizes themselves are refused).
-int64_t tb_attention_noalloc_floats_needed(int splits, int total_rows, int num_heads, int head_dim);
+// How many floats of the array a call with these sizes needs: 0 up to 8 splits (negative: the sizes
+// themselves are refused).
+int64_t tb_attention_noalloc_floats_needed(int splits, int num_seqs, int num_kv_heads, int head_dim);
 
 // A sentence for a return code of tb_attention_decode_noalloc.
 const char* tb_attention_noalloc_strerror(int code);

@@ -25,12 +25,10 @@ namespace {
 using namespace tbtma;
 
 constexpr int BM = 128;          // folded query rows per CTA
-#ifndef TB_ATTN_BN
-#define TB_ATTN_BN 128
-#endif
-// Keys per block for head_dim 64: 128 (two CTAs per SM) or 64 (three).  head_dim 128 takes 64 keys per block, which
-// lets two CTAs share an SM (112 KiB of shared memory and 256 tensor-memory columns each).
-constexpr int kBlockKeys64 = TB_ATTN_BN;
+// Keys per block for head_dim 64: 128, two CTAs per SM (64 with three CTAs per SM was faster only beyond some 4,000
+// tokens of context).  head_dim 128 takes 64 keys per block, which lets two CTAs share an SM (112 KiB of shared
+// memory and 256 tensor-memory columns each).
+constexpr int kBlockKeys64 = 128;
 constexpr int STAGES = 2;        // K/V ring depth
 constexpr int kThreads = 192;         // warps 0..3 softmax, warp 4 issuer, warp 5 TMA producer
 // A swizzled tile of 128 rows x 64 bfloat16 (128 bytes a row): the unit that Q, P, K and V tiles are made of.  A Q

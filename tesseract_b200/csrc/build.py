@@ -32,7 +32,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 INCLUDES: Dict[str, List[str]] = {
     "attention_noalloc": ["attention_mma.cu", "attention_noalloc.h"],
     "attention_tcgen05": ["tma.cuh"],
-    "skinny_gemm": ["tma.cuh"],
+    "gemm_tcgen05": ["tma.cuh"],
 }
 
 # Every source file, with the extra flags it needs.
@@ -47,7 +47,6 @@ SOURCES: Dict[str, List[str]] = {
     "gemm_f32": [],
     "decode_linear": [],
     "gemm_tcgen05": [],
-    "skinny_gemm": [],
     "sampling": [],
 }
 

@@ -14,11 +14,11 @@
 // Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by the TMA unit and never stored.
 // Every wait on an mbarrier is bounded: a wait that runs out sets *error, tells the other roles to stop, and the
 // CTA still frees its tensor memory before it returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace {
+
+using namespace tbtma;
 
 constexpr int BM = 128, BK = 64;
 // Tiles of 128 x 256 with a four-stage ring; products of at most 128 rows (one row of tiles) take 128 x 128 tiles
@@ -31,38 +31,10 @@ template <int BN>
 constexpr uint32_t kStageBytes = kATileBytes + BN * BK * 2;
 template <int BN>
 constexpr uint32_t kTmemColumns = 2 * BN;   // two accumulators of BN columns
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-// Bounded wait: false if the barrier did not flip within the limit or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 1023) == 1023 && *abort_flag) return false;
-    }
-    return false;
-}
+// smem_u32, the mbarrier helpers (every wait bounded) and the tensor-map encoder come from tma.cuh
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile(
@@ -188,7 +160,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(acc_full0 + 8 * b, 1);
             mbar_init(acc_empty0 + 8 * b, 4);      // one arrival per epilogue warp
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
@@ -294,22 +266,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
     }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
 }
 
 // A row-major [rows, cols] bfloat16 matrix with `stride` elements between rows, cut into boxes of box_rows x 64.

@@ -33,6 +33,17 @@ def _next_pow2(n: int) -> int:
     return p
 
 
+def graph_safe(model) -> bool:
+    """Whether a step of this model may be captured: every part that runs in it (each block's norms, mixer and
+    feed-forward, the embedding, the final norm and the head) declares ``graph_safe``, i.e. that everything which
+    varies between two steps of the same shape reaches it through device tensors, never through a host-side field
+    of the step context."""
+    parts = [model.embedding, model.final_norm, model.head]
+    for block in model.layers:
+        parts += [block.mixer, block.feed_forward, *block.norms.values()]
+    return all(getattr(part, "graph_safe", False) for part in parts)
+
+
 HOST_RING = 3          # pinned copies of a graph's metadata: a launch may be prepared while two are still in flight
 
 
@@ -165,7 +176,7 @@ class DecodeGraphs:
         self.replays = 0
         self.captures = 0
         self.kernels_replayed = 0
-        self.safe = all(getattr(block.mixer, "graph_safe", False) for block in stepper.model.layers)
+        self.safe = graph_safe(stepper.model)
         widest = max(_next_pow2(max_batch), max_batch)
         self.sampled = torch.zeros(widest, dtype=torch.int32, device=stepper.runtime.device)
         self._token_ring = [torch.zeros(widest, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
@@ -313,8 +324,10 @@ class ChunkGraphs:
     configured portion size) and wants nothing or its last place; every other sequence brings one decoded token
     and wants it.  Between two such steps only device metadata differs (token ids, positions, block tables), so
     the launches of the whole model are replayed instead of issued one by one; at 2,048 rows of the 1B sizes that
-    takes the step from 4.6 to 3.9 ms.  One graph per (decode rows rounded up to a power of two, wants-last);
-    rows that pad the decode part point at the scratch page and the scratch state slot."""
+    takes the step from 4.6 to 3.9 ms.  One graph per (decode rows rounded up to a power of two, wants-last,
+    block-table width rounded up to a power of two): the width bounds the context, and with it the split count
+    that the decode rows' attention is captured with, as for the decode graphs.  Rows that pad the decode part
+    point at the scratch page and the scratch state slot."""
 
     def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int, max_decodes: int):
         self.stepper = stepper
@@ -322,10 +335,10 @@ class ChunkGraphs:
         self.max_decodes = max_decodes
         page = stepper.cache.page_size
         self.columns = max(1, -(-min(max_sequence_length, stepper.max_positions) // page))
-        self.graphs: Dict[Tuple[int, bool], _ChunkGraph] = {}
+        self.graphs: Dict[Tuple[int, bool, int], _ChunkGraph] = {}
         self.replays = 0
         self.kernels_replayed = 0
-        self.safe = all(getattr(block.mixer, "graph_safe", False) for block in stepper.model.layers)
+        self.safe = graph_safe(stepper.model)
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not self.safe or not entries or len(entries) - 1 > self.max_decodes:
@@ -345,12 +358,15 @@ class ChunkGraphs:
         rows, decodes = self.rows, len(entries) - 1
         wants_last = bool(entries[0].want)
         bucket = 0 if decodes == 0 else min(_next_pow2(decodes), max(self.max_decodes, decodes))
-        graph = self.graphs.get((bucket, wants_last))
-        if graph is None:
-            graph = _ChunkGraph(stepper, rows, bucket, wants_last, self.columns)
-            self.graphs[(bucket, wants_last)] = graph
-        total, seqs = rows + bucket, 1 + bucket
         begins = [cache.length(e.request) for e in entries]
+        pages = -(-max(b + len(e.tokens) for b, e in zip(begins, entries)) // cache.page_size)
+        columns = min(self.columns, max(8, _next_pow2(pages)))
+        key = (bucket, wants_last, columns)
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = _ChunkGraph(stepper, rows, bucket, wants_last, columns)
+            self.graphs[key] = graph
+        total, seqs = rows + bucket, 1 + bucket
         for entry in entries:
             cache.extend(entry.request, len(entry.tokens))
         index = graph.next_host

@@ -95,6 +95,22 @@ class LLM:
             raise RuntimeError(f"a bounded wait inside a tcgen05 kernel ran out (code {code}); the generated "
                                f"tokens of this call are unreliable")
 
+    def replay(self, trace) -> List[Optional["torch.Tensor"]]:
+        """Feed given token ids step by step and return the logits at the wanted places: for each step of ``trace``
+        (``{"step", "entries": [{"id", "tokens", "want"}], "end"}``, the replay program's records) float32
+        ``[wanted, vocab]`` on the host, or ``None``.  It drives this engine's own step function and cache and
+        samples nothing; use it while no generation is in flight."""
+        from .replay import TraceRunner
+
+        if self.scheduler.has_work():
+            raise RuntimeError("replay needs an idle engine: generation is in flight")
+        runner = TraceRunner(self.stepper)
+        out = []
+        for record in trace:
+            logits = runner.step(record)
+            out.append(None if logits is None else logits.cpu())
+        return out
+
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:
         """Generate for every prompt under continuous batching; outputs in the order of the prompts."""

@@ -99,11 +99,23 @@ class ScheduledSequence:
 
 @dataclass
 class StepResult:
-    """What one scheduler iteration did."""
+    """What one scheduler iteration did.  ``new_tokens`` holds, per request, the tokens it received in this
+    iteration, oldest first (two when a step launched ahead was read back and an ordinary step followed)."""
 
     batch: List[ScheduledSequence]
-    new_tokens: Dict[Hashable, int]
+    new_tokens: Dict[Hashable, List[int]]
     finished: List[Request]
+
+    def token_count(self) -> int:
+        return sum(len(tokens) for tokens in self.new_tokens.values())
+
+    def absorb_earlier(self, earlier: "StepResult") -> None:
+        """Put the tokens and endings of a step that was read back before this one in front of this one's."""
+        merged = {request: list(tokens) for request, tokens in earlier.new_tokens.items()}
+        for request, tokens in self.new_tokens.items():
+            merged.setdefault(request, []).extend(tokens)
+        self.new_tokens = merged
+        self.finished[:0] = earlier.finished
 
 
 class Scheduler:
@@ -240,8 +252,7 @@ class Scheduler:
         else:
             result = self._apply(batch, sampled, tokens)
         if drained is not None:
-            result.new_tokens.update(drained.new_tokens)
-            result.finished[:0] = drained.finished
+            result.absorb_earlier(drained)
         return result
 
     def _fail(self, batch, exc) -> StepResult:
@@ -276,9 +287,7 @@ class Scheduler:
             self._inflight = None
             result = self._fail(batch, exc)
             if previous is not None:
-                earlier = self._collect(previous)
-                result.new_tokens.update(earlier.new_tokens)
-                result.finished[:0] = earlier.finished
+                result.absorb_earlier(self._collect(previous))
             return result
         for s in batch:
             s.request.computed_tokens += 1
@@ -305,7 +314,7 @@ class Scheduler:
                 raise RuntimeError("the sampler returned a wrong number of tokens")
         except Exception as exc:  # noqa: BLE001
             return self._fail(batch, exc)
-        new_tokens: Dict[Hashable, int] = {}
+        new_tokens: Dict[Hashable, List[int]] = {}
         finished: List[Request] = []
         for s, token in zip(batch, tokens):
             request = s.request
@@ -313,7 +322,7 @@ class Scheduler:
                 continue                                  # ended meanwhile: this row was computed in vain
             token = int(token)
             request.generated[s.slot] = token
-            new_tokens[request.id] = token
+            new_tokens.setdefault(request.id, []).append(token)
             reason = self._stop_reason(request, token, s.slot + 1)
             if reason is not None:
                 del request.generated[s.slot + 1:]        # a token launched after the last one is dropped
@@ -333,7 +342,7 @@ class Scheduler:
         return None
 
     def _apply(self, batch, sampled, tokens) -> StepResult:
-        new_tokens: Dict[Hashable, int] = {}
+        new_tokens: Dict[Hashable, List[int]] = {}
         finished: List[Request] = []
         for s in batch:
             s.request.computed_tokens += len(s.tokens)
@@ -341,7 +350,7 @@ class Scheduler:
             request = s.request
             token = int(token)
             request.generated.append(token)
-            new_tokens[request.id] = token
+            new_tokens.setdefault(request.id, []).append(token)
             reason = self._stop_reason(request, token, len(request.generated))
             if reason is not None:
                 done = self._finish(request.id, reason)

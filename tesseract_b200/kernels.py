@@ -256,55 +256,72 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return out
 
 
-_SM_COUNT = 148
-_attention_scratch = {}
+_sm_counts = {}
 
 
-def _scratch(device, name: str, floats: int) -> torch.Tensor:
-    """A float32 work buffer that only ever grows (shared by all layers; they run one after another)."""
-    key = (device, name)
-    buf = _attention_scratch.get(key)
-    if buf is None or buf.numel() < floats:
-        buf = torch.empty(max(floats, 1024), dtype=torch.float32, device=device)
-        _attention_scratch[key] = buf
-    return buf
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device, never assumed)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    count = _sm_counts.get(index)
+    if count is None:
+        count = int(torch.cuda.get_device_properties(index).multi_processor_count)
+        _sm_counts[index] = count
+    return count
 
 
-_attention_counters = {}
+MAX_ATTENTION_SPLITS = 32
+_CLUSTER_SPLITS = 8          # up to this many splits merge inside a thread-block cluster and use no scratch
 
 
-def _counters(device, count: int) -> torch.Tensor:
-    """Zeroed int32 arrival counters for the split decode kernel (each launch leaves them zero again)."""
-    buf = _attention_counters.get(device)
-    if buf is None or buf.numel() < count:
-        buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
-        _attention_counters[device] = buf
-    return buf
+class _AttentionWorkspace:
+    """The split decode attention's scratch memory on one device: partial results and arrival counters for more
+    than eight splits.  It is allocated once, at the largest size ``plan.attention_splits`` can ask for, and never
+    replaced or freed: a captured CUDA graph holds its addresses for as long as the process lives.
+
+    A (split, sequence, kv head) CTA owns sixteen folded rows of ``padded`` floats, and ``plan.attention_splits``
+    never chooses more CTAs than are resident at once (two per SM), so ``2 * SMs * 16 * 256`` floats cover every
+    choice of it at every head size, whatever the step's row count.  A caller that names its own split count may
+    bring more CTAs of narrower heads into the same floats (the narrowest padded head is 32 wide), so the maxima
+    and sums are sized for that many."""
+
+    def __init__(self, device):
+        ctas = 2 * sm_count(device)
+        self.part_o = torch.empty(ctas * 16 * 256, dtype=torch.float32, device=device)
+        self.max_ctas = self.part_o.numel() // (16 * 32)
+        self.part_ml = torch.empty(self.max_ctas * 16 * 2, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(max(4096, self.max_ctas), dtype=torch.int32, device=device)   # left zero by every launch
 
 
-def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64) -> int:
-    """How many key splits the decode kernel uses.
+_attention_workspaces = {}
 
-    A CTA's warps (eight up to a head size of 64, six up to 128, four above) each stream their share of the tiles
-    of 16 keys at about 0.65 microseconds a tile of 64-wide heads (wider heads in proportion); merging splits
-    costs about 2.5 microseconds inside a thread-block cluster (up to 8 splits) and 5 through scratch memory; two
-    CTAs fit an SM up to a head size of 128, one above.  The choice minimises that estimate over the split counts
-    that keep all CTAs resident at once (at most 32: one sequence of 131,072 tokens reads its keys at 5.2 TB/s
-    with 32 splits, 4.5 with 16)."""
-    tiles = -(-max_context // 16)
-    warps = 8 if head_dim <= 64 else 6 if head_dim <= 128 else 4
-    ctas = max(1, num_seqs * num_kv_heads)
-    per_sm = 2 if head_dim <= 128 else 1
-    tile_cost = 0.65 * max(1.0, head_dim / 64.0)
-    limit = max(1, min(32, per_sm * _SM_COUNT // ctas))
-    best, best_cost = 1, float("inf")
-    for splits in range(1, limit + 1):
-        per_warp = -(-(-(-tiles // splits)) // warps)
-        merge = 0.0 if splits == 1 else 2.5 if splits <= 8 else 5.0
-        cost = tile_cost * per_warp + merge + 0.15 * splits
-        if cost < best_cost:
-            best, best_cost = splits, cost
-    return best
+
+def _split_scratch(device, splits: int, num_seqs: int, num_kv_heads: int, padded: int):
+    """``(part_o, part_ml, counters)`` for a launch of more than eight splits.  What fits the device's permanent
+    workspace uses it; a larger call (only a caller that names its own split count can make one) gets buffers of
+    its own for this launch, which the allocator keeps valid in stream order and, inside a graph capture, for the
+    life of the graph."""
+    work = _attention_workspaces.get(device)
+    if work is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention workspace must exist before a graph is captured "
+                              "(call kernels.attention_workspace(device) first)")
+        work = _AttentionWorkspace(device)
+        _attention_workspaces[device] = work
+    ctas = splits * num_seqs * num_kv_heads
+    if ctas * 16 * padded <= work.part_o.numel() and ctas <= work.max_ctas:
+        return work.part_o, work.part_ml, work.counters
+    return (torch.empty(ctas * 16 * padded, dtype=torch.float32, device=device),
+            torch.empty(ctas * 16 * 2, dtype=torch.float32, device=device),
+            torch.zeros(num_seqs * num_kv_heads, dtype=torch.int32, device=device))
+
+
+def attention_workspace(device) -> None:
+    """Create the device's permanent attention workspace now (before any graph capture)."""
+    device = torch.device(device)
+    if device not in _attention_workspaces:
+        _attention_workspaces[device] = _AttentionWorkspace(device)
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,
@@ -329,11 +346,8 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_s
         raise KernelError(f"attention_mma: head_dim {head_dim} is not a multiple of 16 up to 256")
     part_o = part_ml = counters = None
     capacity = 0
-    if run_decode and splits > 1:
-        counters = _counters(q.device, num_seqs * num_kv_heads)
-        capacity = splits * rows * num_heads * padded
-        part_o = _scratch(q.device, "part_o", capacity)
-        part_ml = _scratch(q.device, "part_ml", splits * rows * num_heads * 2)
+    if run_decode and splits > _CLUSTER_SPLITS:
+        part_o, part_ml, counters = _split_scratch(q.device, splits, num_seqs, num_kv_heads, padded)
         capacity = part_o.numel()
     _check(lib.tb_attention_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                 _ptr(row_start), _ptr(seq_begin), _ptr(block_table), _i32(block_table.stride(0)),
@@ -374,10 +388,8 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Ten
         raise KernelError(f"attention_decode_rope: head_dim {head_dim} is not a multiple of 16 up to 256")
     part_o = part_ml = counters = None
     capacity = 0
-    if splits > 8:
-        counters = _counters(qkv.device, num_seqs * num_kv_heads)
-        part_o = _scratch(qkv.device, "part_o", splits * num_seqs * num_heads * padded)
-        part_ml = _scratch(qkv.device, "part_ml", splits * num_seqs * num_heads * 2)
+    if splits > _CLUSTER_SPLITS:
+        part_o, part_ml, counters = _split_scratch(qkv.device, splits, num_seqs, num_kv_heads, padded)
         capacity = part_o.numel()
     _check(lib.tb_attention_decode_rope(_ptr(qkv), _i64(qkv.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                         _ptr(row_start), _ptr(seq_begin), _ptr(block_table),
@@ -391,18 +403,6 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Ten
 
 PRO_NONE, PRO_NORM, PRO_ADD_NORM = 0, 1, 2
 EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
-# From this many rows on (the skinny decode product takes up to 16), gate/up + SwiGLU in one tcgen05 GEMM beats the
-# library product plus the activation kernel: a decode step of 32 rows 1.48 -> 1.42 ms, of 64 rows 1.91 -> 1.89 ms
-# with the 128-wide tiles that products of at most 128 rows get; 100 against 114 us per product at 2,048 rows.
-FUSED_GATE_UP_MIN_ROWS = 17
-
-
-# Up to how many rows the engine sends a product to decode_linear: plain, and with the norm folded in.  Sixteen is
-# what the kernel takes; against the library product with norm and activation kernels of their own a decode step
-# of 16 rows takes 1.12 instead of 1.33 ms.
-DECODE_LINEAR_MAX_ROWS = 16
-DECODE_LINEAR_NORMED_MAX_ROWS = 16
-
 
 def decode_linear_supported(rows: int, out_features: int, in_features: int, prologue: int = PRO_NONE) -> bool:
     """Whether the skinny decode product takes these sizes (else the caller uses the general path)."""
@@ -484,33 +484,6 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     _check(lib.tb_gemm_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
                                _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
                                _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
-    return out
-
-
-def skinny_gemm_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
-    """Whether the weight-streaming tcgen05 product takes these sizes (at most 128 rows)."""
-    if epilogue not in (EPI_BF16, EPI_SWIGLU):
-        return False
-    return bool(load_library("skinny_gemm").tb_skinny_gemm_supported(_i32(rows), _i32(out_features),
-                                                                    _i32(in_features), _i32(epilogue)))
-
-
-def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16) -> torch.Tensor:
-    """``out = x @ weight^T`` for at most 128 rows on the tcgen05 tensor cores, the weights streamed once
-    (bfloat16 in and out, 32-bit accumulation, K split over a thread-block cluster for narrow outputs).
-
-    ``EPI_BF16`` stores ``[M, N]``; ``EPI_SWIGLU`` takes a weight whose rows interleave eight gate rows and their
-    eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``."""
-    _cuda(x, weight, out)
-    m, k = x.shape
-    n = weight.shape[0]
-    _need(x.dtype == weight.dtype == out.dtype == torch.bfloat16, "skinny_gemm takes bfloat16")
-    _need(weight.shape[1] == k and x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1, "gemm layout")
-    _need(out.shape == (m, n // 2 if epilogue == EPI_SWIGLU else n), "skinny_gemm out shape")
-    lib = load_library("skinny_gemm")
-    _check(lib.tb_skinny_gemm(_ptr(x), _i64(x.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
-                              _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
-                              _ptr(_error_word(x.device)), _stream()), "skinny_gemm")
     return out
 
 

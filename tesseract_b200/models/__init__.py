@@ -2,3 +2,4 @@
 
 from . import llama  # noqa: F401  (registration)
 from .decoder import DecoderModel, expected_tensors, tensor_roles
+from .llama_config import LlamaConfig, RopeScaling

@@ -82,13 +82,10 @@ class DecoderModel:
             feed_forward = build(FEED_FORWARDS, layer.feed_forward)
             self.layers.append(block_cls(norms, mixer, feed_forward))
         self.final_norm = build(NORMS, spec.final_norm)
-        tied = (spec.head.weights.get("weight") is not None
-                and spec.head.weights.get("weight") == spec.embedding.weights.get("table")
-                and hasattr(self.embedding, "table"))
-        if tied and spec.head.kind == "lm_head":
-            self.head = build(HEADS, spec.head, shared=self.embedding.table)
-        else:
-            self.head = build(HEADS, spec.head)
+        # A head that names the embedding's checkpoint tensor (tied embeddings) gets the same host tensor, and the
+        # runtime hands it the device copy that the embedding made: tying is a matter of tensor names alone.
+        self.head = build(HEADS, spec.head)
+        runtime.forget_uploads()
 
     # ------------------------------------------------------------------ cache description
     def cache_needs(self) -> List[Optional[object]]:

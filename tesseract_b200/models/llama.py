@@ -8,7 +8,7 @@ Tensor names are the checkpoint's own (src/model/llama_3_2.rs:226-266).
 
 from __future__ import annotations
 
-from ..config.model_config import LlamaConfig
+from .llama_config import LlamaConfig
 from ..config.registry import Architecture, register_architecture
 from ..config.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
 

@@ -1,46 +1,20 @@
-"""Typed model configuration read from a model folder's ``config.json``.
+"""Typed configuration of ``LlamaForCausalLM``, read from ``config.json``.
 
-The Llama reader mirrors the keys that the reference's Llama module reads
+The reader mirrors the keys that the reference's Llama module reads
 (src/model/llama_3_2.rs:72-94) and its validation (src/model/llama_3_2.rs:108-174),
 relaxed where the reference ties itself to one checkpoint: ``rope_scaling`` may
 be absent or null, ``eos_token_id`` may be one integer, ``head_dim`` defaults to
 ``hidden_size / num_attention_heads`` and need not multiply back to
 ``hidden_size``, and ``torch_dtype`` may be ``float32``.
-
-No size or constant that ``config.json`` gives is repeated anywhere else in the
-package: every part receives its numbers from the objects built here.
 """
 
 from __future__ import annotations
 
-import json
 import math
-import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Mapping, Optional, Tuple
 
-
-class ConfigError(ValueError):
-    """A ``config.json`` that is missing a key, has a wrong type or breaks an invariant."""
-
-
-class NoArchitectureError(ConfigError):
-    """``config.json`` names no architecture (src/model/mod.rs:190-202)."""
-
-
-class UnsupportedArchitectureError(ConfigError):
-    """``config.json`` names an architecture that no model is registered for."""
-
-
-def _require(data: Mapping[str, Any], key: str, kinds, what: str = "config.json"):
-    if key not in data or data[key] is None:
-        raise ConfigError(f"{what}: missing required key '{key}'")
-    value = data[key]
-    if isinstance(value, bool) and bool not in (kinds if isinstance(kinds, tuple) else (kinds,)):
-        raise ConfigError(f"{what}: key '{key}' must be {kinds}, got bool")
-    if not isinstance(value, kinds):
-        raise ConfigError(f"{what}: key '{key}' has type {type(value).__name__}, expected {kinds}")
-    return value
+from ..config.reading import ConfigError, require as _require
 
 
 @dataclass(frozen=True)
@@ -227,17 +201,3 @@ class LlamaConfig:
             "bos_token_id": self.bos_token_id,
             "eos_token_id": list(self.eos_token_id),
         }
-
-
-def read_config_json(model_dir: str) -> dict:
-    path = os.path.join(model_dir, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as handle:
-            data = json.load(handle)
-    except FileNotFoundError as exc:
-        raise ConfigError(f"{path}: no such file") from exc
-    except json.JSONDecodeError as exc:
-        raise ConfigError(f"{path}: invalid JSON: {exc}") from exc
-    if not isinstance(data, dict):
-        raise ConfigError(f"{path}: top level must be an object")
-    return data

@@ -17,7 +17,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from .. import kernels
+from .. import kernels, plan
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
 from .base import (MIXERS, POSITION_ENCODINGS, CacheBinding, DeferredNorm, Mixer, PagedKVNeed, Runtime,
@@ -56,11 +56,12 @@ class Attention(Mixer):
         self.prompt_kernel = str(p.get("prompt_kernel") or "tcgen05")
         if self.prompt_kernel not in ("mma", "tcgen05"):
             raise ValueError(f"prompt_kernel must be 'mma' or 'tcgen05', got '{self.prompt_kernel}'")
-        self._tcgen05 = None      # decided at the first prompt portion (needs the cache's page size)
         position_spec = spec.children.get("position")
         if position_spec is None:
             position_spec = PartSpec.make("none")
         self.position = POSITION_ENCODINGS.get(position_spec.kind)(position_spec, {}, runtime)
+        if not runtime.is_float32:
+            kernels.attention_workspace(runtime.device)     # permanent: captured graphs keep its addresses
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -91,15 +92,17 @@ class Attention(Mixer):
         inv_freq = self.position.rotary_inv_freq
         rows = qkv.shape[0]
         attended = torch.empty((rows, self.q_width), dtype=qkv.dtype, device=qkv.device)
-        fold = self.num_heads // self.num_kv_heads
-        if (not self.runtime.is_float32 and fold <= 16 and ctx.max_new == 1 and ctx.num_seqs == rows
-                and (inv_freq is not None or self.position.kind == "none")):
+        new_tokens = ctx.host_new if len(ctx.host_new) == ctx.num_seqs else [ctx.max_new] * ctx.num_seqs
+        choice = plan.attention(self.runtime.dtype, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                                head_dim=self.head_dim, page_size=cache.page_size, new_tokens=new_tokens,
+                                max_context=ctx.max_context, prompt_kernel=self.prompt_kernel,
+                                rotary_in_kernel=inv_freq is not None or self.position.kind == "none")
+        if choice.fused_decode:
             # a pure decode step: rotation, cache write and attention in one kernel
-            splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context, self.head_dim)
             kernels.attention_decode_rope(qkv, attended, cache.storage, ctx.row_start, ctx.seq_begin,
                                           group.block_table, ctx.num_seqs, self.num_heads, self.num_kv_heads,
                                           self.head_dim, cache.page_size, self.window, self.scale, inv_freq,
-                                          cache.writes, splits)
+                                          cache.writes, choice.splits)
             return self.o_proj.forward(attended)
         if inv_freq is None and self.position.kind != "none":
             q_view = qkv[:, :self.q_width].view(rows, self.num_heads, self.head_dim)
@@ -109,30 +112,20 @@ class Attention(Mixer):
                               self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
                               write_kv=cache.writes)
         q = qkv[:, :self.q_width]
-        self._attend(q, attended, cache, ctx, group)
-        return self.o_proj.forward(attended)
-
-    def _attend(self, q, out, cache: CacheBinding, ctx: StepContext, group) -> None:
-        if self.runtime.is_float32:
+        if choice.rows:
             # the 32-bit path: one warp per (row, head), a fixed order of every reduction
-            kernels.attention_rows(q, out, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+            kernels.attention_rows(q, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                    self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
                                    self.scale)
-            return
-        fold = self.num_heads // self.num_kv_heads
-        long_seqs = any(n * fold > 16 for n in ctx.host_new)
-        short_seqs = any(n * fold <= 16 for n in ctx.host_new)
-        splits = kernels.attention_splits(ctx.num_seqs, self.num_kv_heads, ctx.max_context, self.head_dim) if short_seqs else 1
-        if long_seqs and self.prompt_kernel == "tcgen05" and self._tcgen05 is None:
-            self._tcgen05 = kernels.attention_tcgen05_supported(self.num_heads, self.num_kv_heads, self.head_dim,
-                                                                cache.page_size)
-        if long_seqs and self._tcgen05:
+            return self.o_proj.forward(attended)
+        tiles = choice.prompt == "mma_tiles"
+        if choice.prompt == "tcgen05":
             # prompt portions on the fifth-generation tensor cores; decode rows (if any) by the split kernel
-            kernels.attention_tcgen05(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
+            kernels.attention_tcgen05(q, attended, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
                                       ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
                                       cache.page_size, self.window, self.scale)
-            long_seqs = False
-        if long_seqs or short_seqs:
-            kernels.attention_mma(q, out, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
+        if tiles or choice.split:
+            kernels.attention_mma(q, attended, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
                                   ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
-                                  cache.page_size, self.window, self.scale, long_seqs, short_seqs, splits)
+                                  cache.page_size, self.window, self.scale, tiles, choice.split, choice.splits)
+        return self.o_proj.forward(attended)

@@ -76,34 +76,69 @@ class Registry(Generic[T]):
 
 @dataclass(frozen=True)
 class Runtime:
-    """Where and in which precision a model runs."""
+    """Where and in which precision a model runs.
+
+    While a model is being built, a checkpoint tensor that two parts name (an output head tied to the embedding
+    table, say) is uploaded once: ``matrix`` and ``vector_f32`` hand the second part the first part's device copy.
+    The builder calls :meth:`forget_uploads` when it is done."""
 
     dtype: torch.dtype
     device: torch.device
+    _uploads: Dict[Tuple[int, torch.dtype], Tuple[torch.Tensor, torch.Tensor]] = field(
+        default_factory=dict, compare=False, repr=False)
 
     @property
     def is_float32(self) -> bool:
         return self.dtype == torch.float32
 
+    def _upload(self, tensor: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        key = (id(tensor), dtype)
+        known = self._uploads.get(key)
+        if known is not None and known[0] is tensor:
+            return known[1]
+        uploaded = tensor.to(device=self.device, dtype=dtype).contiguous()
+        self._uploads[key] = (tensor, uploaded)
+        return uploaded
+
     def matrix(self, tensor: torch.Tensor) -> torch.Tensor:
         """A weight matrix in the run dtype on the run device (bfloat16 widens exactly)."""
-        return tensor.to(device=self.device, dtype=self.dtype).contiguous()
+        return self._upload(tensor, self.dtype)
 
     def vector_f32(self, tensor: torch.Tensor) -> torch.Tensor:
         """A scale vector kept in (or widened exactly to) 32-bit."""
-        return tensor.to(device=self.device, dtype=torch.float32).contiguous()
+        return self._upload(tensor, torch.float32)
+
+    def forget_uploads(self) -> None:
+        self._uploads.clear()
 
 
 # ----------------------------------------------------------------------------- cache needs
 
 
+class PagedNeed:
+    """What a mixer keeps per token, in pages.  A subclass (a frozen dataclass, so that equal needs share a group)
+    gives the shape of one page of one run entry, ``page_shape(page_size)``, and optionally ``window`` (only the
+    last ``window`` tokens are read; older pages go back to the pool) and ``dtype`` (``None``: the model's).  The
+    cache manager allocates ``[entries, pages + 1, *page_shape]`` and hands each entry its ``[pages + 1, ...]``."""
+
+    window: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
-class PagedKVNeed:
-    """Keys and values of every token (``window`` None) or of the last ``window`` tokens."""
+class PagedKVNeed(PagedNeed):
+    """Keys and values of every token (``window`` None) or of the last ``window`` tokens:
+    a page is ``[2 (K, V), kv_heads, page_size, head_dim]``."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (2, self.num_kv_heads, page_size, self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -219,6 +254,11 @@ class DeferredNorm:
 
 class Part:
     kind: str = ""
+    # True if everything that varies between two steps of the same shape reaches ``forward`` through device
+    # tensors (never through a host-side field of the step context): only then may a step be captured in a CUDA
+    # graph.  Every part of a model is asked (norms, mixers, feed-forwards, embedding, head); the parts of this
+    # package set it, a new part has to say so itself.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
@@ -253,10 +293,6 @@ class PositionEncoding(Part):
 class Mixer(Part):
     # True if ``forward`` also takes a :class:`DeferredNorm` in place of ``x``.
     accepts_deferred_norm = False
-    # True if ``forward`` takes everything that varies from step to step from device tensors of the
-    # context (never from its host lists), so that a decode step may be captured in a CUDA graph.
-    graph_safe = False
-
     def cache_need(self):
         return None
 

@@ -2,7 +2,7 @@
 
 The head multiplies the normalised hidden rows by the ``[vocab, hidden]`` matrix
 (src/cuda/dense_decoder.rs:824-831) and returns 32-bit logits.  With tied embeddings the
-model builder hands both parts the same checkpoint tensor, and both keep one device copy.
+model description names one checkpoint tensor for both parts, and both keep one device copy.
 """
 
 from __future__ import annotations
@@ -21,6 +21,8 @@ from .linear import Linear
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
     """params: ``vocab_size, hidden_size``; weights: ``table``."""
+
+    graph_safe = True
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         super().__init__(spec, tensors, runtime)
@@ -43,18 +45,13 @@ class TokenEmbedding(Embedding):
 class LMHead(Head):
     """params: ``vocab_size, hidden_size``; weights: ``weight``.  Returns float32 logits."""
 
-    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime,
-                 shared: Optional[torch.Tensor] = None):
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         super().__init__(spec, tensors, runtime)
         self.vocab_size = int(spec.params["vocab_size"])
         self.hidden_size = int(spec.params["hidden_size"])
-        if shared is not None:
-            self.proj = Linear.__new__(Linear)
-            self.proj.runtime = runtime
-            self.proj.weight = shared
-            self.proj.out_features, self.proj.in_features = shared.shape
-        else:
-            self.proj = Linear(tensors["weight"], runtime)
+        self.proj = Linear(tensors["weight"], runtime)     # the embedding's device copy if both name one tensor
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:

@@ -14,7 +14,7 @@ from typing import Dict, Mapping
 
 import torch
 
-from .. import kernels
+from .. import kernels, plan
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
 from .base import FEED_FORWARDS, DeferredNorm, FeedForward, Runtime, StepContext
@@ -24,6 +24,8 @@ from .linear import Linear
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
     """params: ``hidden_size, intermediate_size``; weights: ``gate, up, down``."""
+
+    graph_safe = True
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         super().__init__(spec, tensors, runtime)
@@ -55,25 +57,16 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx: StepContext) -> torch.Tensor:
         activated = None
+        epilogue = plan.SWIGLU if self.interleaved else plan.BF16
         if isinstance(x, DeferredNorm):
-            if self.interleaved:      # norm, both projections and the activation in one kernel, if the sizes allow
-                activated = self.gate_up_proj.forward_normed(x, epilogue=kernels.EPI_SWIGLU)
+            if self.interleaved:      # norm, both projections and the activation in one kernel, if the plan has one
+                activated = self.gate_up_proj.forward_normed(x, epilogue=epilogue)
             if activated is None:
                 x = x.materialize()
+        if activated is None and self.interleaved:
+            activated = self.gate_up_proj.forward(x, epilogue=epilogue)     # both projections + SwiGLU, if planned
         if activated is None:
-            activated = self._activate(x)
+            gate_up = self.gate_up_proj.forward(x)
+            activated = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)
         return self.down_proj.forward(activated)
-
-    def _activate(self, x: torch.Tensor) -> torch.Tensor:
-        rows = x.shape[0]
-        activated = torch.empty((rows, self.intermediate_size), dtype=x.dtype, device=x.device)
-        proj = self.gate_up_proj
-        if (self.interleaved and not self.runtime.is_float32 and rows <= kernels.DECODE_LINEAR_MAX_ROWS
-                and kernels.decode_linear_supported(rows, proj.out_features, proj.in_features)):
-            return kernels.decode_linear(proj.weight, activated, x=x, epilogue=kernels.EPI_SWIGLU)
-        if (self.interleaved and not self.runtime.is_float32 and rows >= kernels.FUSED_GATE_UP_MIN_ROWS
-                and kernels.gemm_tcgen05_supported(rows, proj.out_features, proj.in_features, kernels.EPI_SWIGLU)):
-            # prompt portions: both projections on the tcgen05 tensor cores, the activation in the epilogue
-            return kernels.gemm_tcgen05(x, proj.weight, activated, epilogue=kernels.EPI_SWIGLU)
-        gate_up = proj.forward(x)
-        return kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)

@@ -21,6 +21,8 @@ from .base import NORMS, Norm, Runtime
 class RMSNorm(Norm):
     """params: ``size``, ``eps``; weights: ``weight`` ``[size]``."""
 
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         super().__init__(spec, tensors, runtime)
         params = spec.params
@@ -35,6 +37,11 @@ class RMSNorm(Norm):
     @classmethod
     def random_tensor(cls, spec, role, shape: Tuple[int, ...], generator) -> torch.Tensor:
         return 1.0 + torch.randn(shape, generator=generator, dtype=torch.float32) * 0.02
+
+    def rms_parameters(self) -> Tuple[torch.Tensor, float]:
+        """``(weight, eps)``: what a product kernel needs to compute this norm in its own first phase.  A norm that
+        has this method may be folded into the product behind it; one that has not runs its own kernel."""
+        return self.weight, self.eps
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if out is None:

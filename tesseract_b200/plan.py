@@ -1,0 +1,233 @@
+"""The kernel plan: which kernel, in which form, every operation of a step takes.
+
+One place decides, for a data type, a row count and the sizes of an operation, which of this package's kernels
+runs it (the reference resolves one plan per model and prints it: src/cuda/kernel_plan.rs:140-161, 168-239).
+The parts ask these functions and do what the answer says; ``describe`` prints the answers for a whole model
+(``tesseract --print-plan``); ``tests/test_kernel_choices.py`` pins them.  There is no other backend to dispatch
+to: a size no kernel takes is an error where the part is built or called.
+
+Thresholds, with the measurement behind each:
+
+* ``DECODE_LINEAR_MAX_ROWS`` (16): up to this many rows a product streams its weights once through the skinny
+  ``decode_linear`` kernel (mma.sync, 16 warps splitting K), with the residual addition and the RMSNorm in front
+  and SwiGLU or a 32-bit store behind folded in.  Against the library product with norm and activation kernels
+  of their own a decode step of 16 rows of the 1B sizes takes 0.94 instead of 1.33 ms.
+* ``FUSED_GATE_UP_MIN_ROWS`` (17): from here on gate/up + SwiGLU is one tcgen05 GEMM (100 against 114 us per
+  product at 2,048 rows; a decode step of 32 rows 1.48 -> 1.42 ms).
+* Plain bfloat16 products over more than 16 rows (QKV, O, down, the head) call the library GEMM, where the
+  reference calls one (src/cuda/cublas.rs:49-92).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from functools import lru_cache
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import kernels
+
+DECODE_LINEAR_MAX_ROWS = 16
+FUSED_GATE_UP_MIN_ROWS = 17
+MAX_ATTENTION_SPLITS = kernels.MAX_ATTENTION_SPLITS
+CLUSTER_SPLITS = 8            # up to this many splits merge inside a thread-block cluster; more go through scratch
+
+BF16, F32, SWIGLU = "bf16", "f32", "swiglu"
+_EPILOGUE_CODE = {BF16: kernels.EPI_BF16, F32: kernels.EPI_F32, SWIGLU: kernels.EPI_SWIGLU}
+
+
+@lru_cache(maxsize=None)
+def _decode_linear_takes(rows: int, out_features: int, in_features: int, prologue: int) -> bool:
+    return kernels.decode_linear_supported(rows, out_features, in_features, prologue)
+
+
+@lru_cache(maxsize=None)
+def _gemm_tcgen05_takes(rows: int, out_features: int, in_features: int, epilogue: int) -> bool:
+    return kernels.gemm_tcgen05_supported(rows, out_features, in_features, epilogue)
+
+
+@lru_cache(maxsize=None)
+def _attention_tcgen05_takes(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return kernels.attention_tcgen05_supported(num_heads, num_kv_heads, head_dim, page_size)
+
+
+@dataclass(frozen=True)
+class ProductPlan:
+    """``kernel``: ``gemm_f32`` (true 32-bit FFMA), ``decode_linear`` (weight streaming, at most 16 rows),
+    ``gemm_tcgen05`` (this package's tensor-memory GEMM) or ``library``.  ``norm_folded``: the RMSNorm (and the
+    residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
+    ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product."""
+
+    kernel: str
+    norm_folded: bool = False
+    epilogue: str = BF16
+    activation_apart: bool = False
+
+    @property
+    def epilogue_code(self) -> int:
+        return _EPILOGUE_CODE[self.epilogue]
+
+    def __str__(self) -> str:
+        extras = [f"{self.epilogue} store"]
+        if self.norm_folded:
+            extras.insert(0, "add+norm folded in front")
+        if self.activation_apart:
+            extras.append("SwiGLU as a kernel of its own")
+        return f"{self.kernel} ({', '.join(extras)})"
+
+
+def product(dtype: torch.dtype, rows: int, out_features: int, in_features: int, *, epilogue: str = BF16,
+            norm: Optional[str] = None, contiguous_rows: bool = True) -> ProductPlan:
+    """The kernel for ``[rows, in] @ [out, in]^T``.  ``norm``: ``"norm"`` or ``"add_norm"`` if an RMSNorm (with the
+    residual addition) stands in front and may be folded in; ``epilogue``: ``bf16``, ``f32`` (logits) or ``swiglu``
+    (the weight's rows interleave eight gates and eight up projections)."""
+    if dtype == torch.float32:
+        return ProductPlan("gemm_f32", False, F32, activation_apart=epilogue == SWIGLU)
+    if rows <= DECODE_LINEAR_MAX_ROWS and contiguous_rows:
+        if norm is not None:
+            prologue = kernels.PRO_NORM if norm == "norm" else kernels.PRO_ADD_NORM
+            if _decode_linear_takes(rows, out_features, in_features, prologue):
+                return ProductPlan("decode_linear", True, epilogue)
+        if _decode_linear_takes(rows, out_features, in_features, kernels.PRO_NONE):
+            return ProductPlan("decode_linear", False, epilogue)
+    if (epilogue == SWIGLU and rows >= FUSED_GATE_UP_MIN_ROWS
+            and _gemm_tcgen05_takes(rows, out_features, in_features, kernels.EPI_SWIGLU)):
+        return ProductPlan("gemm_tcgen05", False, SWIGLU)
+    if epilogue == SWIGLU:
+        return ProductPlan("library", False, BF16, activation_apart=True)
+    return ProductPlan("library", False, epilogue)
+
+
+def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64,
+                     sms: Optional[int] = None) -> int:
+    """How many key splits the decode kernel uses.
+
+    A CTA's warps (eight up to a head size of 64, six up to 128, four above) each stream their share of the tiles
+    of 16 keys at about 0.65 microseconds a tile of 64-wide heads (wider heads in proportion); merging splits
+    costs about 2.5 microseconds inside a thread-block cluster (up to 8 splits) and 5 through scratch memory; two
+    CTAs fit an SM up to a head size of 128, one above.  The choice minimises that estimate over the split counts
+    that keep all CTAs resident at once (at most 32: one sequence of 131,072 tokens reads its keys at 5.2 TB/s
+    with 32 splits, 4.5 with 16)."""
+    tiles = -(-max_context // 16)
+    warps = 8 if head_dim <= 64 else 6 if head_dim <= 128 else 4
+    ctas = max(1, num_seqs * num_kv_heads)
+    per_sm = 2 if head_dim <= 128 else 1
+    tile_cost = 0.65 * max(1.0, head_dim / 64.0)
+    limit = max(1, min(MAX_ATTENTION_SPLITS, per_sm * (sms or kernels.sm_count()) // ctas))
+    best, best_cost = 1, float("inf")
+    for splits in range(1, limit + 1):
+        per_warp = -(-(-(-tiles // splits)) // warps)
+        merge = 0.0 if splits == 1 else 2.5 if splits <= CLUSTER_SPLITS else 5.0
+        cost = tile_cost * per_warp + merge + 0.15 * splits
+        if cost < best_cost:
+            best, best_cost = splits, cost
+    return best
+
+
+@dataclass(frozen=True)
+class AttentionPlan:
+    """``fused_decode``: one kernel rotates q and the new key, writes the cache page and attends (a pure decode
+    step).  Otherwise a rotation + cache-write kernel runs first and ``prompt`` (``tcgen05``, ``mma_tiles`` or
+    None) takes the sequences with more than 16 folded rows (new tokens x query heads per kv head), ``split``
+    (True/False) the others through the split decode kernel.  ``rows``: the 32-bit path's one kernel.
+    ``splits``/``merge``: key splits of the split kernel and how they meet (``none``, ``cluster``, ``scratch``)."""
+
+    fused_decode: bool = False
+    prompt: Optional[str] = None
+    split: bool = False
+    rows: bool = False
+    splits: int = 1
+
+    @property
+    def merge(self) -> str:
+        return "none" if self.splits == 1 else "cluster" if self.splits <= CLUSTER_SPLITS else "scratch"
+
+    def __str__(self) -> str:
+        if self.rows:
+            return "attention_rows (one warp per row and head, fixed order)"
+        if self.fused_decode:
+            return f"attention_decode (rotation and cache write folded in; {self.splits} split(s), merge: {self.merge})"
+        parts = ["rope_kv_write"]
+        if self.prompt:
+            parts.append(f"attention_{self.prompt} for prompt portions")
+        if self.split:
+            parts.append(f"attention_decode for short sequences ({self.splits} split(s), merge: {self.merge})")
+        return " + ".join(parts)
+
+
+def attention(dtype: torch.dtype, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+              new_tokens: Sequence[int], max_context: int, rotary_in_kernel: bool = True,
+              prompt_kernel: str = "tcgen05", sms: Optional[int] = None) -> AttentionPlan:
+    """The attention kernels of a step whose sequences bring ``new_tokens`` tokens each."""
+    if dtype == torch.float32:
+        return AttentionPlan(rows=True)
+    fold = num_heads // num_kv_heads
+    seqs = len(new_tokens)
+    if rotary_in_kernel and fold <= 16 and all(n == 1 for n in new_tokens):
+        return AttentionPlan(fused_decode=True, splits=attention_splits(seqs, num_kv_heads, max_context, head_dim, sms))
+    long_seqs = any(n * fold > 16 for n in new_tokens)
+    short_seqs = any(n * fold <= 16 for n in new_tokens)
+    prompt = None
+    if long_seqs:
+        prompt = "mma_tiles"
+        if prompt_kernel == "tcgen05" and _attention_tcgen05_takes(num_heads, num_kv_heads, head_dim, page_size):
+            prompt = "tcgen05"
+    splits = attention_splits(seqs, num_kv_heads, max_context, head_dim, sms) if short_seqs else 1
+    return AttentionPlan(prompt=prompt, split=short_seqs, splits=splits)
+
+
+def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), context: int = 4096,
+             page_size: int = 16, sms: Optional[int] = None) -> str:
+    """The plan of a built model as text: for every distinct layer and the head, the kernel of each operation at
+    each of ``row_counts`` (a decode step of that many sequences; from 17 rows on also one prompt portion of
+    that many rows)."""
+    from .parts.attention import Attention
+    from .parts.mlp import SwiGLU
+
+    dtype = model.runtime.dtype
+    lines: List[str] = [f"kernel plan for {model.spec.architecture} in {str(dtype).replace('torch.', '')} "
+                        f"(context {context}, pages of {page_size})"]
+    seen = {}
+    for index, block in enumerate(model.layers):
+        key = (repr(model.spec.layers[index].mixer.params), repr(model.spec.layers[index].feed_forward.params))
+        if key in seen:
+            seen[key].append(index)
+            continue
+        seen[key] = [index]
+    for key, layers in seen.items():
+        block = model.layers[layers[0]]
+        lines.append(f"layers {layers[0]}..{layers[-1]} ({len(layers)}): mixer '{block.mixer.kind}', "
+                     f"feed-forward '{block.feed_forward.kind}'")
+        for rows in row_counts:
+            lines.append(f"  {rows} rows")
+            mixer, ffn = block.mixer, block.feed_forward
+            if isinstance(mixer, Attention):
+                qkv = mixer.qkv_proj
+                lines.append(f"    qkv      {product(dtype, rows, qkv.out_features, qkv.in_features, norm='add_norm')}")
+                decode = attention(dtype, num_heads=mixer.num_heads, num_kv_heads=mixer.num_kv_heads,
+                                   head_dim=mixer.head_dim, page_size=page_size, new_tokens=[1] * rows,
+                                   max_context=context, prompt_kernel=mixer.prompt_kernel, sms=sms)
+                lines.append(f"    attend   decode step: {decode}")
+                if rows >= 17:
+                    portion = attention(dtype, num_heads=mixer.num_heads, num_kv_heads=mixer.num_kv_heads,
+                                        head_dim=mixer.head_dim, page_size=page_size, new_tokens=[rows],
+                                        max_context=context, prompt_kernel=mixer.prompt_kernel, sms=sms)
+                    lines.append(f"             one portion: {portion}")
+                o = mixer.o_proj
+                lines.append(f"    o        {product(dtype, rows, o.out_features, o.in_features)}")
+            else:
+                lines.append(f"    mixer    '{mixer.kind}' (its own code)")
+            if isinstance(ffn, SwiGLU):
+                gu, down = ffn.gate_up_proj, ffn.down_proj
+                epilogue = SWIGLU if ffn.interleaved else BF16
+                lines.append(f"    gate/up  {product(dtype, rows, gu.out_features, gu.in_features, epilogue=epilogue, norm='add_norm')}")
+                lines.append(f"    down     {product(dtype, rows, down.out_features, down.in_features)}")
+            else:
+                lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
+    proj = getattr(model.head, "proj", None)
+    if proj is not None:
+        lines.append("head (wanted rows only)")
+        for rows in row_counts:
+            lines.append(f"  {rows} rows  {product(dtype, rows, proj.out_features, proj.in_features, epilogue=F32, norm='add_norm')}")
+    return "\n".join(lines)

@@ -7,9 +7,9 @@ import pytest
 import torch
 
 import tesseract_b200.models  # noqa: F401  (registers the architecture and the parts)
-from tesseract_b200.config import (ConfigError, EngineConfig, LlamaConfig, NoArchitectureError,
+from tesseract_b200.config import (ConfigError, EngineConfig, NoArchitectureError,
                                    UnsupportedArchitectureError, load_model_description, resolve_architecture)
-from tesseract_b200.models import expected_tensors
+from tesseract_b200.models import LlamaConfig, expected_tensors
 from tesseract_b200.weights import (SafetensorsError, SafetensorsSource, WeightError, check_and_load,
                                     write_safetensors)
 from tesseract_b200.weights.random_init import random_tensors, write_random_model

@@ -599,41 +599,6 @@ def test_gemm_tcgen05(m, n, k):
         torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("m, n, k", [(9, 3072, 2048), (64, 2048, 8192), (128, 16384, 2048), (33, 200, 72),
-                                     (1, 16, 8), (17, 144, 136), (100, 1000, 520), (16, 128, 256), (48, 4096, 64)])
-def test_skinny_gemm(m, n, k):
-    """The weight-streaming tcgen05 product (K split over a cluster where N is small) against 64-bit torch."""
-    from tesseract_b200 import kernels
-
-    torch.manual_seed(m + n + k)
-    x = torch.randn(m, k).to(torch.bfloat16)
-    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
-    want = x.double() @ w.double().T
-    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    kernels.skinny_gemm(dev(x), dev(w), out)
-    assert kernels.tcgen05_error() == 0, "a bounded wait inside the kernel ran out"
-    torch.testing.assert_close(out.cpu().double(), want, rtol=1e-2, atol=1e-2)
-    # a row's result does not depend on the rows beside it
-    alone = torch.full((1, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    kernels.skinny_gemm(dev(x[m - 1:m].contiguous()), dev(w), alone)
-    assert torch.equal(alone[0], out[m - 1])
-    # a view with a row stride
-    wide = torch.randn(m, k + 16).to(torch.bfloat16)
-    out2 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    kernels.skinny_gemm(dev(wide)[:, 8:k + 8], dev(w), out2)
-    torch.testing.assert_close(out2.cpu().double(), wide[:, 8:k + 8].double() @ w.double().T, rtol=1e-2, atol=1e-2)
-    if n % 16 == 0:
-        gate, up = w[: n // 2], w[n // 2:]
-        merged = torch.stack([gate.view(n // 16, 8, k), up.view(n // 16, 8, k)], dim=1).reshape(n, k).contiguous()
-        act = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
-        kernels.skinny_gemm(dev(x), dev(merged), act, epilogue=kernels.EPI_SWIGLU)
-        assert kernels.tcgen05_error() == 0
-        g, u = x.double() @ gate.double().T, x.double() @ up.double().T
-        torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
-    assert not kernels.skinny_gemm_supported(129, n, k)
-    assert not kernels.skinny_gemm_supported(m, n, k + 4)
-
-
 @pytest.mark.parametrize("lengths, new, nh, nkv, page_size, window", [
     ([40], [40], 4, 4, 16, 0),                                  # a single block, rows beyond the sequence masked
     ([100, 70], [30, 1], 8, 8, 16, 0),                          # no grouping; the decode row is left to the other kernel

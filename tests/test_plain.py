@@ -7,7 +7,7 @@ import torch
 
 from tesseract_b200.parts.rotary import rotary_inverse_frequencies
 from tesseract_b200.sampling import SplitMix64, sample_top_p_host
-from tests.helpers import TINY, random_tokens
+from tests.helpers import REL, TINY, random_tokens
 from tests.plain import llama
 
 
@@ -89,5 +89,5 @@ def test_plain_forward_prefix_property_and_rounding_mode(tmp_path):
     f32 = llama.forward(config, tensors, tokens, dtype=torch.float32)
     rounded = llama.forward(config, tensors, tokens, dtype=torch.float32, round_to=torch.bfloat16)
     scale = full.abs().max().item()
-    assert (f32 - full).abs().max().item() < 1e-5 * max(1.0, scale)
-    assert 1e-5 < (rounded - full).abs().max().item() < 3e-2 * max(1.0, scale)
+    assert (f32 - full).abs().max().item() < 1e-5 * scale
+    assert 1e-5 * scale < (rounded - full).abs().max().item() < REL["bfloat16"] * scale

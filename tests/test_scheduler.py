@@ -345,3 +345,33 @@ def test_a_failed_launch_fails_its_batch_and_the_engine_goes_on():
     s.add_request(list(range(4)), SamplingParams(max_tokens=3, ignore_eos=True, temperature=0.0))
     assert run_all(s)[0].generated == [1000, 1001, 1002]
     assert s.cache.used_pages() == 0
+
+
+def test_every_token_is_reported_once_and_in_order_when_a_request_arrives_during_a_launch():
+    """A request that arrives while a step launched ahead is in flight makes the next iteration read that step
+    back and run an ordinary step right after it: a decoding request then receives two tokens in one iteration,
+    and the iteration's result has to carry both, oldest first."""
+    s, fake = make_ahead()
+    streamed = {}
+    finished = []
+
+    def step():
+        result = s.step()
+        for request, tokens in result.new_tokens.items():
+            streamed.setdefault(request, []).extend(tokens)
+        finished.extend(result.finished)
+        return result
+
+    first = s.add_request(list(range(4)), SamplingParams(max_tokens=12, ignore_eos=True, temperature=0.0))
+    for _ in range(4):
+        step()
+    assert s._inflight is not None                       # a launched step is waiting to be read
+    second = s.add_request(list(range(6)), SamplingParams(max_tokens=5, ignore_eos=True, temperature=0.0))
+    result = step()
+    assert len(result.new_tokens[first]) == 2            # the token read back, then the ordinary step's
+    assert result.new_tokens[second] == [1000] and result.token_count() == 3   # its whole prompt fit one portion
+    while s.has_work():
+        step()
+    by_id = {r.id: r for r in finished}
+    assert streamed[first] == by_id[first].generated == [1000 + i for i in range(12)]
+    assert streamed[second] == by_id[second].generated == [1000 + i for i in range(5)]

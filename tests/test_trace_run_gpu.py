@@ -8,7 +8,7 @@ import sys
 import numpy as np
 import pytest
 
-from tests.helpers import TINY, compare, max_live_tokens, plain_logits, random_tokens, trace_mixed, trace_tail
+from tests.helpers import REL, TINY, bf16_noise, compare, max_live_tokens, plain_logits, random_tokens, trace_mixed, trace_tail
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -46,7 +46,7 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens):
     return got
 
 
-@pytest.mark.parametrize("dtype, rel", [("float32", 2e-5), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("dtype, rel", sorted(REL.items()))
 def test_trace_run_mixed_and_tail(model_folders, tmp_path, dtype, rel):
     name = "b"
     folder = model_folders(name)
@@ -57,4 +57,8 @@ def test_trace_run_mixed_and_tail(model_folders, tmp_path, dtype, rel):
     got = run_trace(folder, dtype, steps, str(tmp_path / dtype), max_live_tokens(steps, 64))
     plain = plain_logits(folder, requests)
     plain["t"] = plain["r2"]
-    compare(got, plain, rel, f"trace_run/{dtype}")
+    noise = None
+    if dtype == "bfloat16":
+        noise = bf16_noise(folder, requests, plain)
+        noise["t"] = noise["r2"]
+    compare(got, plain, rel, f"trace_run/{dtype}", noise=noise)

@@ -7,7 +7,8 @@ pointers.  For them ``tb_attention_decode_noalloc`` keeps the per-split partial 
 array inside the library image.  This test calls it the way such a caller would (ctypes on the shared
 library, raw pointers, no Python wrapper), twice in a row on different inputs, because the array is
 shared by all calls and keeps the previous call's contents, and checks each result against the
-ordinary entry point, which takes its scratch buffers from the caller.
+ordinary entry point, which takes its scratch buffers from the caller, and against the plain
+whole-sequence attention of the test suite.
 
 The file sorts last on purpose: a run that stops at the first failure has then already run every
 other test.
@@ -52,7 +53,7 @@ def _call(lib, case, nh, nkv, d, page_size, window, scale, splits, claimed_head_
 
 
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
-    from tests.test_kernels_gpu import paged_case, run_attention_mma
+    from tests.test_kernels_gpu import paged_case, plain_paged_attention, run_attention_mma
 
     lib = _library()
     nh, nkv, d, page_size = 32, 8, 64, 16
@@ -65,6 +66,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         assert status == 0, lib.tb_attention_noalloc_strerror(status).decode()
         assert not torch.isnan(got.float()).any()
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+        plain = plain_paged_attention(case, scale).reshape(got.shape)
+        torch.testing.assert_close(got.cpu().double(), plain, rtol=2e-2, atol=2e-2)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
@@ -72,12 +75,30 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
 
     lib = _library()
     limit = 4 * 1024 * 1024
-    assert lib.tb_attention_noalloc_floats_needed(8, 4, 32, 64) == 8 * 4 * 32 * 64 + 8 * 4 * 32 * 2
-    assert lib.tb_attention_noalloc_floats_needed(64, 64, 32, 64) > limit
+    # (splits, sequences, kv heads, head size): sixteen folded rows of 64 + 2 floats per (split, sequence, kv head)
+    assert lib.tb_attention_noalloc_floats_needed(12, 4, 8, 64) == 12 * 4 * 8 * 16 * (64 + 2)
+    assert lib.tb_attention_noalloc_floats_needed(8, 4000, 8, 64) == 0          # up to 8 splits use no scratch
+    assert lib.tb_attention_noalloc_floats_needed(32, 64, 8, 64) > limit
     case = paged_case(torch.bfloat16, [40] * 64, [1] * 64, 32, 8, 64, 16, seed=1)
-    status, out = _call(lib, case, 32, 8, 64, 16, 0, 0.125, 64)
+    status, out = _call(lib, case, 32, 8, 64, 16, 0, 0.125, 32)
     assert status == -5 and torch.isnan(out.float()).all()          # refused, and nothing was launched
     assert b"16 MiB" in lib.tb_attention_noalloc_strerror(status)
     status, _ = _call(lib, paged_case(torch.bfloat16, [40], [1], 4, 2, 16, 16, seed=2), 4, 2, 16, 16, 0, 0.2, 2,
                       claimed_head_dim=20)
     assert status == -3                                              # a head size the kernels do not take
+
+
+def test_no_alloc_entry_point_takes_any_size_that_needs_no_scratch():
+    """Up to eight splits meet inside a thread-block cluster: the static array is not touched, so its limit does
+    not apply, however many sequences the call has (here more than the array could serve with nine splits)."""
+    from tests.test_kernels_gpu import paged_case, run_attention_mma
+
+    lib = _library()
+    nh, nkv, d, page_size, splits = 8, 8, 64, 16, 8
+    lengths = [130 + (k % 7) for k in range(600)]
+    assert 9 * len(lengths) * nkv * 16 * (d + 2) > 4 * 1024 * 1024
+    case = paged_case(torch.bfloat16, lengths, [1] * len(lengths), nh, nkv, d, page_size, seed=3)
+    want = run_attention_mma(case, nh, nkv, d, page_size, 0, 0.125, splits)
+    status, got = _call(lib, case, nh, nkv, d, page_size, 0, 0.125, splits)
+    assert status == 0, lib.tb_attention_noalloc_strerror(status).decode()
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
