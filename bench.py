@@ -4,11 +4,17 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 (device time, CUDA
-events around K decode steps through the engine's step function and device sampler);
-``e2e`` is the same through the scheduler that ``LLM.generate`` drives, with host token lists
-in and out; ``prefill`` is one 2,048-token prompt in one step; ``points`` holds decode at
-batch 1 and 64; ``roofline`` compares the bytes a decode step must read with the measured
-copy bandwidth.
+events around K decode steps through the engine's step function and device sampler; the
+window of K steps is timed five times and the median is reported, with the fastest and the
+slowest beside it); ``e2e`` is the same through the scheduler that ``LLM.generate`` drives,
+with host token lists in and out; ``prefill`` is one 2,048-token prompt in one step (median
+of twenty) and also as four portions of 512; ``points`` holds decode at batch 1 and 64;
+``roofline`` compares the bytes a decode step must read with the measured copy bandwidth.
+
+``--workload 3b`` and ``--workload 8b`` run the two other workloads instead: continuous
+batching of up to 64 requests with prompts of 512 to 4,096 tokens at the Llama 3.2 3B layer
+sizes (through the scheduler), and steps of one 2,048-token portion beside 64 decode rows at
+contexts up to 16,384 at the Llama 3.1 8B layer sizes; each prints its own JSON line.
 """
 
 from __future__ import annotations
@@ -16,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import tempfile
@@ -47,6 +54,8 @@ OTHER_SIZES = {
 }
 SIZE_NAMES = {"1b": "Llama-3.2-1B sizes", "3b": "Llama-3.2-3B sizes", "8b": "Llama-3.1-8B sizes"}
 PROMPT_TOKENS = 2048
+REPEATS_PREFILL = 20      # the prefill step is timed this often; the median counts
+REPEATS_DECODE = 5        # so is the window of K decode steps
 CONTEXT = 4096
 PAGE_SIZE = 16
 
@@ -172,23 +181,46 @@ def run_ours(args):
         cache.release(rid)
         return start.elapsed_time(stop), logits
 
+    def prefill_in_portions(rid, portion):
+        """The same prompt as portions of ``portion`` tokens, one step each (the reference's default portion is 512)."""
+        assert cache.admit(rid)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tokens = prompt()
+        torch.cuda.synchronize()
+        start.record()
+        for at in range(0, PROMPT_TOKENS, portion):
+            last = at + portion >= PROMPT_TOKENS
+            stepper.step([StepEntry(rid, tokens[at:at + portion], [portion - 1] if last else [])])
+        stop.record()
+        torch.cuda.synchronize()
+        cache.release(rid)
+        return start.elapsed_time(stop)
+
     if args.only == "decode":
-        prefill_ms = float("nan")
+        prefill_times, portions_times = [float("nan")], [float("nan")]
     else:
         for k in range(3):
             prefill_once(f"warm{k}")
+            prefill_in_portions(f"warmp{k}", 512)
         t0 = time.time()
-        prefill_ms = sorted(prefill_once(f"pre{k}")[0] for k in range(5))[2]
+        prefill_times = sorted(prefill_once(f"pre{k}")[0] for k in range(REPEATS_PREFILL))
+        portions_times = sorted(prefill_in_portions(f"prp{k}", 512) for k in range(REPEATS_PREFILL))
         windows.append((t0, time.time()))
+    prefill_ms = statistics.median(prefill_times)
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens_per_s": PROMPT_TOKENS / (prefill_ms / 1e3)}))
+        print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens_per_s": PROMPT_TOKENS / (prefill_ms / 1e3),
+                          "ms_min": prefill_times[0], "ms_max": prefill_times[-1],
+                          "ms_4x512": statistics.median(portions_times)}))
         return 0
     flops = prefill_flops(cfg, layers, PROMPT_TOKENS)
+    portions_ms = statistics.median(portions_times)
     prefill = {"value": PROMPT_TOKENS / (prefill_ms / 1e3), "tokens": PROMPT_TOKENS, "ms": prefill_ms,
-               "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "peak": f"{pk['source']} bf16"}
+               "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "peak": f"{pk['source']} bf16",
+               "repeats": REPEATS_PREFILL, "ms_min": prefill_times[0], "ms_max": prefill_times[-1],
+               "ms_4x512": portions_ms, "value_4x512": PROMPT_TOKENS / (portions_ms / 1e3)}
 
     # ---------------------------------------------------------------- decode on the device clock
-    def decode_device(batch, steps, warmup):
+    def decode_device(batch, steps, warmup, repeats=REPEATS_DECODE):
         ids = [f"d{batch}_{k}" for k in range(batch)]
         last = []
         for rid in ids:
@@ -217,41 +249,47 @@ def run_ours(args):
 
         for _ in range(warmup):
             last = one_step(last)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        launches = launched()
-        t0 = time.time()
-        start.record()
-        if stepper.graphs is not None:
-            inflight = launch(None, last)
-            for _ in range(steps - 1):
-                following = launch(inflight, None)
-                last = inflight.tokens()                  # host tokens out, one step behind the launches
-                inflight = following
-            last = inflight.tokens()
-        else:
-            for _ in range(steps):
-                last = one_step(last)
-        stop.record()
-        torch.cuda.synchronize()
-        windows.append((t0, time.time()))
-        launches = launched() - launches
-        ms = start.elapsed_time(stop) / steps
+        times = []
+        for _ in range(repeats):                          # the same window of `steps` steps, several times
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            launches = launched()
+            t0 = time.time()
+            start.record()
+            if stepper.graphs is not None:
+                inflight = launch(None, last)
+                for _ in range(steps - 1):
+                    following = launch(inflight, None)
+                    last = inflight.tokens()              # host tokens out, one step behind the launches
+                    inflight = following
+                last = inflight.tokens()
+            else:
+                for _ in range(steps):
+                    last = one_step(last)
+            stop.record()
+            torch.cuda.synchronize()
+            windows.append((t0, time.time()))
+            launches = launched() - launches
+            times.append(start.elapsed_time(stop) / steps)
         context = cache.length(ids[0])
         for rid in ids:
             cache.release(rid)
-        return ms, launches, context
+        times.sort()
+        return statistics.median(times), launches, context, times
 
-    ms_step, launches, context = decode_device(args.batch, args.steps, args.warmup)
+    ms_step, launches, context, step_times = decode_device(args.batch, args.steps, args.warmup)
     if args.only == "decode":
         print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms_step,
                           "tokens_per_s": args.batch / (ms_step / 1e3), "context": context}))
         return 0
     point_steps = max(8, min(args.steps, 64))
-    ms_b1, _, _ = decode_device(1, point_steps, args.warmup)
-    ms_b64, _, _ = decode_device(64, point_steps, args.warmup)
+    ms_b1, _, context_b1, _ = decode_device(1, point_steps, args.warmup)
+    ms_b64, _, context_b64, _ = decode_device(64, point_steps, args.warmup)
     step_bytes = numbers["weight_bytes"] + args.batch * context * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (ms_step / 1e3) / 1e9
+
+    def point_frac(batch, ms, ctx):
+        return (numbers["weight_bytes"] + batch * ctx * numbers["kv_bytes_per_token"]) / (ms / 1e3) / 1e9 / pk["hbm_gbs"]
 
     # ---------------------------------------------------------------- end to end through the scheduler
     params = SamplingParams(max_tokens=args.steps + args.warmup + 4, temperature=0.0, ignore_eos=True)
@@ -280,7 +318,8 @@ def run_ours(args):
     value = args.batch / (ms_step / 1e3)
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "ms_per_step": ms_step, "ms_per_step_min": step_times[0], "ms_per_step_max": step_times[-1],
+        "repeats": REPEATS_DECODE, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
         "config": {"model": SIZE_NAMES[args.size], "layers": layers, "layers_of_model": model["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
@@ -289,13 +328,152 @@ def run_ours(args):
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_tokens": PROMPT_TOKENS,
                    "decode_context": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
                    "l2": f"inputs larger than L2 ({numbers['weight_bytes'] / 1e9:.2f} GB of weights read every step)",
-                   "decode_steps": "CUDA graph per step, launched one ahead of the token read-back"},
+                   "decode_steps": "CUDA graph per step, launched one ahead of the token read-back",
+                   "timing": "median of 5 windows of `steps` steps (decode) and of 20 steps (prefill)"},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "of": pk["source"]},
-        "points": {"decode_b1": 1 / (ms_b1 / 1e3), "decode_b64": 64 / (ms_b64 / 1e3)},
+        "points": {"decode_b1": 1 / (ms_b1 / 1e3), "decode_b64": 64 / (ms_b64 / 1e3),
+                   "decode_b1_frac": point_frac(1, ms_b1, context_b1), "decode_b64_frac": point_frac(64, ms_b64, context_b64)},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "impl": "ours",
     }
+    print(json.dumps(line))
+    scratch.cleanup()
+    return 0
+
+
+WORKLOAD_LAYERS = 8      # layers the workload runs build by default (of 28 and 32): memory and time; --layers says otherwise
+
+
+def run_workload(args):
+    """The two workloads beside the headline one (each prints its own JSON line):
+
+    ``3b``  Llama 3.2 3B layer sizes, continuous batching through the scheduler: 128 requests with prompts of 512 to
+            4,096 random tokens and 128 generated tokens each, at most 64 running, portions of 512, context 8,192.
+    ``8b``  Llama 3.1 8B layer sizes, the mixed step of continuous batching under load: one 2,048-token portion of a
+            16,384-token prompt beside 64 decode rows whose contexts spread from 2,048 to 16,000 tokens.
+    """
+    import numpy as np
+    import torch
+
+    from tesseract_b200 import LLM, SamplingParams, kernels
+    from tesseract_b200.engine import StepEntry
+    from tesseract_b200.weights.random_init import write_random_model
+
+    size = args.workload
+    model = dict(LLAMA_1B, **OTHER_SIZES[size])
+    layers = args.layers or WORKLOAD_LAYERS
+    cfg = dict(model, num_hidden_layers=layers)
+    pk = peaks()
+    numbers = model_numbers(cfg, layers)
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    scratch = tempfile.TemporaryDirectory(prefix="tesseract_bench_")
+    write_random_model(scratch.name, cfg, seed=0)
+    vocab, d, nh = cfg["vocab_size"], cfg["head_dim"], cfg["num_attention_heads"]
+    base = {"metric": METRIC, "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "higher_is_better": True,
+            "data": "synthetic: seeded random weights N(0,0.02) and random token ids", "impl": "ours"}
+    shape = {"model": SIZE_NAMES[size], "layers": layers, "layers_of_model": model["num_hidden_layers"],
+             "hidden": cfg["hidden_size"], "heads": nh, "kv_heads": cfg["num_key_value_heads"], "head_dim": d,
+             "intermediate": cfg["intermediate_size"], "vocab": vocab, "page_size": PAGE_SIZE}
+    sampler.start()
+    if size == "3b":
+        context, running, requests, generated = 8192, 64, 128, 128
+        llm = LLM(scratch.name, dtype="bfloat16", max_running=running, max_queue=requests, max_batch_tokens=4096,
+                  prefill_chunk_tokens=512, kv_capacity_tokens=running * context, page_size=PAGE_SIZE,
+                  max_sequence_length=context, cuda_graphs=not args.no_graphs)
+        lengths = rng.integers(512, 4097, requests).tolist()
+        prompts = [rng.integers(0, vocab, n).tolist() for n in lengths]
+        params = SamplingParams(max_tokens=generated, temperature=0.0, ignore_eos=True)
+        llm.generate(prompts[:8], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))     # warm-up: graphs, workspaces
+        torch.cuda.synchronize()
+        steps_before, t0 = llm.scheduler.steps, time.time()
+        outs = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        seconds = time.time() - t0
+        produced = sum(len(o.token_ids) for o in outs)
+        assert produced == requests * generated, "every request must run to its length"
+        prompt_tokens = sum(lengths)
+        # what the model computed: every prompt and generated token once through the products, each attending to all before it
+        flops = 2 * (prompt_tokens + produced) * layers * numbers["layer_params"] + 2 * produced * vocab * cfg["hidden_size"]
+        flops += sum(layers * 2 * (n + generated) ** 2 * d * nh for n in lengths)
+        line = dict(base, workload="continuous batching: 128 requests, prompts of 512-4,096 tokens, 128 generated each, "
+                                   "at most 64 running, portions of 512, context 8,192, through the scheduler",
+                    value=(prompt_tokens + produced) / seconds, generated_tokens_per_s=produced / seconds,
+                    seconds=seconds, scheduler_steps=llm.scheduler.steps - steps_before,
+                    prompt_tokens=prompt_tokens, generated_tokens=produced,
+                    frac_of_bf16_peak=flops / seconds / (pk["bf16_tflops"] * 1e12), peak=f"{pk['source']} bf16",
+                    config=dict(shape, global_batch=running, seq_len=context, prefill_chunk_tokens=512))
+        windows = [(t0, t0 + seconds)]
+    else:
+        context, decodes, portion = 16384, 64, PROMPT_TOKENS
+        portions_per_prompt = context // portion
+        steps = args.steps if args.steps != 128 else 2 * portions_per_prompt
+        capacity = decodes * context + 2 * context
+        llm = LLM(scratch.name, dtype="bfloat16", max_running=decodes + 2, max_batch_tokens=portion + decodes,
+                  prefill_chunk_tokens=portion, kv_capacity_tokens=capacity, page_size=PAGE_SIZE,
+                  max_sequence_length=context, cuda_graphs=not args.no_graphs)
+        stepper, cache = llm.stepper, llm.stepper.cache
+        contexts = np.linspace(2048, 16000, decodes).astype(int).tolist()
+        ids = [f"d{k}" for k in range(decodes)]
+        for rid, n in zip(ids, contexts):      # the decode rows' earlier tokens: pages held, contents whatever they are
+            assert cache.admit(rid)
+            cache.extend(rid, n)
+            cache.commit(rid, n)
+        state = {"prompt": 0, "at": 0}
+
+        def mixed_step():
+            if state["at"] == 0:
+                assert cache.admit(("p", state["prompt"]))
+            rid = ("p", state["prompt"])
+            last = state["at"] + portion >= context - portion       # leave room: the prompt ends one portion early
+            entries = [StepEntry(rid, rng.integers(0, vocab, portion).tolist(), [portion - 1] if last else [])]
+            entries += [StepEntry(r, [int(rng.integers(0, vocab))], [0]) for r in ids]
+            stepper.step(entries)
+            state["at"] += portion
+            if last:
+                cache.release(rid)
+                state["prompt"] += 1
+                state["at"] = 0
+
+        for _ in range(max(args.warmup, portions_per_prompt)):
+            mixed_step()
+        times, windows = [], []
+        launches = 0
+        for _ in range(REPEATS_DECODE):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            before = kernels.launch_count + (stepper.chunk_graphs.kernels_replayed if stepper.chunk_graphs else 0)
+            t0 = time.time()
+            start.record()
+            for _ in range(steps):
+                mixed_step()
+            stop.record()
+            torch.cuda.synchronize()
+            windows.append((t0, time.time()))
+            launches = kernels.launch_count + (stepper.chunk_graphs.kernels_replayed if stepper.chunk_graphs else 0) - before
+            times.append(start.elapsed_time(stop) / steps)
+        times.sort()
+        ms = statistics.median(times)
+        rows = portion + decodes
+        mean_decode_context = float(np.mean([cache.length(r) for r in ids]))
+        mean_prompt_context = (context - portion) / 2            # a portion sees, on average, half the prompt before it
+        flops = 2 * rows * layers * numbers["layer_params"] + 2 * (decodes + 1) * vocab * cfg["hidden_size"]
+        flops += layers * 4 * portion * (mean_prompt_context + portion / 2) * d * nh      # QK^T and PV of the portion
+        embedding_bytes = 0 if cfg.get("tie_word_embeddings") else 2 * vocab * cfg["hidden_size"]
+        step_bytes = numbers["weight_bytes"] + embedding_bytes * 0 + (decodes * mean_decode_context + mean_prompt_context) * numbers["kv_bytes_per_token"]
+        t_compute = flops / (pk["bf16_tflops"] * 1e12)
+        t_memory = step_bytes / (pk["hbm_gbs"] * 1e9)
+        line = dict(base, workload="mixed step: one 2,048-token portion of a 16,384-token prompt beside 64 decode rows "
+                                   "(contexts 2,048 to 16,000)",
+                    value=rows / (ms / 1e3), ms_per_step=ms, ms_per_step_min=times[0], ms_per_step_max=times[-1],
+                    steps=steps, repeats=REPEATS_DECODE, gpu_launches=launches,
+                    bound={"compute_ms": t_compute * 1e3, "hbm_ms": t_memory * 1e3,
+                           "frac": max(t_compute, t_memory) / (ms / 1e3), "of": pk["source"]},
+                    config=dict(shape, global_batch=decodes + 1, seq_len=context, prompt_portion=portion,
+                                mean_decode_context=mean_decode_context))
+    line["clocks"] = sampler.stop(windows)
+    line["tcgen05_wait_timeouts"] = kernels.tcgen05_error()
     print(json.dumps(line))
     scratch.cleanup()
     return 0
@@ -418,12 +596,17 @@ def main():
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     parser.add_argument("--no-graphs", action="store_true", help="decode without CUDA-graph replay")
+    parser.add_argument("--workload", choices=["3b", "8b"], default=None,
+                        help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
+                             "or a 2,048-token portion beside 64 decode rows at the 8B sizes")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return run_workload(args)
     if args.only == "kernels":
         return run_kernels(args)
     return run_ours(args)

@@ -36,12 +36,6 @@ enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
 
 // smem_u32, the mbarrier helpers (every wait bounded) and the tensor-map encoder come from tma.cuh
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-
 // Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
 // start address, leading offset 1 (unused for swizzled K-major), 1024 bytes between groups of eight rows,
 // descriptor version 1, layout type 2 (SWIZZLE_128B).
@@ -268,20 +262,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// A row-major [rows, cols] bfloat16 matrix with `stride` elements between rows, cut into boxes of box_rows x 64.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t stride, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (fn == nullptr) return TB_ERR_BAD_SIZE;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {stride * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : TB_ERR_BAD_SIZE;
-}
-
 }  // namespace
 
 // 1 if the kernel takes these sizes.  K and the row strides must be multiples of 8 (16-byte TMA strides), N of 8
@@ -303,8 +283,8 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
     // one row of tiles: narrower tiles, so that twice as many SMs stream the weights
     const int bn = M <= BM ? 128 : 256;
     CUtensorMap map_a, map_b;
-    if (int status = make_map(&map_a, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_stride, BM)) return status;
-    if (int status = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, bn)) return status;
+    if (int status = make_map_2d(&map_a, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_stride, BM)) return status;
+    if (int status = make_map_2d(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, bn)) return status;
     GemmParams p;
     p.out = out;
     p.out_stride = out_stride;

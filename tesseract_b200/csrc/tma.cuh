@@ -57,6 +57,13 @@ __device__ __forceinline__ void tma_load_kv(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(dim0), "r"(key_in_page), "r"(kv_head), "r"(which), "r"(page) : "memory");
 }
 
+// One box of a two-dimensional tensor map at element coordinates (c0 along the rows, c1 = the row).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -71,6 +78,23 @@ inline EncodeTiledFn encode_tiled() {
             fn = reinterpret_cast<EncodeTiledFn>(ptr);
     }
     return fn;
+}
+
+// A row-major [rows, cols] bfloat16 matrix with `stride` elements between rows, cut into boxes of box_rows rows of
+// 64 elements (128 bytes, stored with the 128-byte swizzle).  Rows and columns beyond the matrix read as zero.
+// The base address and the stride in bytes must be multiples of 16.
+inline int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t stride,
+                       uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return TB_ERR_BAD_SIZE;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {stride * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : TB_ERR_BAD_SIZE;
 }
 
 // Tensor map of one cache entry [pages][K|V][kv head][key][head_dim] (head_dim a multiple of 64), boxes of 64 dims

@@ -39,14 +39,14 @@ def test_split_counts_follow_the_measurements():
 
 def test_products_of_the_1b_sizes():
     hidden, inter, qkv, vocab = 2048, 8192, 3072, 128256
-    for rows in (1, 8, 16):
-        assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan("decode_linear", True, "bf16")
-        assert plan.product(BF, rows, hidden, hidden) == plan.ProductPlan("decode_linear", False, "bf16")
+    for rows, kernel in ((1, "decode_linear"), (8, "decode_linear"), (16, "decode_linear")):
+        assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan(kernel, True, "bf16")
+        assert plan.product(BF, rows, hidden, hidden) == plan.ProductPlan(kernel, False, "bf16")
         assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu", norm="add_norm") == \
-            plan.ProductPlan("decode_linear", True, "swiglu")
-        assert plan.product(BF, rows, hidden, inter) == plan.ProductPlan("decode_linear", False, "bf16")
+            plan.ProductPlan(kernel, True, "swiglu")
+        assert plan.product(BF, rows, hidden, inter) == plan.ProductPlan(kernel, False, "bf16")
         assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="add_norm") == \
-            plan.ProductPlan("decode_linear", True, "f32")
+            plan.ProductPlan(kernel, True, "f32")
     for rows in (17, 64, 2048):
         assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan("library", False, "bf16")
         assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu") == plan.ProductPlan("gemm_tcgen05", False, "swiglu")
