@@ -181,6 +181,12 @@ def run_ours(args):
         cache.release(rid)
         return start.elapsed_time(stop), logits
 
+    portion_graphs = None
+    if not args.no_graphs:
+        from tesseract_b200.engine.graph import ChunkGraphs
+
+        portion_graphs = ChunkGraphs(stepper, 512, CONTEXT, max_batch)
+
     def prefill_in_portions(rid, portion):
         """The same prompt as portions of ``portion`` tokens, one step each (the reference's default portion is 512)."""
         assert cache.admit(rid)
@@ -190,7 +196,11 @@ def run_ours(args):
         start.record()
         for at in range(0, PROMPT_TOKENS, portion):
             last = at + portion >= PROMPT_TOKENS
-            stepper.step([StepEntry(rid, tokens[at:at + portion], [portion - 1] if last else [])])
+            entries = [StepEntry(rid, tokens[at:at + portion], [portion - 1] if last else [])]
+            if portion_graphs is not None and portion_graphs.eligible(entries):
+                portion_graphs.step(entries)       # as an engine configured with this portion size replays it
+            else:
+                stepper.step(entries)
         stop.record()
         torch.cuda.synchronize()
         cache.release(rid)
@@ -222,12 +232,17 @@ def run_ours(args):
     # ---------------------------------------------------------------- decode on the device clock
     def decode_device(batch, steps, warmup, repeats=REPEATS_DECODE):
         ids = [f"d{batch}_{k}" for k in range(batch)]
-        last = []
-        for rid in ids:
-            assert cache.admit(rid)
-            stepper.step([StepEntry(rid, prompt(), [])])
-            last.append(int(rng.integers(0, cfg["vocab_size"])))
         greedy, ones = [0.0] * batch, [1.0] * batch
+
+        def fresh_requests():
+            """Every window decodes the same stretch: `batch` new requests, each with its 2,048-token prompt cached."""
+            tokens = []
+            for rid in ids:
+                cache.release(rid)
+                assert cache.admit(rid)
+                stepper.step([StepEntry(rid, prompt(), [])])
+                tokens.append(int(rng.integers(0, cfg["vocab_size"])))
+            return tokens
 
         entries = [StepEntry(rid, [0], [0]) for rid in ids]
         all_fed = [True] * batch
@@ -247,10 +262,11 @@ def run_ours(args):
         def launched():
             return kernels.launch_count + (stepper.graphs.kernels_replayed if stepper.graphs else 0)
 
-        for _ in range(warmup):
-            last = one_step(last)
         times = []
         for _ in range(repeats):                          # the same window of `steps` steps, several times
+            last = fresh_requests()
+            for _ in range(warmup):
+                last = one_step(last)
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             launches = launched()

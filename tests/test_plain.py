@@ -1,8 +1,10 @@
 """The plain implementation itself, and host-side restatements the engine shares formulas with."""
 
 import math
+import os
 
 import numpy as np
+import pytest
 import torch
 
 from tesseract_b200.parts.rotary import rotary_inverse_frequencies
@@ -91,3 +93,55 @@ def test_plain_forward_prefix_property_and_rounding_mode(tmp_path):
     scale = full.abs().max().item()
     assert (f32 - full).abs().max().item() < 1e-5 * scale
     assert 1e-5 * scale < (rounded - full).abs().max().item() < REL["bfloat16"] * scale
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_the_two_plain_models_agree(tmp_path, name):
+    """tests/plain/llama.py (whole sequences, torch) against tests/plain/llama_scalar.cpp (token by token, scalar
+    loops, its own key/value list and its own frequency recipe): two implementations written apart from the same
+    formulas.  The reference itself cannot be built here (Rust, GPU-only kernels), so this pair, not an output of
+    the reference, is what anchors the plain model: with and without frequency scaling, tied and untied head,
+    grouped heads, head sizes that do not multiply back to the width."""
+    import shutil
+    import struct
+    import subprocess
+
+    from tesseract_b200.weights.random_init import write_random_model
+
+    compiler = shutil.which("g++") or shutil.which("c++")
+    if compiler is None:
+        pytest.skip("no C++ compiler")
+    source = os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain", "llama_scalar.cpp")
+    binary = str(tmp_path / "llama_scalar")
+    subprocess.run([compiler, "-O2", "-std=c++17", "-o", binary, source], check=True)
+    folder = write_random_model(str(tmp_path / "m"), dict(TINY[name], torch_dtype="float32"), seed=4)
+    config, tensors = llama.load_folder(folder)
+    tokens = random_tokens(config["vocab_size"], 70, seed=9)
+    nh, nkv = config["num_attention_heads"], config["num_key_value_heads"]
+    d = config.get("head_dim") or config["hidden_size"] // nh
+    scaling = config.get("rope_scaling")
+    tied = bool(config.get("tie_word_embeddings"))
+    with open(tmp_path / "model.bin", "wb") as out:
+        out.write(struct.pack("<11i", config["num_hidden_layers"], config["hidden_size"], nh, nkv, d,
+                              config["intermediate_size"], config["vocab_size"], int(tied), int(scaling is not None),
+                              scaling["original_max_position_embeddings"] if scaling else 0, len(tokens)))
+        out.write(struct.pack("<5d", config["rms_norm_eps"], config["rope_theta"],
+                              *([scaling["factor"], scaling["low_freq_factor"], scaling["high_freq_factor"]]
+                                if scaling else [1.0, 1.0, 1.0])))
+        out.write(np.asarray(tokens, dtype="<i4").tobytes())
+        names = ["model.embed_tokens.weight"]
+        for layer in range(config["num_hidden_layers"]):
+            p = f"model.layers.{layer}"
+            names += [f"{p}.input_layernorm.weight", f"{p}.self_attn.q_proj.weight", f"{p}.self_attn.k_proj.weight",
+                      f"{p}.self_attn.v_proj.weight", f"{p}.self_attn.o_proj.weight",
+                      f"{p}.post_attention_layernorm.weight", f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight",
+                      f"{p}.mlp.down_proj.weight"]
+        names += ["model.norm.weight"] + ([] if tied else ["lm_head.weight"])
+        for tensor_name in names:
+            out.write(tensors[tensor_name].to(torch.float32).contiguous().numpy().astype("<f4").tobytes())
+    subprocess.run([binary, str(tmp_path / "model.bin"), str(tmp_path / "logits.bin")], check=True)
+    scalar = np.fromfile(tmp_path / "logits.bin", dtype="<f8").reshape(len(tokens), config["vocab_size"])
+    whole = llama.forward(config, tensors, tokens).numpy()
+    # float64 both: what is left is the order of summation and one unit in the last place of a 32-bit frequency
+    assert np.abs(scalar - whole).max() <= 1e-6 * np.abs(whole).max()
+    assert (scalar.argmax(axis=1) == whole.argmax(axis=1)).all()
