@@ -185,7 +185,7 @@ def run_ours(args):
     if not args.no_graphs:
         from tesseract_b200.engine.graph import ChunkGraphs
 
-        portion_graphs = ChunkGraphs(stepper, 512, CONTEXT, max_batch)
+        portion_graphs = ChunkGraphs(stepper, 512, CONTEXT, max_batch, max_portions=1)
 
     def prefill_in_portions(rid, portion):
         """The same prompt as portions of ``portion`` tokens, one step each (the reference's default portion is 512)."""

@@ -257,13 +257,18 @@ class DecodeGraphs:
 
 
 class _ChunkGraph:
-    """Buffers and the captured graph for steps in which one sequence brings ``rows`` prompt tokens and up to
-    ``decodes`` others one decoded token each (rows ``rows`` .. ``rows + decodes - 1``, all wanted)."""
+    """Buffers and the captured graph for steps in which ``portions`` sequences bring ``rows`` prompt tokens each
+    (rows ``k * rows`` .. ``(k + 1) * rows - 1``) and up to ``decodes`` others one decoded token each (the rows
+    after them, all wanted).  With ``wants_last`` the last row of every portion goes through the head as well (the
+    caller picks the ones it asked for); without, no portion row does."""
 
-    def __init__(self, stepper: Stepper, rows: int, decodes: int, wants_last: bool, columns: int):
+    def __init__(self, stepper: Stepper, rows: int, portions: int, decodes: int, wants_last: bool, columns: int,
+                 pool=None):
         cache, device = stepper.cache, stepper.runtime.device
-        self.rows, self.decodes, self.columns = rows, decodes, columns
-        total, seqs = rows + decodes, 1 + decodes
+        self.rows, self.portions, self.decodes, self.columns = rows, portions, decodes, columns
+        self.wants_last = wants_last
+        prompt_rows = portions * rows
+        total, seqs = prompt_rows + decodes, portions + decodes
         self.paged = [i for i, g in enumerate(cache.groups) if g.pool is not None]
         # int32 block: tokens[total] positions[total] begin[seqs] slot[seqs]; block tables apart (only the columns
         # in use are copied)
@@ -279,20 +284,21 @@ class _ChunkGraph:
         tables = dict(zip(self.paged, self.dev_tables))
         groups = [GroupView(tables.get(index), cache.page_size if g.pool is not None else 0)
                   for index, g in enumerate(cache.groups)]
-        seq_of_row = torch.cat([torch.zeros(rows, dtype=torch.int32),
-                                torch.arange(1, seqs, dtype=torch.int32)]).to(device)
-        row_start = torch.cat([torch.zeros(1, dtype=torch.int32),
-                               torch.arange(rows, total + 1, dtype=torch.int32)]).to(device)
+        seq_of_row = torch.cat([torch.arange(portions, dtype=torch.int32).repeat_interleave(rows),
+                                torch.arange(portions, seqs, dtype=torch.int32)]).to(device)
+        row_start = torch.cat([torch.arange(0, prompt_rows, rows, dtype=torch.int32),
+                               torch.arange(prompt_rows, total + 1, dtype=torch.int32)]).to(device)
         self.ctx = StepContext(
             num_rows=total, num_seqs=seqs, token_ids=d[:total], positions=d[total:2 * total], seq_of_row=seq_of_row,
             row_start=row_start, seq_begin=d[2 * total:2 * total + seqs],
-            state_slots=d[2 * total + seqs:2 * total + 2 * seqs], groups=groups, host_new=[rows] + [1] * decodes,
-            host_begin=(), host_slots=(), max_new=rows, max_context=columns * cache.page_size)
-        wanted = ([rows - 1] if wants_last else []) + list(range(rows, total))
+            state_slots=d[2 * total + seqs:2 * total + 2 * seqs], groups=groups,
+            host_new=[rows] * portions + [1] * decodes, host_begin=(), host_slots=(), max_new=rows,
+            max_context=columns * cache.page_size)
+        wanted = ([(k + 1) * rows - 1 for k in range(portions)] if wants_last else []) + list(range(prompt_rows, total))
         self.want_rows = torch.tensor(wanted, dtype=torch.int32, device=device) if wanted else None
         # capture on harmless metadata: positions 0.., the scratch slot, the scratch page
         host = self.hosts[0].numpy()
-        host[total:total + rows] = np.arange(rows, dtype=np.int32)
+        host[total:total + prompt_rows] = np.tile(np.arange(rows, dtype=np.int32), portions)
         host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
         self.dev.copy_(self.hosts[0])
         torch.cuda.synchronize()
@@ -309,7 +315,7 @@ class _ChunkGraph:
         collecting = gc.isenabled()
         gc.disable()                                 # see _Graph._capture
         try:
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=pool):
                 self.logits = stepper.model.forward(self.ctx, cache.bindings, self.want_rows)
         finally:
             if collecting:
@@ -320,53 +326,81 @@ class _ChunkGraph:
 
 
 class ChunkGraphs:
-    """CUDA-graph replay of steps with a prompt portion: the first sequence brings exactly ``rows`` tokens (the
-    configured portion size) and wants nothing or its last place; every other sequence brings one decoded token
-    and wants it.  Between two such steps only device metadata differs (token ids, positions, block tables), so
-    the launches of the whole model are replayed instead of issued one by one; at 2,048 rows of the 1B sizes that
-    takes the step from 4.6 to 3.9 ms.  One graph per (decode rows rounded up to a power of two, wants-last,
-    block-table width rounded up to a power of two): the width bounds the context, and with it the split count
-    that the decode rows' attention is captured with, as for the decode graphs.  Rows that pad the decode part
-    point at the scratch page and the scratch state slot."""
+    """CUDA-graph replay of steps with prompt portions: the first one to ``max_portions`` sequences bring exactly
+    ``rows`` tokens each (the configured portion size) and want nothing or their last place; every other sequence
+    brings one decoded token and wants it.  Between two such steps only device metadata differs (token ids,
+    positions, block tables), so the launches of the whole model are replayed instead of issued one by one; at
+    2,048 rows of the 1B sizes that takes the step from 4.6 to 3.9 ms.  One graph per (portions, decode rows
+    rounded up to a power of two, whether any portion wants its last place, block-table width rounded up to a
+    power of two): the width bounds the context, and with it the split count that the decode rows' attention is
+    captured with, as for the decode graphs.  Rows that pad the decode part point at the scratch page and the
+    scratch state slot.  If one portion wants its last place the last rows of all portions go through the head
+    and the caller gets the ones it asked for.  The graphs share one memory pool (they never run at the same
+    time), so the returned logits are valid until the next replayed step; at most ``MAX_GRAPHS`` are captured,
+    other shapes run launch by launch."""
 
-    def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int, max_decodes: int):
+    MAX_GRAPHS = 48
+
+    def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int, max_decodes: int, max_portions: int = 1):
         self.stepper = stepper
         self.rows = rows
         self.max_decodes = max_decodes
+        self.max_portions = max(1, max_portions)
         page = stepper.cache.page_size
         self.columns = max(1, -(-min(max_sequence_length, stepper.max_positions) // page))
-        self.graphs: Dict[Tuple[int, bool, int], _ChunkGraph] = {}
+        self.graphs: Dict[Tuple[int, int, bool, int], _ChunkGraph] = {}
+        self.pool = None
         self.replays = 0
         self.kernels_replayed = 0
         self.safe = graph_safe(stepper.model)
 
+    def _portions(self, entries: Sequence[StepEntry]) -> int:
+        """How many leading entries are full portions that want nothing or their last place."""
+        count = 0
+        for entry in entries:
+            if len(entry.tokens) != self.rows or list(entry.want) not in ([], [self.rows - 1]):
+                break
+            count += 1
+        return count
+
+    def _key(self, entries: Sequence[StepEntry], portions: int) -> Tuple[int, int, bool, int]:
+        cache = self.stepper.cache
+        decodes = len(entries) - portions
+        bucket = 0 if decodes == 0 else min(_next_pow2(decodes), max(self.max_decodes, decodes))
+        pages = -(-max(cache.length(e.request) + len(e.tokens) for e in entries) // cache.page_size)
+        columns = min(self.columns, max(8, _next_pow2(pages)))
+        return portions, bucket, any(e.want for e in entries[:portions]), columns
+
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
-        if not self.safe or not entries or len(entries) - 1 > self.max_decodes:
+        if not self.safe or not entries:
             return False
-        first = entries[0]
-        if len(first.tokens) != self.rows or list(first.want) not in ([], [self.rows - 1]):
+        portions = self._portions(entries)
+        if portions == 0 or portions > self.max_portions or len(entries) - portions > self.max_decodes:
             return False
-        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries[1:]):
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries[portions:]):
             return False
         cache = self.stepper.cache
         limit = self.columns * cache.page_size
-        return all(cache.is_live(e.request) and cache.length(e.request) + len(e.tokens) <= limit for e in entries)
+        if not all(cache.is_live(e.request) and cache.length(e.request) + len(e.tokens) <= limit for e in entries):
+            return False
+        return len(self.graphs) < self.MAX_GRAPHS or self._key(entries, portions) in self.graphs
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         stepper, cache = self.stepper, self.stepper.cache
         stepper._validate(entries)
-        rows, decodes = self.rows, len(entries) - 1
-        wants_last = bool(entries[0].want)
-        bucket = 0 if decodes == 0 else min(_next_pow2(decodes), max(self.max_decodes, decodes))
-        begins = [cache.length(e.request) for e in entries]
-        pages = -(-max(b + len(e.tokens) for b, e in zip(begins, entries)) // cache.page_size)
-        columns = min(self.columns, max(8, _next_pow2(pages)))
-        key = (bucket, wants_last, columns)
+        rows, portions = self.rows, self._portions(entries)
+        decodes = len(entries) - portions
+        key = self._key(entries, portions)
+        _, bucket, wants_last, columns = key
         graph = self.graphs.get(key)
         if graph is None:
-            graph = _ChunkGraph(stepper, rows, bucket, wants_last, columns)
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            graph = _ChunkGraph(stepper, rows, portions, bucket, wants_last, columns, self.pool)
             self.graphs[key] = graph
-        total, seqs = rows + bucket, 1 + bucket
+        prompt_rows = portions * rows
+        total, seqs = prompt_rows + bucket, portions + bucket
+        begins = [cache.length(e.request) for e in entries]
         for entry in entries:
             cache.extend(entry.request, len(entry.tokens))
         index = graph.next_host
@@ -375,23 +409,24 @@ class ChunkGraphs:
             graph.host_events[index].synchronize()
         host = graph.hosts[index].numpy()
         slots = [cache.slot(e.request) for e in entries]
-        host[:rows] = np.asarray(entries[0].tokens, dtype=np.int32)
-        host[total:total + rows] = np.arange(begins[0], begins[0] + rows, dtype=np.int32)
-        host[rows:total] = 0
-        host[total + rows:2 * total] = 0
+        host[prompt_rows:total] = 0
+        host[total + prompt_rows:2 * total] = 0
         host[2 * total:2 * total + seqs] = 0
         host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
+        for k in range(portions):
+            host[k * rows:(k + 1) * rows] = np.asarray(entries[k].tokens, dtype=np.int32)
+            host[total + k * rows:total + (k + 1) * rows] = np.arange(begins[k], begins[k] + rows, dtype=np.int32)
         if decodes:
-            host[rows:rows + decodes] = [int(e.tokens[0]) for e in entries[1:]]
-            host[total + rows:total + rows + decodes] = begins[1:]
-        host[2 * total:2 * total + 1 + decodes] = begins
-        host[2 * total + seqs:2 * total + seqs + 1 + decodes] = slots
+            host[prompt_rows:prompt_rows + decodes] = [int(e.tokens[0]) for e in entries[portions:]]
+            host[total + prompt_rows:total + prompt_rows + decodes] = begins[portions:]
+        host[2 * total:2 * total + portions + decodes] = begins
+        host[2 * total + seqs:2 * total + seqs + portions + decodes] = slots
         used = min(graph.columns, -(-max(b + len(e.tokens) for b, e in zip(begins, entries)) // cache.page_size))
         graph.dev.copy_(graph.hosts[index], non_blocking=True)
         for k, group_index in enumerate(graph.paged):
             table = graph.host_tables[index][k].numpy()
-            table[:1 + decodes, :used] = cache.block_table_rows(group_index, slots, used)
-            table[1 + decodes:, :used] = 0
+            table[:portions + decodes, :used] = cache.block_table_rows(group_index, slots, used)
+            table[portions + decodes:, :used] = 0
             graph.dev_tables[k][:, :used].copy_(graph.host_tables[index][k][:, :used], non_blocking=True)
         copied = torch.cuda.Event()
         copied.record()
@@ -404,4 +439,10 @@ class ChunkGraphs:
         self.kernels_replayed += graph.kernels_per_replay
         if graph.logits is None:
             return None
-        return graph.logits[:(1 if wants_last else 0) + decodes]
+        head_portions = portions if wants_last else 0
+        picked = [k for k in range(head_portions) if entries[k].want] + list(range(head_portions, head_portions + decodes))
+        if not picked:
+            return None
+        if picked == list(range(picked[0], picked[0] + len(picked))):
+            return graph.logits[picked[0]:picked[0] + len(picked)]
+        return graph.logits[torch.tensor(picked, dtype=torch.long, device=graph.logits.device)]

@@ -56,7 +56,7 @@ class LLM:
         self.sampler = Sampler(self.model.runtime.device)
         if cuda_graphs:
             self.stepper.enable_graphs(max_running, chunk_rows=prefill_chunk_tokens,
-                                       max_sequence_length=max_sequence_length)
+                                       max_sequence_length=max_sequence_length, max_batch_tokens=max_batch_tokens)
         self.scheduler = Scheduler(self.config, self.stepper.cache, self.stepper.step, self.sampler.sample,
                                    eos_token_ids=self.model.spec.eos_token_ids,
                                    max_positions=self.model.spec.max_positions,

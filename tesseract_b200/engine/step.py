@@ -164,14 +164,17 @@ class Stepper:
 
     # ------------------------------------------------------------------ step + sampling
     def enable_graphs(self, max_batch: int, chunk_rows: Optional[int] = None,
-                      max_sequence_length: Optional[int] = None) -> None:
-        """Replay pure decode steps as CUDA graphs from now on (if every mixer allows it), and, with
-        ``chunk_rows``, steps in which a single sequence brings exactly that many prompt tokens."""
+                      max_sequence_length: Optional[int] = None, max_batch_tokens: Optional[int] = None) -> None:
+        """Replay pure decode steps as CUDA graphs from now on (if every part of the model allows it), and, with
+        ``chunk_rows``, steps in which one or more sequences (as many as fit ``max_batch_tokens``) bring exactly
+        that many prompt tokens each, beside single decoded tokens of others."""
         from .graph import ChunkGraphs, DecodeGraphs
 
         self.graphs = DecodeGraphs(self, max_batch)
         if chunk_rows is not None and chunk_rows > 16:
-            self.chunk_graphs = ChunkGraphs(self, chunk_rows, max_sequence_length or self.max_positions, max_batch)
+            portions = max(1, (max_batch_tokens or chunk_rows) // chunk_rows)
+            self.chunk_graphs = ChunkGraphs(self, chunk_rows, max_sequence_length or self.max_positions, max_batch,
+                                            max_portions=portions)
 
     def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float], top_ps: Sequence[float],
                         draws: Sequence[float]) -> List[int]:

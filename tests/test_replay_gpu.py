@@ -275,8 +275,52 @@ def test_replayed_portions_beside_decoded_tokens_equal_ordinary_steps(model_fold
     want, _ = run(False)
     got, stepper = run(True)
     assert stepper.chunk_graphs.replays == 4
-    assert sorted(stepper.chunk_graphs.graphs) == [(1, True, 8), (2, False, 8), (4, False, 8)]
+    assert sorted(stepper.chunk_graphs.graphs) == [(1, 1, True, 8), (1, 2, False, 8), (1, 4, False, 8)]
     assert torch.equal(got, want)
+    stepper.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_steps_with_several_portions_equal_ordinary_steps(model_folders, dtype):
+    """A burst of arrivals: three prompts' portions in one step beside decoded tokens of two other requests, then
+    two portions, then one, as the scheduler builds them under its token budget.  Each shape replays as one graph
+    (the last rows of all portions go through the head when one of them is wanted); bit-equal to launch by
+    launch."""
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    folder = model_folders("c")
+    config = TINY["c"]
+    model = load_model(folder, dtype=dtype)
+    chunk = 24
+    prompts = {name: random_tokens(config["vocab_size"], n * chunk, seed=70 + n) for name, n in (("p", 4), ("q", 3), ("r", 2))}
+    others = {name: random_tokens(config["vocab_size"], n, seed=80 + n) for name, n in (("x", 30), ("y", 7))}
+    feed = {name: random_tokens(config["vocab_size"], 8, seed=90 + ord(name)) for name in others}
+
+    def run(graphs):
+        stepper = make_stepper(model, capacity_tokens=512, max_requests=5)
+        if graphs:
+            stepper.enable_graphs(4, chunk_rows=chunk, max_sequence_length=256, max_batch_tokens=4 * chunk)
+        for name, prompt in others.items():
+            assert stepper.cache.admit(name)
+            stepper.step([StepEntry(name, prompt, [])])
+        for name in prompts:
+            assert stepper.cache.admit(name)
+        out = []
+        for k in range(4):
+            entries = []
+            for name, tokens in prompts.items():
+                if (k + 1) * chunk <= len(tokens):
+                    last = (k + 1) * chunk == len(tokens)
+                    entries.append(StepEntry(name, tokens[k * chunk:(k + 1) * chunk], [chunk - 1] if last else []))
+            entries += [StepEntry(name, [feed[name][k]], [0]) for name in (("x", "y") if k < 2 else ("x",))]
+            out.append(stepper.step(entries).clone())
+        return torch.cat(out), stepper
+
+    want, _ = run(False)
+    got, stepper = run(True)
+    assert stepper.chunk_graphs.replays == 4
+    assert sorted(stepper.chunk_graphs.graphs) == [(1, 1, True, 8), (2, 1, True, 8), (3, 2, False, 8), (3, 2, True, 8)]
+    assert got.shape == want.shape and torch.equal(got, want)
     stepper.cache.check()
 
 
