@@ -389,6 +389,42 @@ def test_the_four_cuts_at_the_1b_layer_sizes_with_2_of_16_layers(two_layers_of_t
                 assert np.array_equal(row, results["whole"][key]), f"{cut} differs from whole at {key}"
 
 
+def test_decode_graphs_at_the_1b_head_geometry_across_a_table_width(two_layers_of_the_1b_sizes):
+    """Decode steps replayed as graphs at 32 heads of 64 in 8 groups, two requests, while the longer one's context
+    crosses 128 tokens (its block table outgrows eight pages: another graph, captured with another split count):
+    every step's logits equal the launch-by-launch step's bit for bit, before and after the crossing."""
+    from tesseract_b200 import kernels
+    from tesseract_b200.engine import StepEntry, load_model, make_stepper
+
+    folder, requests, *_ = two_layers_of_the_1b_sizes
+    model = load_model(folder, dtype="bfloat16")
+    prompts = {"long": requests["w2"][:120], "short": requests["w3"][:30]}
+    feed = {"long": requests["w1"][:20], "short": requests["w4"][:20]}
+
+    def run(graphs):
+        stepper = make_stepper(model, capacity_tokens=1024, max_requests=4)
+        if graphs:
+            stepper.enable_graphs(4)
+        for name, prompt in prompts.items():
+            assert stepper.cache.admit(name)
+            stepper.step([StepEntry(name, prompt, [])])
+        out = []
+        for k in range(20):
+            entries = [StepEntry(name, [feed[name][k]], [0]) for name in prompts]
+            if graphs:
+                out.append(stepper.graphs.step(entries, [0.0, 0.0], [0.0, 0.0])[1].clone())
+            else:
+                out.append(stepper.step(entries).clone())
+        return torch.stack(out), stepper
+
+    want, _ = run(False)
+    got, stepper = run(True)
+    assert sorted(stepper.graphs.graphs) == [(2, 8), (2, 16)] and stepper.graphs.replays == 20
+    assert kernels.tcgen05_error() == 0
+    for k in range(20):
+        assert torch.equal(got[k], want[k]), f"decode step {k} (context {120 + k + 1}) differs"
+
+
 # ----------------------------------------------------------------------------- scratch memory under captured graphs
 
 LONG_CONTEXT = {
