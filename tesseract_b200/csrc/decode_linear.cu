@@ -9,6 +9,17 @@
 //   out[m, j] = round(silu(gate_j) * up_j)   (src/cuda/kernels.rs:191-208), for a weight whose rows
 // interleave gate and up in blocks of eight: rows 16b..16b+7 = gate 8b..8b+7, rows 16b+8..16b+15 = up 8b..8b+7.
 //
+// Two more forms move a norm's work out of the product behind it and into the product in front of it:
+//   EPI_ADD_NORM (a product without a norm in front, bfloat16 out): with o = round(y), c = res + o (32-bit),
+//     it stores res_out = round(c), xw = round(c * w) (w: the weights of the norm that FOLLOWS this product)
+//     and, per 16- or 32-feature tile and batch row, the sum of c^2 over the tile's features;
+//   PRO_SCALED: X = xw as it stands, and y = s * sum_k xw_k W_k with s = rsqrt(sum over the tiles' sums / K + eps).
+//   Together: y = s * sum_k round(c_k w_k) W_k, where the reference has sum_k round(c_k s w_k) W_k
+//   (src/cuda/kernels.rs:59-103): the same single rounding of the operand, the same 32-bit statistics of the
+//   unrounded c, the scale applied to the 32-bit sums (a per-row scalar commutes with the sum).  The product
+//   behind then starts like one without a norm (measured alone at 8 rows of the 1B sizes: QKV 3.6 against 5.7 us
+//   with the norm folded in front, gate/up 11.0 against 12.6).
+//
 // Why not the library: at these sizes a decode layer is a chain of launches of a few microseconds
 // each, and the norm and activation kernels between the products cost as much as the products.
 // A CTA owns tiles of 32 (or, for narrow outputs, 16) output features; its 16 warps split K, each streaming its slice of the 32 weight
@@ -26,8 +37,9 @@ constexpr int kThreads = kWarps * 32;
 // One CTA per SM (the prologue, which every CTA repeats, then costs each SM once) with rings deep enough for it
 // to cover the memory latency alone: five stages of 32-feature tiles or six of 16-feature tiles per warp.
 
-enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2 };
-enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2, PRO_SCALED = 3 };
+enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2, EPI_ADD_NORM = 3 };
+constexpr int kSsStride = 16;      // floats per tile in the sums-of-squares array (rows beyond M hold zeros)
 
 struct LinearParams {
     const __nv_bfloat16* x;        // PRO_NONE: [M, K] activations (row stride x_stride)
@@ -40,6 +52,16 @@ struct LinearParams {
     int64_t x_stride, out_stride;
     int M, N, K;
     float eps;
+    // PRO_SCALED: sums of squares [ss_tiles][kSsStride] that an EPI_ADD_NORM product left; eps above
+    const float* ss_in;
+    int ss_tiles;
+    // EPI_ADD_NORM: the residual rows [M, N] that this product's output is added to, the following norm's weights
+    // [N], and what it leaves: the new residual [M, N], round(c * w) [M, N], sums of squares [N / TF][kSsStride]
+    const __nv_bfloat16* epi_res;
+    const float* epi_norm_w;
+    __nv_bfloat16* epi_res_out;
+    __nv_bfloat16* epi_xw;
+    float* epi_ss;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -92,25 +114,29 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     constexpr int ROWS = 8 * MT;
+    constexpr bool kRowsRide = PRO == PRO_NONE || PRO == PRO_SCALED;   // the input rows ride in the ring beside the weights
+    constexpr bool kNormInFront = PRO == PRO_NORM || PRO == PRO_ADD_NORM;
+    __shared__ float scale_s[16];          // PRO_SCALED: the rows' reciprocal root mean squares
+    __shared__ float tile_ss[kWarps][16];  // EPI_ADD_NORM: the warps' sums of squares of a tile
 
     // shared memory: [ROWS][K + 32] bf16 normalised activations (PRO only), the warps' partial sums, the rings
     const int x_pitch = K + 32;  // 64 bytes of padding: the eight rows a quarter-warp reads hit distinct banks
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
-    float* partial = reinterpret_cast<float*>(smem + (PRO != PRO_NONE ? (size_t)ROWS * x_pitch * 2 : 0));
+    float* partial = reinterpret_cast<float*>(smem + (kNormInFront ? (size_t)ROWS * x_pitch * 2 : 0));
 
     // K is cut into 32-wide blocks; warp w takes blocks w, w + 16, ... of every tile (fixed by K alone).  A tile
     // is 32 output features (two 16-row operands that share the activation fragments).  A CTA walks over several
     // tiles, so that the prologue above is paid once.  Each warp keeps a private ring of STAGES blocks in shared
     // memory, filled by cp.async: a lane copies exactly the 16-byte pieces that it later reads back itself, so the
     // ring needs no barrier, only cp.async.wait_group, and runs on across tile boundaries.
-    constexpr int X_BYTES = (PRO == PRO_NONE) ? 512 * MT : 0;   // activations ride along when they come from memory
+    constexpr int X_BYTES = kRowsRide ? 512 * MT : 0;   // activations ride along when they come from memory
     constexpr int TF = 16 * NH;                                  // features per tile
     constexpr int STAGE_BYTES = 1024 * NH + X_BYTES;
     const int blocks = K / 32;
     const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
     const int num_tiles = p.N / TF;
     const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    unsigned char* ring = smem + (PRO != PRO_NONE ? (size_t)ROWS * x_pitch * 2 : 0) +
+    unsigned char* ring = smem + (kNormInFront ? (size_t)ROWS * x_pitch * 2 : 0) +
                           (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)warp * STAGES * STAGE_BYTES;
     const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
     const uint32_t lane_off = (uint32_t)(g * 64 + t * 16);
@@ -129,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 const __nv_bfloat16* src = p_src + b * 32;
 #pragma unroll
                 for (int h = 0; h < 2 * NH; ++h) cp_async16(dst + 512 * h, src + (int64_t)(8 * h) * K);
-                if (PRO == PRO_NONE && with_x) {
+                if (kRowsRide && with_x) {
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         const int row = mt * 8 + g;
@@ -158,19 +184,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
             for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
     pdl_trigger();
     float4 nw_first = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // the norm's weights are weights too: fetch them early
-    if (PRO != PRO_NONE && (int)threadIdx.x * 4 < K) nw_first = *reinterpret_cast<const float4*>(p.norm_w + threadIdx.x * 4);
+    if (kNormInFront && (int)threadIdx.x * 4 < K) nw_first = *reinterpret_cast<const float4*>(p.norm_w + threadIdx.x * 4);
     // Weights do not depend on the kernel before: their first stages go out ahead of the dependency wait.  With a
     // norm in front, the last POST of them are held back until the rows' own loads are out: those would otherwise
     // queue behind the whole ring (some microseconds of HBM time), and the memory would then idle while the norm
     // is computed; held back, they arrive under it (a decode step of eight rows: 0.783 -> 0.772 ms; with sixteen
     // rows and their shallower rings it cost 2 %, so those keep the whole prefetch in front).
-    constexpr int POST = PRO == PRO_NONE || MT > 1 ? 0 : (NH == 2 ? 2 : 3) < STAGES - 1 ? (NH == 2 ? 2 : 3) : STAGES - 2;
+    constexpr int POST = !kNormInFront || MT > 1 ? 0 : (NH == 2 ? 2 : 3) < STAGES - 1 ? (NH == 2 ? 2 : 3) : STAGES - 2;
     constexpr int PRE = STAGES - 1 - POST;
     int early[STAGES - 1];
 #pragma unroll
     for (int q = 0; q < PRE; ++q) early[q] = issue(false);
     pdl_wait();                                      // from here on the previous kernel's results are visible
-    if (PRO == PRO_NONE) {
+    if (PRO == PRO_SCALED) {
+        // The rows' sums of squares that the product in front left, one value per tile of its features: every warp
+        // sums the tiles w, w + 16, ... (two lanes a row, each every other one of them), in an order that depends
+        // on the sizes alone; the first tile's epilogue, behind a block barrier, adds the sixteen warps' sums.
+        const int m = lane & 15;
+        float part = 0.0f;
+        for (int tile = warp + kWarps * (lane >> 4); tile < p.ss_tiles; tile += 2 * kWarps)
+            part += __ldcg(p.ss_in + tile * kSsStride + m);
+        part += __shfl_xor_sync(0xffffffffu, part, 16);
+        if (lane < 16) tile_ss[warp][lane] = part;
+    }
+    if (kRowsRide) {
         // the activations of the blocks above, a group each: the loop's wait count then covers them as well
 #pragma unroll
         for (int q = 0; q < STAGES - 1; ++q) {
@@ -187,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         }
     }
 
-    if (PRO != PRO_NONE) {
+    if (kNormInFront) {
         // Every CTA normalises the (few) rows itself, all threads side by side along K; CTA 0 also stores the
         // new residual.  Two passes over the rows (the second one hits L1): sums of squares, then the scaling.
         // Eight rows at a time, all their loads issued before the first use (rows beyond M repeat row M - 1, so
@@ -296,6 +333,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
 
     int cs = 0;        // consumer ring slot
     for (int ti = 0; ti < my_tiles; ++ti) {
+        // EPI_ADD_NORM: what this thread's item of the tile's epilogue adds to and multiplies with does not depend
+        // on the products: asked for now, it is there when the products are done
+        __nv_bfloat162 epi_r = __floats2bfloat162_rn(0.0f, 0.0f);
+        float2 epi_w = make_float2(0.0f, 0.0f);
+        if (EPI == EPI_ADD_NORM && (int)threadIdx.x < (TF / 2) * ROWS && (int)threadIdx.x % ROWS < p.M) {
+            const int col = ((int)blockIdx.x + ti * (int)gridDim.x) * TF + 2 * ((int)threadIdx.x / ROWS);
+            epi_r = *reinterpret_cast<const __nv_bfloat162*>(p.epi_res + (int64_t)((int)threadIdx.x % ROWS) * p.N + col);
+            epi_w = *reinterpret_cast<const float2*>(p.epi_norm_w + col);
+        }
         for (int j = 0; j < bpw; ++j) {
             issue(true);
             cp_async_wait<STAGES - 1>();
@@ -309,7 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 for (int mt = 0; mt < MT; ++mt) {
                     uint4 xa;
                     const int row = mt * 8 + g;
-                    if (PRO != PRO_NONE)
+                    if (kNormInFront)
                         xa = *reinterpret_cast<const uint4*>(xs + (size_t)row * x_pitch + b * 32 + 8 * t);
                     else if (row >= p.M)
                         xa = make_uint4(0, 0, 0, 0);
@@ -340,6 +386,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
             }
         __syncthreads();
+        if (PRO == PRO_SCALED && ti == 0 && threadIdx.x < 16) {
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) total += tile_ss[w][threadIdx.x];
+            scale_s[threadIdx.x] = 1.0f / sqrtf(total / (float)K + p.eps);
+        }
+        if (PRO == PRO_SCALED && ti == 0) __syncthreads();
         if (EPI == EPI_SWIGLU) {
             // of every 16 features the first eight are gates, the last eight the matching up projections
             for (int idx = threadIdx.x; idx < 8 * NH * ROWS; idx += kThreads) {
@@ -352,6 +405,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     gate += partial[(size_t)w * TF * ROWS + gate_row * ROWS + m];
                     up += partial[(size_t)w * TF * ROWS + (gate_row + 8) * ROWS + m];
                 }
+                if (PRO == PRO_SCALED) {
+                    gate *= scale_s[m];
+                    up *= scale_s[m];
+                }
                 const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
                 reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.out_stride + tile * 8 * NH + f] =
                     __float2bfloat16_rn(act);
@@ -360,6 +417,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
             // A thread sums two neighbouring features of one batch row: consecutive lanes then read consecutive
             // batch rows of the partial sums (at most two lanes per bank; one feature per lane along the features
             // would put 8 or 16 lanes on a bank) and store the pair at once.
+            static_assert((TF / 2) * ROWS <= kThreads, "one item per thread");
+            float ss = 0.0f;                     // EPI_ADD_NORM: this thread's share of its row's sum of squares
             for (int idx = threadIdx.x; idx < (TF / 2) * ROWS; idx += kThreads) {
                 const int f = 2 * (idx / ROWS), m = idx % ROWS;
                 if (m >= p.M) continue;
@@ -369,7 +428,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     sum0 += partial[(size_t)w * TF * ROWS + f * ROWS + m];
                     sum1 += partial[(size_t)w * TF * ROWS + (f + 1) * ROWS + m];
                 }
-                if (EPI == EPI_F32) {
+                if (PRO == PRO_SCALED) {
+                    sum0 *= scale_s[m];
+                    sum1 *= scale_s[m];
+                }
+                if (EPI == EPI_ADD_NORM) {
+                    // o = round(y) as the product alone would store it; c = res + o; the new residual, the
+                    // following norm's operand round(c * w), and c^2 towards the row's statistics
+                    const int64_t at = (int64_t)m * p.N + n0 + f;
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(sum0, sum1);
+                    const __nv_bfloat162 r = epi_r;
+                    const float c0 = __bfloat162float(r.x) + __bfloat162float(o.x);
+                    const float c1 = __bfloat162float(r.y) + __bfloat162float(o.y);
+                    const float2 w2 = epi_w;
+                    *reinterpret_cast<__nv_bfloat162*>(p.epi_res_out + at) = __floats2bfloat162_rn(c0, c1);
+                    *reinterpret_cast<__nv_bfloat162*>(p.epi_xw + at) = __floats2bfloat162_rn(c0 * w2.x, c1 * w2.y);
+                    ss = fmaf(c0, c0, c1 * c1);
+                } else if (EPI == EPI_F32) {
                     float* o = reinterpret_cast<float*>(p.out) + (int64_t)m * p.out_stride + n0 + f;
                     if ((uintptr_t)o % 8 == 0) {
                         *reinterpret_cast<float2*>(o) = make_float2(sum0, sum1);
@@ -387,8 +462,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     }
                 }
             }
+            if (EPI == EPI_ADD_NORM) {
+                // a row's items sit in lanes m, m + ROWS, ...: sum them in a fixed order, one value per warp and row
+                if (ROWS == 8) ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+                if (lane < ROWS) tile_ss[warp][lane] = ss;
+            }
         }
         __syncthreads();  // the partial sums are reused by the next tile
+        if (EPI == EPI_ADD_NORM && threadIdx.x < kSsStride) {
+            float total = 0.0f;
+            if ((int)threadIdx.x < ROWS) {
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) total += tile_ss[w][threadIdx.x];
+            }
+            p.epi_ss[(int64_t)tile * kSsStride + threadIdx.x] = total;    // rows beyond M (and beyond ROWS) hold zeros
+        }
     }
 }
 
@@ -429,7 +518,7 @@ int stages_for(int rows8, bool prologue, int nh, int K) {
 template <int MT, int PRO, int EPI, int NH, int STAGES>
 int launch_ring(const LinearParams& p, cudaStream_t stream) {
     constexpr int TF = 16 * NH;
-    const size_t smem = smem_bytes(MT, PRO != PRO_NONE, NH, p.K, STAGES);
+    const size_t smem = smem_bytes(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM, NH, p.K, STAGES);
     auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, STAGES>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -446,7 +535,7 @@ int launch_ring(const LinearParams& p, cudaStream_t stream) {
 
 template <int MT, int PRO, int EPI, int NH>
 int launch_tiles(const LinearParams& p, cudaStream_t stream) {
-    const int stages = stages_for(MT, PRO != PRO_NONE, NH, p.K);
+    const int stages = stages_for(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM, NH, p.K);
     if (stages == deep_stages(NH, MT)) return launch_ring<MT, PRO, EPI, NH, deep_stages(NH, MT)>(p, stream);
     if constexpr (MT > 1) {
         if (stages == kShallowStages) return launch_ring<MT, PRO, EPI, NH, kShallowStages>(p, stream);
@@ -473,6 +562,10 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
     TB_CASE(PRO_ADD_NORM, EPI_BF16)
     TB_CASE(PRO_ADD_NORM, EPI_F32)
     TB_CASE(PRO_ADD_NORM, EPI_SWIGLU)
+    TB_CASE(PRO_NONE, EPI_ADD_NORM)
+    TB_CASE(PRO_SCALED, EPI_BF16)
+    TB_CASE(PRO_SCALED, EPI_F32)
+    TB_CASE(PRO_SCALED, EPI_SWIGLU)
 #undef TB_CASE
     return TB_ERR_BAD_SIZE;
 }
@@ -482,18 +575,34 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
 // 1 if the sizes are ones this kernel takes, else 0 (the caller then uses the general path).
 TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
     if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < 32 || K % 32 != 0) return 0;
-    return stages_for(M <= 8 ? 1 : 2, prologue != PRO_NONE, wide_tiles(N) ? 2 : 1, K) != 0;
+    const bool norm_in_front = prologue == PRO_NORM || prologue == PRO_ADD_NORM;
+    return stages_for(M <= 8 ? 1 : 2, norm_in_front, wide_tiles(N) ? 2 : 1, K) != 0;
 }
 
-// x: PRO_NONE only.  res/upd/norm_w/res_out: see LinearParams.  out_stride in elements of the output type.
-TB_EXPORT int tb_decode_linear(const void* x, int64_t x_stride, const void* res, const void* upd,
-                               const float* norm_w, float eps, void* res_out, const void* w, void* out,
-                               int64_t out_stride, int M, int N, int K, int prologue, int epilogue,
-                               cudaStream_t stream) {
+// Features per tile for an output width (what EPI_ADD_NORM's sums of squares are counted in).
+TB_EXPORT int tb_decode_linear_tile_features(int N) { return wide_tiles(N) ? 32 : 16; }
+
+// x: PRO_NONE and PRO_SCALED (the rows as they are).  res/upd/norm_w/res_out: see LinearParams.  out_stride in
+// elements of the output type.
+// PRO_SCALED: ss_in [ss_tiles][16] sums of squares that an EPI_ADD_NORM call left; the scale uses eps.
+// EPI_ADD_NORM (with PRO_NONE): epi_res [M, N] residual, epi_norm_w [N], and the outputs epi_res_out [M, N],
+//   epi_xw [M, N], epi_ss [N / tb_decode_linear_tile_features(N)][16]; `out` is not written.
+TB_EXPORT int tb_decode_linear_ex(const void* x, int64_t x_stride, const void* res, const void* upd,
+                                  const float* norm_w, float eps, void* res_out, const void* w, void* out,
+                                  int64_t out_stride, int M, int N, int K, int prologue, int epilogue,
+                                  const float* ss_in, int ss_tiles, const void* epi_res, const float* epi_norm_w,
+                                  void* epi_res_out, void* epi_xw, float* epi_ss, cudaStream_t stream) {
     if (!tb_decode_linear_supported(M, N, K, prologue)) return TB_ERR_BAD_SIZE;
-    const uintptr_t bits = (uintptr_t)x | (uintptr_t)res | (uintptr_t)upd | (uintptr_t)res_out | (uintptr_t)w;
-    if (bits % 16 != 0 || (prologue == PRO_NONE && x_stride % 8 != 0)) return TB_ERR_BAD_ALIGN;
+    const uintptr_t bits = (uintptr_t)x | (uintptr_t)res | (uintptr_t)upd | (uintptr_t)res_out | (uintptr_t)w |
+                           (uintptr_t)epi_res | (uintptr_t)epi_res_out | (uintptr_t)epi_xw;
+    const bool rows_ride = prologue == PRO_NONE || prologue == PRO_SCALED;
+    if (bits % 16 != 0 || (rows_ride && (x == nullptr || x_stride % 8 != 0))) return TB_ERR_BAD_ALIGN;
     if (prologue == PRO_ADD_NORM && (res_out == nullptr || res_out == res)) return TB_ERR_BAD_ALIGN;
+    if (prologue == PRO_SCALED && (ss_in == nullptr || ss_tiles < 1)) return TB_ERR_BAD_ALIGN;
+    if (epilogue == EPI_ADD_NORM &&
+        (prologue != PRO_NONE || epi_res == nullptr || epi_norm_w == nullptr || epi_res_out == nullptr ||
+         epi_xw == nullptr || epi_ss == nullptr || epi_res_out == epi_res || (uintptr_t)epi_norm_w % 8 != 0))
+        return TB_ERR_BAD_ALIGN;
     LinearParams p;
     p.x = (const __nv_bfloat16*)x;
     p.res = (const __nv_bfloat16*)res;
@@ -508,5 +617,21 @@ TB_EXPORT int tb_decode_linear(const void* x, int64_t x_stride, const void* res,
     p.N = N;
     p.K = K;
     p.eps = eps;
+    p.ss_in = ss_in;
+    p.ss_tiles = ss_tiles;
+    p.epi_res = (const __nv_bfloat16*)epi_res;
+    p.epi_norm_w = epi_norm_w;
+    p.epi_res_out = (__nv_bfloat16*)epi_res_out;
+    p.epi_xw = (__nv_bfloat16*)epi_xw;
+    p.epi_ss = epi_ss;
     return M <= 8 ? dispatch<1>(p, prologue, epilogue, stream) : dispatch<2>(p, prologue, epilogue, stream);
+}
+
+TB_EXPORT int tb_decode_linear(const void* x, int64_t x_stride, const void* res, const void* upd,
+                               const float* norm_w, float eps, void* res_out, const void* w, void* out,
+                               int64_t out_stride, int M, int N, int K, int prologue, int epilogue,
+                               cudaStream_t stream) {
+    if (prologue == PRO_SCALED || epilogue == EPI_ADD_NORM) return TB_ERR_BAD_SIZE;
+    return tb_decode_linear_ex(x, x_stride, res, upd, norm_w, eps, res_out, w, out, out_stride, M, N, K, prologue,
+                               epilogue, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, stream);
 }

@@ -156,7 +156,10 @@ class Stepper:
         for entry in entries:
             self.cache.extend(entry.request, len(entry.tokens))
         ctx, want_rows, _ = self.build_context(entries)
-        logits = self.model.forward(ctx, self.cache.bindings, want_rows)
+        # every place of every entry wanted, in order (a decode step): the model need not pick rows out, and takes
+        # the same path as a replayed decode step, bit for bit
+        every_row = all(list(e.want) == list(range(len(e.tokens))) for e in entries)
+        logits = self.model.forward(ctx, self.cache.bindings, want_rows, want_every_row=every_row)
         for entry in entries:
             self.cache.commit(entry.request, len(entry.tokens))
         self.steps_run += 1

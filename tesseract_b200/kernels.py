@@ -410,24 +410,50 @@ def decode_linear_supported(rows: int, out_features: int, in_features: int, prol
                                                                         _i32(in_features), _i32(prologue)))
 
 
-def decode_linear(weight: torch.Tensor, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
+EPI_ADD_NORM = 3
+PRO_SCALED = 3
+SS_STRIDE = 16      # floats per tile in the sums-of-squares array that one product leaves for the next
+
+
+def decode_linear_tile_features(out_features: int) -> int:
+    """Features per tile of the skinny decode product at this output width (16 or 32)."""
+    return int(load_library("decode_linear").tb_decode_linear_tile_features(_i32(out_features)))
+
+
+def decode_linear(weight: torch.Tensor, out: Optional[torch.Tensor], *, x: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, update: Optional[torch.Tensor] = None,
                   norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
-                  residual_out: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16) -> torch.Tensor:
+                  residual_out: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
+                  scaled_by: Optional[torch.Tensor] = None, prepare: Optional[tuple] = None) -> Optional[torch.Tensor]:
     """``out = X @ weight^T`` for at most 16 rows (bfloat16 weights, 32-bit accumulation).
 
     ``X`` is ``x``, or ``rms_norm(residual)`` (``norm_weight`` given), or ``rms_norm(residual + update)``
     with the rounded sum stored in ``residual_out`` (which must not be ``residual``).  ``epilogue``:
     ``EPI_BF16`` / ``EPI_F32`` store ``[M, N]``; ``EPI_SWIGLU`` treats the weight's rows as blocks of eight gates
     and eight up projections and stores ``silu(gate) * up`` as ``[M, N / 2]``.
+
+    Two forms move the work of the norm that FOLLOWS a product into that product:
+    ``prepare=(residual, norm_weight, residual_out, scaled_rows, sums)`` (with ``x``; ``out`` is not written and
+    may be None): with ``c = residual + round(x @ weight^T)`` it stores ``residual_out = round(c)``,
+    ``scaled_rows = round(c * norm_weight)`` and per tile of output features the rows' sums of ``c^2`` into
+    ``sums`` (float32 ``[N / decode_linear_tile_features(N), 16]``).  ``scaled_by=sums`` (with ``x`` = such
+    ``scaled_rows`` and ``eps``): ``out = rsqrt(sum(sums) / K + eps) * (x @ weight^T)``, row by row: together the
+    norm's scale meets the 32-bit sums of the product behind it.
     """
-    _cuda(weight, out, x, residual, update, norm_weight, residual_out)
+    _cuda(weight, out, x, residual, update, norm_weight, residual_out, scaled_by)
     n, k = weight.shape
     _need(weight.dtype == torch.bfloat16 and weight.is_contiguous(), "decode_linear weight must be contiguous bfloat16")
+    ss_in, ss_tiles = None, 0
     if norm_weight is None:
         prologue, source = PRO_NONE, x
         _need(x is not None and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == k, "decode_linear x")
+        if scaled_by is not None:
+            prologue = PRO_SCALED
+            _need(scaled_by.dtype == torch.float32 and scaled_by.dim() == 2 and scaled_by.shape[1] == SS_STRIDE
+                  and scaled_by.is_contiguous() and scaled_by.shape[0] >= 1, "decode_linear sums of squares")
+            ss_in, ss_tiles = scaled_by, scaled_by.shape[0]
     else:
+        _need(scaled_by is None and prepare is None, "decode_linear: a norm in front excludes scaled_by and prepare")
         prologue, source = (PRO_ADD_NORM if update is not None else PRO_NORM), residual
         _need(residual is not None and residual.dtype == torch.bfloat16 and residual.is_contiguous()
               and residual.shape[1] == k, "decode_linear residual")
@@ -439,14 +465,30 @@ def decode_linear(weight: torch.Tensor, out: torch.Tensor, *, x: Optional[torch.
                   and residual_out.dtype == torch.bfloat16 and residual_out.data_ptr() != residual.data_ptr(),
                   "decode_linear residual_out must be a separate bfloat16 buffer")
     m = source.shape[0]
-    width = n // 2 if epilogue == EPI_SWIGLU else n
-    _need(out.shape == (m, width) and out.stride(1) == 1, "decode_linear out shape")
-    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "decode_linear out dtype")
+    epi = (None,) * 5
+    if prepare is not None:
+        _need(prologue == PRO_NONE and epilogue == EPI_BF16, "decode_linear: prepare goes with plain rows and a bfloat16 product")
+        epilogue = EPI_ADD_NORM
+        p_res, p_norm, p_res_out, p_rows, p_sums = prepare
+        _cuda(p_res, p_norm, p_res_out, p_rows, p_sums)
+        for t in (p_res, p_res_out, p_rows):
+            _need(t.shape == (m, n) and t.dtype == torch.bfloat16 and t.is_contiguous(), "decode_linear prepare rows")
+        _need(p_res_out.data_ptr() != p_res.data_ptr(), "decode_linear prepare: the new residual needs a buffer of its own")
+        _need(p_norm.dtype == torch.float32 and p_norm.numel() == n and p_norm.is_contiguous(), "decode_linear prepare norm weight")
+        tiles = n // decode_linear_tile_features(n)
+        _need(p_sums.dtype == torch.float32 and tuple(p_sums.shape) == (tiles, SS_STRIDE) and p_sums.is_contiguous(),
+              f"decode_linear prepare sums must be float32 [{tiles}, {SS_STRIDE}]")
+        epi = (p_res, p_norm, p_res_out, p_rows, p_sums)
+    else:
+        width = n // 2 if epilogue == EPI_SWIGLU else n
+        _need(out is not None and out.shape == (m, width) and out.stride(1) == 1, "decode_linear out shape")
+        _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "decode_linear out dtype")
     lib = load_library("decode_linear")
-    _check(lib.tb_decode_linear(_ptr(x), _i64(x.stride(0) if x is not None else 0), _ptr(residual), _ptr(update),
-                                _ptr(norm_weight), _f32(eps), _ptr(residual_out), _ptr(weight), _ptr(out),
-                                _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(prologue), _i32(epilogue),
-                                _stream()), "decode_linear")
+    _check(lib.tb_decode_linear_ex(_ptr(x), _i64(x.stride(0) if x is not None else 0), _ptr(residual), _ptr(update),
+                                   _ptr(norm_weight), _f32(eps), _ptr(residual_out), _ptr(weight), _ptr(out),
+                                   _i64(out.stride(0) if out is not None else 0), _i32(m), _i32(n), _i32(k),
+                                   _i32(prologue), _i32(epilogue), _ptr(ss_in), _i32(ss_tiles), _ptr(epi[0]),
+                                   _ptr(epi[1]), _ptr(epi[2]), _ptr(epi[3]), _ptr(epi[4]), _stream()), "decode_linear")
     return out
 
 

@@ -111,15 +111,30 @@ class DecoderModel:
         rows need not be gathered before the head."""
         hidden = self.embedding.forward(ctx.token_ids[:ctx.num_rows])
         stream = ResidualStream(hidden, None)
-        for index, entry in enumerate(self.spec.run_order):
-            stream = self.layers[entry.layer].forward(stream, ctx, bindings[index])
-        if want_rows is None or want_rows.numel() == 0:
+        order = self.spec.run_order
+        wants_logits = want_rows is not None and want_rows.numel() > 0
+        every_row = wants_logits and want_every_row and want_rows.numel() == ctx.num_rows
+        for index, entry in enumerate(order):
+            block = self.layers[entry.layer]
+            if not block.accepts_next_norm:
+                stream = block.forward(stream, ctx, bindings[index])
+                continue
+            # the norm that will consume what this block returns: the next block's first one, or the final norm if
+            # it runs on every row (on a few wanted rows it runs after they have been picked out)
+            if index + 1 < len(order):
+                next_norm = self.layers[order[index + 1].layer].entry_norm()
+            else:
+                next_norm = self.final_norm if every_row else None
+            stream = block.forward(stream, ctx, bindings[index], next_norm=next_norm)
+        if not wants_logits:
             return None
-        return self.logits_at(stream, want_rows, want_every_row and want_rows.numel() == ctx.num_rows)
+        return self.logits_at(stream, want_rows, every_row)
 
     def logits_at(self, stream: ResidualStream, want_rows: torch.Tensor, every_row: bool = False) -> torch.Tensor:
         count = want_rows.numel()
         width = stream.residual.shape[1]
+        if every_row and stream.prepared is not None and stream.prepared.norm is self.final_norm:
+            return self.head.forward(stream.prepared if self.head.accepts_deferred_norm else stream.prepared.materialize())
         if every_row:
             residual, update = stream.residual[:count], None if stream.update is None else stream.update[:count]
         else:

@@ -31,6 +31,7 @@ class Attention(Mixer):
     weights: ``q, k, v, o``.  children: ``position`` (a position encoding spec)."""
 
     accepts_deferred_norm = True
+    accepts_follow_norm = True
     graph_safe = True      # reads only device-side metadata of the step, so a decode step can be captured
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
@@ -78,7 +79,7 @@ class Attention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window or None)
 
-    def forward(self, x, ctx: StepContext, cache: Optional[CacheBinding]) -> torch.Tensor:
+    def forward(self, x, ctx: StepContext, cache: Optional[CacheBinding], follow=None):
         if cache is None or cache.storage is None:
             raise RuntimeError("attention needs a paged key/value cache binding")
         group = ctx.groups[cache.group]
@@ -103,7 +104,7 @@ class Attention(Mixer):
                                           group.block_table, ctx.num_seqs, self.num_heads, self.num_kv_heads,
                                           self.head_dim, cache.page_size, self.window, self.scale, inv_freq,
                                           cache.writes, choice.splits)
-            return self.o_proj.forward(attended)
+            return self.o_proj.forward(attended, follow=follow)
         if inv_freq is None and self.position.kind != "none":
             q_view = qkv[:, :self.q_width].view(rows, self.num_heads, self.head_dim)
             k_view = qkv[:, self.q_width:self.q_width + self.kv_width].view(rows, self.num_kv_heads, self.head_dim)
@@ -117,7 +118,7 @@ class Attention(Mixer):
             kernels.attention_rows(q, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
                                    self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
                                    self.scale)
-            return self.o_proj.forward(attended)
+            return self.o_proj.forward(attended, follow=follow)
         tiles = choice.prompt == "mma_tiles"
         if choice.prompt == "tcgen05":
             # prompt portions on the fifth-generation tensor cores; decode rows (if any) by the split kernel
@@ -128,4 +129,4 @@ class Attention(Mixer):
             kernels.attention_mma(q, attended, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
                                   ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
                                   cache.page_size, self.window, self.scale, tiles, choice.split, choice.splits)
-        return self.o_proj.forward(attended)
+        return self.o_proj.forward(attended, follow=follow)

@@ -206,11 +206,14 @@ class ResidualStream:
     """The hidden state between blocks: ``residual + update`` (``update`` may be absent).
 
     Keeping the pending update apart lets the next norm fuse the addition
-    (src/cuda/dense_decoder.rs:668-672, 775).
+    (src/cuda/dense_decoder.rs:668-672, 775).  ``prepared``: the block in front has already added its update and
+    done the work of the norm that consumes this stream (a :class:`PreparedNorm`; ``residual`` is then the new
+    residual and ``update`` is None).
     """
 
     residual: torch.Tensor
     update: Optional[torch.Tensor] = None
+    prepared: Optional["PreparedNorm"] = None
 
 
 class DeferredNorm:
@@ -247,6 +250,29 @@ class DeferredNorm:
         if new_residual is not None:
             self.residual = new_residual
         self.done = True
+
+
+class FollowNorm:
+    """What a part is told about the norm BEHIND it, so that its last product may do that norm's work on the way
+    out: ``norm`` follows the part's output, which is added to the residual stream as it stands once ``before``
+    (the deferred norm in front of the part) has been consumed (``before.residual``)."""
+
+    def __init__(self, norm: "Norm", before: DeferredNorm):
+        self.norm = norm
+        self.before = before
+
+
+class PreparedNorm(DeferredNorm):
+    """``norm(residual)`` whose work the product in front has already done: ``residual`` holds the new residual
+    (the update is added), ``rows`` holds ``round(residual_unrounded * weight)`` and ``sums`` the sums of squares of
+    the unrounded rows per tile of features.  A product that can apply the scale to its own sums takes ``rows``
+    and ``sums`` (``Linear.forward_normed``); any other consumer calls :meth:`materialize`, which runs the norm's
+    own kernel on the new residual."""
+
+    def __init__(self, norm: "Norm", residual: torch.Tensor, rows: torch.Tensor, sums: torch.Tensor):
+        super().__init__(norm, residual, None)
+        self.scaled_rows = rows
+        self.sums = sums
 
 
 # ----------------------------------------------------------------------------- part bases
@@ -293,6 +319,9 @@ class PositionEncoding(Part):
 class Mixer(Part):
     # True if ``forward`` also takes a :class:`DeferredNorm` in place of ``x``.
     accepts_deferred_norm = False
+    # True if ``forward`` takes ``follow=FollowNorm(...)`` and may then return a :class:`PreparedNorm` instead of
+    # its output rows (its last product did the following norm's work).
+    accepts_follow_norm = False
     def cache_need(self):
         return None
 
@@ -302,6 +331,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_deferred_norm = False     # True if ``forward`` also takes a :class:`DeferredNorm` in place of ``x``
+    accepts_follow_norm = False       # True if ``forward`` takes ``follow=FollowNorm(...)`` (see :class:`Mixer`)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -321,11 +351,18 @@ class Head(Part):
 
 class Block:
     kind: str = ""
+    # True if ``forward`` takes ``next_norm`` (the norm that will consume the stream this block returns) and may
+    # return a stream whose ``prepared`` is set for it.
+    accepts_next_norm = False
 
     def __init__(self, norms: Mapping[str, Norm], mixer: Mixer, feed_forward: FeedForward):
         self.norms = dict(norms)
         self.mixer = mixer
         self.feed_forward = feed_forward
+
+    def entry_norm(self) -> Optional[Norm]:
+        """The norm that consumes the incoming stream first (None: the block does not say)."""
+        return None
 
     @classmethod
     def norm_roles(cls) -> Tuple[str, ...]:

@@ -24,9 +24,9 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
 
     def plan(self, rows: int, epilogue: str = plan.BF16, norm: Optional[str] = None,
-             contiguous_rows: bool = True) -> plan.ProductPlan:
+             contiguous_rows: bool = True, follow: bool = False) -> plan.ProductPlan:
         return plan.product(self.runtime.dtype, rows, self.out_features, self.in_features, epilogue=epilogue,
-                            norm=norm, contiguous_rows=contiguous_rows)
+                            norm=norm, contiguous_rows=contiguous_rows, follow=follow)
 
     def _out(self, rows: int, choice: plan.ProductPlan, device) -> torch.Tensor:
         width = self.out_features // 2 if choice.epilogue == plan.SWIGLU else self.out_features
@@ -34,9 +34,11 @@ class Linear:
         return torch.empty((rows, width), dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, float32_out: bool = False,
-                epilogue: Optional[str] = None) -> torch.Tensor:
+                epilogue: Optional[str] = None, follow=None):
         """``x @ W^T``; with ``epilogue="swiglu"`` the activated product ``[rows, out / 2]`` if the plan has a kernel
-        that folds the activation in, else ``None`` (the caller then activates the plain product itself)."""
+        that folds the activation in, else ``None`` (the caller then activates the plain product itself).  With
+        ``follow`` (a :class:`FollowNorm`) the product may do the work of the norm behind it and return a
+        :class:`PreparedNorm` instead of its rows, if the plan has a kernel for that."""
         if x.shape[-1] != self.in_features:
             raise ValueError(f"linear expects width {self.in_features}, got {x.shape[-1]}")
         if not x.is_cuda:
@@ -46,6 +48,10 @@ class Linear:
         choice = self.plan(rows, wanted, contiguous_rows=x.stride(1) == 1)
         if wanted == plan.SWIGLU and choice.activation_apart:
             return None
+        if follow is not None and out is None and wanted == plan.BF16:
+            prepared = self._prepare(x, follow)
+            if prepared is not None:
+                return prepared
         if choice.kernel == "library":
             if choice.epilogue == plan.F32:
                 result = torch.mm(x, self.weight.t(), out_dtype=torch.float32)
@@ -59,14 +65,50 @@ class Linear:
             return kernels.decode_linear(self.weight, out, x=x, epilogue=choice.epilogue_code)
         return kernels.gemm_tcgen05(x, self.weight, out, epilogue=choice.epilogue_code)
 
+    def _prepare(self, x: torch.Tensor, follow):
+        """The product with the following norm's work folded behind it, or None if that cannot be."""
+        from .base import PreparedNorm
+
+        parameters = getattr(follow.norm, "rms_parameters", None)
+        residual = follow.before.residual
+        rows = x.shape[0]
+        if (parameters is None or not follow.before.done or residual.shape != (rows, self.out_features)
+                or residual.dtype != self.runtime.dtype or not residual.is_contiguous() or x.stride(1) != 1):
+            return None
+        if not self.plan(rows, plan.BF16, follow=True).prepares_norm:
+            return None
+        weight, _ = parameters()
+        if weight.numel() != self.out_features:
+            return None
+        new_residual = torch.empty_like(residual)
+        scaled_rows = torch.empty_like(residual)
+        tiles = self.out_features // kernels.decode_linear_tile_features(self.out_features)
+        sums = torch.empty((tiles, kernels.SS_STRIDE), dtype=torch.float32, device=residual.device)
+        kernels.decode_linear(self.weight, None, x=x, prepare=(residual, weight, new_residual, scaled_rows, sums))
+        return PreparedNorm(follow.norm, new_residual, scaled_rows, sums)
+
     def forward_normed(self, deferred, float32_out: bool = False, epilogue: Optional[str] = None) -> torch.Tensor:
         """``norm(residual [+ update]) @ W^T`` with the norm folded into the product's kernel, or ``None`` when the
         plan has no such kernel for these sizes or the norm does not offer its parameters for folding
         (``rms_parameters()``): the caller then lets the norm run on its own."""
+        from .base import PreparedNorm
+
         parameters = getattr(deferred.norm, "rms_parameters", None)
         if parameters is None or deferred.done or not deferred.residual.is_contiguous():
             return None
         wanted = epilogue or (plan.F32 if float32_out else plan.BF16)
+        if isinstance(deferred, PreparedNorm):
+            # the product in front left the rows times the norm's weights and their sums of squares: this product
+            # takes them as they are and applies the scale to its 32-bit sums
+            choice = self.plan(deferred.rows, wanted, norm="prepared")
+            if not choice.norm_folded:
+                return None
+            _, eps = parameters()
+            out = self._out(deferred.rows, choice, deferred.residual.device)
+            kernels.decode_linear(self.weight, out, x=deferred.scaled_rows, scaled_by=deferred.sums, eps=eps,
+                                  epilogue=choice.epilogue_code)
+            deferred.fused(None)
+            return out
         choice = self.plan(deferred.rows, wanted, norm="norm" if deferred.update is None else "add_norm")
         if not choice.norm_folded:
             return None

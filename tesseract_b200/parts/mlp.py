@@ -54,8 +54,9 @@ class SwiGLU(FeedForward):
         }
 
     accepts_deferred_norm = True
+    accepts_follow_norm = True
 
-    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+    def forward(self, x, ctx: StepContext, follow=None):
         activated = None
         epilogue = plan.SWIGLU if self.interleaved else plan.BF16
         if isinstance(x, DeferredNorm):
@@ -69,4 +70,4 @@ class SwiGLU(FeedForward):
             gate_up = self.gate_up_proj.forward(x)
             activated = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
             kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)
-        return self.down_proj.forward(activated)
+        return self.down_proj.forward(activated, follow=follow)

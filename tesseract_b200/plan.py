@@ -57,12 +57,16 @@ class ProductPlan:
     """``kernel``: ``gemm_f32`` (true 32-bit FFMA), ``decode_linear`` (weight streaming, at most 16 rows),
     ``gemm_tcgen05`` (this package's tensor-memory GEMM) or ``library``.  ``norm_folded``: the RMSNorm (and the
     residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
-    ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product."""
+    ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product.
+    ``prepares_norm``: the product also does the work of the norm BEHIND it (new residual, rows times the norm's
+    weights, sums of squares); the product behind that then runs with ``norm="prepared"``: it takes those rows as
+    they are and applies the scale to its 32-bit sums."""
 
     kernel: str
     norm_folded: bool = False
     epilogue: str = BF16
     activation_apart: bool = False
+    prepares_norm: bool = False
 
     @property
     def epilogue_code(self) -> int:
@@ -74,17 +78,27 @@ class ProductPlan:
             extras.insert(0, "add+norm folded in front")
         if self.activation_apart:
             extras.append("SwiGLU as a kernel of its own")
+        if self.prepares_norm:
+            extras.append("does the following add+norm's work")
         return f"{self.kernel} ({', '.join(extras)})"
 
 
 def product(dtype: torch.dtype, rows: int, out_features: int, in_features: int, *, epilogue: str = BF16,
-            norm: Optional[str] = None, contiguous_rows: bool = True) -> ProductPlan:
+            norm: Optional[str] = None, contiguous_rows: bool = True, follow: bool = False) -> ProductPlan:
     """The kernel for ``[rows, in] @ [out, in]^T``.  ``norm``: ``"norm"`` or ``"add_norm"`` if an RMSNorm (with the
-    residual addition) stands in front and may be folded in; ``epilogue``: ``bf16``, ``f32`` (logits) or ``swiglu``
-    (the weight's rows interleave eight gates and eight up projections)."""
+    residual addition) stands in front and may be folded in, ``"prepared"`` if the product in front has done that
+    norm's work; ``epilogue``: ``bf16``, ``f32`` (logits) or ``swiglu`` (the weight's rows interleave eight gates
+    and eight up projections); ``follow``: an addition and an RMSNorm of the product's own width follow it."""
     if dtype == torch.float32:
         return ProductPlan("gemm_f32", False, F32, activation_apart=epilogue == SWIGLU)
     if rows <= DECODE_LINEAR_MAX_ROWS and contiguous_rows:
+        if norm == "prepared":
+            if _decode_linear_takes(rows, out_features, in_features, kernels.PRO_NONE):
+                return ProductPlan("decode_linear", True, epilogue)
+            return ProductPlan("library", False, BF16 if epilogue == SWIGLU else epilogue, activation_apart=epilogue == SWIGLU)
+        if follow and norm is None and epilogue == BF16 and _decode_linear_takes(rows, out_features, in_features,
+                                                                                kernels.PRO_NONE):
+            return ProductPlan("decode_linear", False, BF16, prepares_norm=True)
         if norm is not None:
             prologue = kernels.PRO_NORM if norm == "norm" else kernels.PRO_ADD_NORM
             if _decode_linear_takes(rows, out_features, in_features, prologue):
@@ -202,9 +216,16 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
         for rows in row_counts:
             lines.append(f"  {rows} rows")
             mixer, ffn = block.mixer, block.feed_forward
+            down_prepares = False
+            if isinstance(ffn, SwiGLU):
+                down_prepares = product(dtype, rows, ffn.down_proj.out_features, ffn.down_proj.in_features,
+                                        follow=True).prepares_norm
             if isinstance(mixer, Attention):
                 qkv = mixer.qkv_proj
                 lines.append(f"    qkv      {product(dtype, rows, qkv.out_features, qkv.in_features, norm='add_norm')}")
+                if down_prepares:
+                    behind = product(dtype, rows, qkv.out_features, qkv.in_features, norm='prepared')
+                    lines.append(f"             behind a layer whose down product prepared the norm: {behind}")
                 decode = attention(dtype, num_heads=mixer.num_heads, num_kv_heads=mixer.num_kv_heads,
                                    head_dim=mixer.head_dim, page_size=page_size, new_tokens=[1] * rows,
                                    max_context=context, prompt_kernel=mixer.prompt_kernel, sms=sms)
@@ -215,14 +236,16 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                                         max_context=context, prompt_kernel=mixer.prompt_kernel, sms=sms)
                     lines.append(f"             one portion: {portion}")
                 o = mixer.o_proj
-                lines.append(f"    o        {product(dtype, rows, o.out_features, o.in_features)}")
+                o_plan = product(dtype, rows, o.out_features, o.in_features, follow=True)
+                lines.append(f"    o        {o_plan}")
             else:
                 lines.append(f"    mixer    '{mixer.kind}' (its own code)")
             if isinstance(ffn, SwiGLU):
                 gu, down = ffn.gate_up_proj, ffn.down_proj
                 epilogue = SWIGLU if ffn.interleaved else BF16
-                lines.append(f"    gate/up  {product(dtype, rows, gu.out_features, gu.in_features, epilogue=epilogue, norm='add_norm')}")
-                lines.append(f"    down     {product(dtype, rows, down.out_features, down.in_features)}")
+                prepared = isinstance(mixer, Attention) and o_plan.prepares_norm
+                lines.append(f"    gate/up  {product(dtype, rows, gu.out_features, gu.in_features, epilogue=epilogue, norm='prepared' if prepared else 'add_norm')}")
+                lines.append(f"    down     {product(dtype, rows, down.out_features, down.in_features, follow=True)}")
             else:
                 lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
     proj = getattr(model.head, "proj", None)

@@ -47,6 +47,18 @@ def test_products_of_the_1b_sizes():
         assert plan.product(BF, rows, hidden, inter) == plan.ProductPlan(kernel, False, "bf16")
         assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="add_norm") == \
             plan.ProductPlan(kernel, True, "f32")
+    for rows in (1, 8, 16):
+        # a product in front of an addition and a norm of its own width does that norm's work; the product behind
+        # takes the prepared rows
+        assert plan.product(BF, rows, hidden, hidden, follow=True) == \
+            plan.ProductPlan("decode_linear", False, "bf16", prepares_norm=True)
+        assert plan.product(BF, rows, hidden, inter, follow=True).prepares_norm
+        assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu", norm="prepared") == \
+            plan.ProductPlan("decode_linear", True, "swiglu")
+        assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="prepared") == \
+            plan.ProductPlan("decode_linear", True, "f32")
+    assert not plan.product(BF, 17, hidden, hidden, follow=True).prepares_norm
+    assert not plan.product(F32, 8, hidden, hidden, follow=True).prepares_norm
     for rows in (17, 64, 2048):
         assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan("library", False, "bf16")
         assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu") == plan.ProductPlan("gemm_tcgen05", False, "swiglu")

@@ -557,6 +557,56 @@ def test_decode_linear_fused_norm_and_swiglu(m, n, k, eps):
     torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("m, inner, hidden, wide, eps", [(8, 2048, 2048, 3072, 1e-5), (3, 96, 160, 64, 1e-6),
+                                                         (13, 320, 512, 1024, 1e-5), (1, 8192, 2048, 16384, 1e-5),
+                                                         (16, 64, 5024, 48, 1e-3)])
+def test_decode_linear_prepares_the_following_norm(m, inner, hidden, wide, eps):
+    """A product that also does the work of the norm behind it (new residual, rows times the norm's weights, sums
+    of squares per tile), and the product behind that, which applies the norm's scale to its 32-bit sums: together
+    add + RMSNorm + product, with one rounding of the operand as in the reference's order, placed before the scale
+    instead of after it."""
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m + inner + hidden)
+    bf = torch.bfloat16
+    x = torch.randn(m, inner).to(bf)
+    w_first = (torch.randn(hidden, inner) / math.sqrt(inner)).to(bf)
+    res = (torch.randn(m, hidden) * 2).to(bf)
+    nw = 1 + 0.1 * torch.randn(hidden)
+    w_second = (torch.randn(wide, hidden) / math.sqrt(hidden)).to(bf)
+    tiles = hidden // kernels.decode_linear_tile_features(hidden)
+    res_out = torch.zeros(m, hidden, dtype=bf, device="cuda")
+    rows = torch.zeros(m, hidden, dtype=bf, device="cuda")
+    sums = torch.full((tiles, kernels.SS_STRIDE), float("nan"), device="cuda")
+    res_dev = dev(res)
+    kernels.decode_linear(dev(w_first), None, x=dev(x), prepare=(res_dev, dev(nw), res_out, rows, sums))
+    o = (x.double() @ w_first.double().T).to(bf)                       # the product as it would be stored alone
+    c = res.double() + o.double()
+    close = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(res_out.cpu().double(), c, **close)
+    torch.testing.assert_close(rows.cpu().double(), c * nw.double(), **close)
+    assert torch.equal(res_dev.cpu(), res)                                  # the old residual is left alone
+    got_sums = sums.cpu().double()
+    assert torch.isfinite(got_sums).all() and (got_sums[:, m:] == 0).all()   # rows beyond M hold zeros
+    torch.testing.assert_close(got_sums[:, :m].sum(0), (c * c).sum(1), rtol=2e-2, atol=1e-3)
+    # the product behind: scale from the sums, operand as prepared
+    out = torch.empty(m, wide, dtype=torch.float32, device="cuda")
+    kernels.decode_linear(dev(w_second), out, x=rows, scaled_by=sums, eps=eps, epilogue=kernels.EPI_F32)
+    exact_c = res_out.cpu().double()        # what the kernel itself rounded: its statistics come from the unrounded c
+    s = torch.rsqrt(got_sums[:, :m].sum(0) / hidden + eps)[:, None]
+    torch.testing.assert_close(out.cpu().double(), (rows.cpu().double() @ w_second.double().T) * s, rtol=1e-4, atol=1e-4)
+    reference = llama.rms_norm(c, nw.double(), eps).to(bf).double() @ w_second.double().T
+    torch.testing.assert_close(out.cpu().double(), reference, **close)
+    if wide % 16 == 0 and (wide // 2) % 8 == 0:
+        act = torch.empty(m, wide // 2, dtype=bf, device="cuda")
+        kernels.decode_linear(dev(w_second), act, x=rows, scaled_by=sums, eps=eps, epilogue=kernels.EPI_SWIGLU)
+        y = out.cpu().double().view(m, wide // 16, 2, 8)
+        g, u = y[:, :, 0].reshape(m, wide // 2), y[:, :, 1].reshape(m, wide // 2)
+        torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, **close)
+    with pytest.raises(kernels.KernelError):       # the new residual needs a buffer of its own
+        kernels.decode_linear(dev(w_first), None, x=dev(x), prepare=(res_dev, dev(nw), res_dev, rows, sums))
+
+
 def test_decode_linear_refuses_other_sizes():
     from tesseract_b200 import kernels
 
