@@ -160,8 +160,8 @@ def run_ours(args):
     scratch = tempfile.TemporaryDirectory(prefix="tesseract_bench_")
     write_random_model(scratch.name, cfg, seed=0)
     max_batch = max(args.batch, 64)
-    decode_capacity = REPEATS_DECODE * max_batch * (PROMPT_TOKENS + 320)     # every window's requests at once
-    llm = LLM(scratch.name, dtype="bfloat16", max_running=REPEATS_DECODE * max_batch, max_batch_tokens=4096,
+    decode_capacity = args.repeats * max_batch * (PROMPT_TOKENS + 320)     # every window's requests at once
+    llm = LLM(scratch.name, dtype="bfloat16", max_running=args.repeats * max_batch, max_batch_tokens=4096,
               prefill_chunk_tokens=PROMPT_TOKENS, kv_capacity_tokens=max(decode_capacity, max_batch * CONTEXT),
               page_size=PAGE_SIZE,
               max_sequence_length=CONTEXT, cuda_graphs=not args.no_graphs)
@@ -238,7 +238,8 @@ def run_ours(args):
                "ms_4x512": portions_ms, "value_4x512": PROMPT_TOKENS / (portions_ms / 1e3)}
 
     # ---------------------------------------------------------------- decode on the device clock
-    def decode_device(batch, steps, warmup, repeats=REPEATS_DECODE):
+    def decode_device(batch, steps, warmup, repeats=None):
+        repeats = repeats or args.repeats
         greedy, ones = [0.0] * batch, [1.0] * batch
         # Every window decodes the same stretch (positions 2,048 + warmup .. + steps) with `batch` requests of its
         # own; all their 2,048-token prompts are cached before the first window, so that no prefill runs between
@@ -344,7 +345,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "ms_per_step_min": step_times[0], "ms_per_step_max": step_times[-1],
-        "repeats": REPEATS_DECODE, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "repeats": args.repeats, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
         "config": {"model": SIZE_NAMES[args.size], "layers": layers, "layers_of_model": model["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
@@ -630,6 +631,9 @@ def main():
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     parser.add_argument("--no-graphs", action="store_true", help="decode without CUDA-graph replay")
+    parser.add_argument("--repeats", type=int, default=REPEATS_DECODE,
+                        help="how often the window of --steps decode steps is timed (the median counts); 1 keeps a "
+                             "profiling run short")
     parser.add_argument("--workload", choices=["3b", "8b"], default=None,
                         help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
                              "or a 2,048-token portion beside 64 decode rows at the 8B sizes")

@@ -37,7 +37,7 @@ constexpr int kThreads = kWarps * 32;
 // One CTA per SM (the prologue, which every CTA repeats, then costs each SM once) with rings deep enough for it
 // to cover the memory latency alone: five stages of 32-feature tiles or six of 16-feature tiles per warp.
 
-enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2, PRO_SCALED = 3 };
+enum Prologue : int { PRO_NONE = 0, PRO_NORM = 1, PRO_ADD_NORM = 2, PRO_SCALED = 3, PRO_SCALED_RESIDENT = 4 };
 enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2, EPI_ADD_NORM = 3 };
 constexpr int kSsStride = 16;      // floats per tile in the sums-of-squares array (rows beyond M hold zeros)
 
@@ -62,6 +62,10 @@ struct LinearParams {
     __nv_bfloat16* epi_res_out;
     __nv_bfloat16* epi_xw;
     float* epi_ss;
+    // EPI_F32 (or null): this CTA's best value and its lowest column per row, [gridDim.x][kSsStride] each: the first
+    // stage of a two-stage argmax over the output columns (src/cuda/kernels.rs:803-873)
+    float* best_value;
+    int* best_index;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -114,15 +118,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     constexpr int ROWS = 8 * MT;
-    constexpr bool kRowsRide = PRO == PRO_NONE || PRO == PRO_SCALED;   // the input rows ride in the ring beside the weights
+    // The input rows either ride in the ring beside the weights, block by block (read from L2 once per tile: right
+    // for a CTA with a tile or two), or lie in shared memory for all tiles (a norm in front puts them there anyway;
+    // PRO_SCALED_RESIDENT copies them there: right for a CTA with many tiles, the head has 27).
+    constexpr bool kRowsRide = PRO == PRO_NONE || PRO == PRO_SCALED;
     constexpr bool kNormInFront = PRO == PRO_NORM || PRO == PRO_ADD_NORM;
+    constexpr bool kRowsResident = kNormInFront || PRO == PRO_SCALED_RESIDENT;
+    constexpr bool kScaled = PRO == PRO_SCALED || PRO == PRO_SCALED_RESIDENT;
     __shared__ float scale_s[16];          // PRO_SCALED: the rows' reciprocal root mean squares
     __shared__ float tile_ss[kWarps][16];  // EPI_ADD_NORM: the warps' sums of squares of a tile
 
     // shared memory: [ROWS][K + 32] bf16 normalised activations (PRO only), the warps' partial sums, the rings
     const int x_pitch = K + 32;  // 64 bytes of padding: the eight rows a quarter-warp reads hit distinct banks
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
-    float* partial = reinterpret_cast<float*>(smem + (kNormInFront ? (size_t)ROWS * x_pitch * 2 : 0));
+    float* partial = reinterpret_cast<float*>(smem + (kRowsResident ? (size_t)ROWS * x_pitch * 2 : 0));
 
     // K is cut into 32-wide blocks; warp w takes blocks w, w + 16, ... of every tile (fixed by K alone).  A tile
     // is 32 output features (two 16-row operands that share the activation fragments).  A CTA walks over several
@@ -136,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
     const int bpw = (blocks + kWarps - 1) / kWarps;              // blocks per warp and tile
     const int num_tiles = p.N / TF;
     const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    unsigned char* ring = smem + (kNormInFront ? (size_t)ROWS * x_pitch * 2 : 0) +
+    unsigned char* ring = smem + (kRowsResident ? (size_t)ROWS * x_pitch * 2 : 0) +
                           (size_t)kWarps * TF * ROWS * sizeof(float) + (size_t)warp * STAGES * STAGE_BYTES;
     const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
     const uint32_t lane_off = (uint32_t)(g * 64 + t * 16);
@@ -196,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
 #pragma unroll
     for (int q = 0; q < PRE; ++q) early[q] = issue(false);
     pdl_wait();                                      // from here on the previous kernel's results are visible
-    if (PRO == PRO_SCALED) {
+    if (kScaled) {
         // The rows' sums of squares that the product in front left, one value per tile of its features: every warp
         // sums the tiles w, w + 16, ... (two lanes a row, each every other one of them), in an order that depends
         // on the sizes alone; the first tile's epilogue, behind a block barrier, adds the sixteen warps' sums.
@@ -224,6 +233,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         }
     }
 
+    if (PRO == PRO_SCALED_RESIDENT) {
+        // the rows as they are, into shared memory once (rows beyond M as zeros)
+        for (int idx = threadIdx.x; idx < ROWS * (K / 8); idx += kThreads) {
+            const int row = idx / (K / 8), j = (idx - row * (K / 8)) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < p.M) v = *reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + j);
+            *reinterpret_cast<uint4*>(xs + (size_t)row * x_pitch + j) = v;
+        }
+        __syncthreads();
+    }
     if (kNormInFront) {
         // Every CTA normalises the (few) rows itself, all threads side by side along K; CTA 0 also stores the
         // new residual.  Two passes over the rows (the second one hits L1): sums of squares, then the scaling.
@@ -331,6 +350,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
         __syncthreads();
     }
 
+    float best_v = -INFINITY;      // EPI_F32: the best value this thread has stored for its row, and its column
+    int best_i = 0x7fffffff;
     int cs = 0;        // consumer ring slot
     for (int ti = 0; ti < my_tiles; ++ti) {
         // EPI_ADD_NORM: what this thread's item of the tile's epilogue adds to and multiplies with does not depend
@@ -355,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 for (int mt = 0; mt < MT; ++mt) {
                     uint4 xa;
                     const int row = mt * 8 + g;
-                    if (kNormInFront)
+                    if (kRowsResident)
                         xa = *reinterpret_cast<const uint4*>(xs + (size_t)row * x_pitch + b * 32 + 8 * t);
                     else if (row >= p.M)
                         xa = make_uint4(0, 0, 0, 0);
@@ -386,13 +407,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.0f;
             }
         __syncthreads();
-        if (PRO == PRO_SCALED && ti == 0 && threadIdx.x < 16) {
+        if (kScaled && ti == 0 && threadIdx.x < 16) {
             float total = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) total += tile_ss[w][threadIdx.x];
             scale_s[threadIdx.x] = 1.0f / sqrtf(total / (float)K + p.eps);
         }
-        if (PRO == PRO_SCALED && ti == 0) __syncthreads();
+        if (kScaled && ti == 0) __syncthreads();
         if (EPI == EPI_SWIGLU) {
             // of every 16 features the first eight are gates, the last eight the matching up projections
             for (int idx = threadIdx.x; idx < 8 * NH * ROWS; idx += kThreads) {
@@ -405,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     gate += partial[(size_t)w * TF * ROWS + gate_row * ROWS + m];
                     up += partial[(size_t)w * TF * ROWS + (gate_row + 8) * ROWS + m];
                 }
-                if (PRO == PRO_SCALED) {
+                if (kScaled) {
                     gate *= scale_s[m];
                     up *= scale_s[m];
                 }
@@ -428,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     sum0 += partial[(size_t)w * TF * ROWS + f * ROWS + m];
                     sum1 += partial[(size_t)w * TF * ROWS + (f + 1) * ROWS + m];
                 }
-                if (PRO == PRO_SCALED) {
+                if (kScaled) {
                     sum0 *= scale_s[m];
                     sum1 *= scale_s[m];
                 }
@@ -445,6 +466,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                     *reinterpret_cast<__nv_bfloat162*>(p.epi_xw + at) = __floats2bfloat162_rn(c0 * w2.x, c1 * w2.y);
                     ss = fmaf(c0, c0, c1 * c1);
                 } else if (EPI == EPI_F32) {
+                    // columns rise from tile to tile, so "greater" alone keeps the lowest column of equal values
+                    if (sum0 > best_v) { best_v = sum0; best_i = n0 + f; }
+                    if (sum1 > best_v) { best_v = sum1; best_i = n0 + f + 1; }
                     float* o = reinterpret_cast<float*>(p.out) + (int64_t)m * p.out_stride + n0 + f;
                     if ((uintptr_t)o % 8 == 0) {
                         *reinterpret_cast<float2*>(o) = make_float2(sum0, sum1);
@@ -477,6 +501,34 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Linear
                 for (int w = 0; w < kWarps; ++w) total += tile_ss[w][threadIdx.x];
             }
             p.epi_ss[(int64_t)tile * kSsStride + threadIdx.x] = total;    // rows beyond M (and beyond ROWS) hold zeros
+        }
+    }
+    if (EPI == EPI_F32 && p.best_value != nullptr) {
+        // this CTA's best per row: a row's items sit in lanes m, m + ROWS, ... of the warps that had items
+        auto take = [&](float v, int i) {
+            if (v > best_v || (v == best_v && i < best_i)) { best_v = v; best_i = i; }
+        };
+        if (ROWS == 8) take(__shfl_xor_sync(0xffffffffu, best_v, 8), __shfl_xor_sync(0xffffffffu, best_i, 8));
+        take(__shfl_xor_sync(0xffffffffu, best_v, 16), __shfl_xor_sync(0xffffffffu, best_i, 16));
+        float* best_vs = &tile_ss[0][0];                                   // [kWarps][16], free by now
+        int* best_is = reinterpret_cast<int*>(partial);                     // the partial sums are done with
+        if (lane < ROWS) {
+            best_vs[warp * 16 + lane] = best_v;
+            best_is[warp * 16 + lane] = best_i;
+        }
+        __syncthreads();
+        if (threadIdx.x < kSsStride) {
+            float v = -INFINITY;
+            int i = 0x7fffffff;
+            if ((int)threadIdx.x < ROWS) {
+                for (int w = 0; w < kWarps; ++w) {
+                    const float wv = best_vs[w * 16 + threadIdx.x];
+                    const int wi = best_is[w * 16 + threadIdx.x];
+                    if (wv > v || (wv == v && wi < i)) { v = wv; i = wi; }
+                }
+            }
+            p.best_value[(int64_t)blockIdx.x * kSsStride + threadIdx.x] = v;
+            p.best_index[(int64_t)blockIdx.x * kSsStride + threadIdx.x] = i;
         }
     }
 }
@@ -518,7 +570,7 @@ int stages_for(int rows8, bool prologue, int nh, int K) {
 template <int MT, int PRO, int EPI, int NH, int STAGES>
 int launch_ring(const LinearParams& p, cudaStream_t stream) {
     constexpr int TF = 16 * NH;
-    const size_t smem = smem_bytes(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM, NH, p.K, STAGES);
+    const size_t smem = smem_bytes(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM || PRO == PRO_SCALED_RESIDENT, NH, p.K, STAGES);
     auto kernel = decode_linear_kernel<MT, PRO, EPI, NH, STAGES>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -535,7 +587,7 @@ int launch_ring(const LinearParams& p, cudaStream_t stream) {
 
 template <int MT, int PRO, int EPI, int NH>
 int launch_tiles(const LinearParams& p, cudaStream_t stream) {
-    const int stages = stages_for(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM, NH, p.K);
+    const int stages = stages_for(MT, PRO == PRO_NORM || PRO == PRO_ADD_NORM || PRO == PRO_SCALED_RESIDENT, NH, p.K);
     if (stages == deep_stages(NH, MT)) return launch_ring<MT, PRO, EPI, NH, deep_stages(NH, MT)>(p, stream);
     if constexpr (MT > 1) {
         if (stages == kShallowStages) return launch_ring<MT, PRO, EPI, NH, kShallowStages>(p, stream);
@@ -566,6 +618,9 @@ int dispatch(const LinearParams& p, int prologue, int epilogue, cudaStream_t str
     TB_CASE(PRO_SCALED, EPI_BF16)
     TB_CASE(PRO_SCALED, EPI_F32)
     TB_CASE(PRO_SCALED, EPI_SWIGLU)
+    TB_CASE(PRO_SCALED_RESIDENT, EPI_BF16)
+    TB_CASE(PRO_SCALED_RESIDENT, EPI_F32)
+    TB_CASE(PRO_SCALED_RESIDENT, EPI_SWIGLU)
 #undef TB_CASE
     return TB_ERR_BAD_SIZE;
 }
@@ -582,16 +637,25 @@ TB_EXPORT int tb_decode_linear_supported(int M, int N, int K, int prologue) {
 // Features per tile for an output width (what EPI_ADD_NORM's sums of squares are counted in).
 TB_EXPORT int tb_decode_linear_tile_features(int N) { return wide_tiles(N) ? 32 : 16; }
 
+// CTAs that a product of this output width is launched with (what EPI_F32's per-CTA best values are counted in).
+TB_EXPORT int tb_decode_linear_ctas(int N) {
+    const int tiles = N / tb_decode_linear_tile_features(N);
+    return tiles < sm_count() ? tiles : sm_count();
+}
+
 // x: PRO_NONE and PRO_SCALED (the rows as they are).  res/upd/norm_w/res_out: see LinearParams.  out_stride in
 // elements of the output type.
 // PRO_SCALED: ss_in [ss_tiles][16] sums of squares that an EPI_ADD_NORM call left; the scale uses eps.
 // EPI_ADD_NORM (with PRO_NONE): epi_res [M, N] residual, epi_norm_w [N], and the outputs epi_res_out [M, N],
 //   epi_xw [M, N], epi_ss [N / tb_decode_linear_tile_features(N)][16]; `out` is not written.
+// EPI_F32 with best_value / best_index [tb_decode_linear_ctas(N)][16] (or null): each CTA's best output value per
+//   row and its lowest column.
 TB_EXPORT int tb_decode_linear_ex(const void* x, int64_t x_stride, const void* res, const void* upd,
                                   const float* norm_w, float eps, void* res_out, const void* w, void* out,
                                   int64_t out_stride, int M, int N, int K, int prologue, int epilogue,
                                   const float* ss_in, int ss_tiles, const void* epi_res, const float* epi_norm_w,
-                                  void* epi_res_out, void* epi_xw, float* epi_ss, cudaStream_t stream) {
+                                  void* epi_res_out, void* epi_xw, float* epi_ss, float* best_value, int* best_index,
+                                  cudaStream_t stream) {
     if (!tb_decode_linear_supported(M, N, K, prologue)) return TB_ERR_BAD_SIZE;
     const uintptr_t bits = (uintptr_t)x | (uintptr_t)res | (uintptr_t)upd | (uintptr_t)res_out | (uintptr_t)w |
                            (uintptr_t)epi_res | (uintptr_t)epi_res_out | (uintptr_t)epi_xw;
@@ -624,6 +688,16 @@ TB_EXPORT int tb_decode_linear_ex(const void* x, int64_t x_stride, const void* r
     p.epi_res_out = (__nv_bfloat16*)epi_res_out;
     p.epi_xw = (__nv_bfloat16*)epi_xw;
     p.epi_ss = epi_ss;
+    p.best_value = epilogue == EPI_F32 && best_index != nullptr ? best_value : nullptr;
+    p.best_index = best_index;
+    if (prologue == PRO_SCALED) {
+        // a CTA with three tiles or more keeps the rows in shared memory instead of reading them again per tile
+        const int tf = tb_decode_linear_tile_features(N);
+        const int ctas = tb_decode_linear_ctas(N);
+        if ((N / tf + ctas - 1) / ctas >= 3 && K % 8 == 0 && x_stride % 8 == 0 &&
+            stages_for(M <= 8 ? 1 : 2, true, tf / 16, K) != 0)
+            prologue = PRO_SCALED_RESIDENT;
+    }
     return M <= 8 ? dispatch<1>(p, prologue, epilogue, stream) : dispatch<2>(p, prologue, epilogue, stream);
 }
 
@@ -633,5 +707,5 @@ TB_EXPORT int tb_decode_linear(const void* x, int64_t x_stride, const void* res,
                                cudaStream_t stream) {
     if (prologue == PRO_SCALED || epilogue == EPI_ADD_NORM) return TB_ERR_BAD_SIZE;
     return tb_decode_linear_ex(x, x_stride, res, upd, norm_w, eps, res_out, w, out, out_stride, M, N, K, prologue,
-                               epilogue, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, stream);
+                               epilogue, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, stream);
 }

@@ -20,6 +20,7 @@ namespace {
 
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
+constexpr int kPartStride = 16;     // rows per CTA in the partial results that a product leaves (at most 16 rows)
 
 struct MaxIdx {
     float v;
@@ -153,7 +154,8 @@ argmax_kernel(const float* __restrict__ logits, int64_t stride, int* __restrict_
 
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t stride, const float* __restrict__ temperature,
-              const double* __restrict__ uniform, int* __restrict__ out, int vocab, int chunk) {
+              const double* __restrict__ uniform, int* __restrict__ out, const float* __restrict__ part_value,
+              const int* __restrict__ part_index, int parts, int vocab, int chunk) {
     __shared__ MaxIdx scratch[kWarps];
     __shared__ double warp_total[kWarps];
     __shared__ double warp_base[kWarps];
@@ -168,11 +170,30 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, const float* __r
     const int first = min(vocab, block * chunk), last = min(vocab, first + chunk);
     const float* row = logits + (int64_t)r * stride;
     const float temp = temperature[r];
-    MaxIdx best = cluster_argmax(block_argmax(row + first, last - first, scratch, first), blocks, &x_value, &x_index);
+    MaxIdx best;
+    if (part_value != nullptr) {
+        // The product that wrote the logits also left each of its CTAs' best token of the row (the reference's
+        // two-stage argmax, src/cuda/kernels.rs:803-873): the row's best is the best of those, and the logits need
+        // not be read for it.  Every block works it out for itself; nothing is exchanged.
+        MaxIdx mine{-INFINITY, 0x7fffffff};
+        if (threadIdx.x < 32) {
+            for (int c = threadIdx.x; c < parts; c += 32)
+                mine = better(mine, MaxIdx{part_value[c * kPartStride + r], part_index[c * kPartStride + r]});
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                mine = better(mine, MaxIdx{__shfl_xor_sync(0xffffffffu, mine.v, o), __shfl_xor_sync(0xffffffffu, mine.i, o)});
+            if (threadIdx.x == 0) scratch[0] = mine;
+        }
+        __syncthreads();
+        best = scratch[0];
+        __syncthreads();
+    } else {
+        best = cluster_argmax(block_argmax(row + first, last - first, scratch, first), blocks, &x_value, &x_index);
+    }
     if (best.i == 0x7fffffff) best.i = 0;
     if (!(temp > 0.0f)) {
         if (block == 0 && threadIdx.x == 0) out[r] = best.i;
-        if (blocks > 1) cluster_sync();
+        if (blocks > 1 && part_value == nullptr) cluster_sync();   // (with partial results no peer reads this block)
         return;
     }
     const float inv_t = 1.0f / temp;
@@ -299,9 +320,15 @@ TB_EXPORT int tb_argmax(const float* logits, int64_t stride, int* out, int rows,
     return launch_rows(argmax_kernel, rows, vocab, stream, logits, stride, out);
 }
 
+// part_value / part_index (or null): [parts][16] per-CTA best value and token of each of at most 16 rows, left by
+// the product that wrote the logits; with them a greedy row is decided without reading its logits and a sampled
+// row skips the pass that finds its maximum.
 TB_EXPORT int tb_sample(const float* logits, int64_t stride, const float* temperature, const double* uniform,
-                        int* out, int rows, int vocab, cudaStream_t stream) {
+                        int* out, int rows, int vocab, const float* part_value, const int* part_index, int parts,
+                        cudaStream_t stream) {
     if (rows == 0) return 0;
     if (vocab <= 0 || rows > 65535) return TB_ERR_BAD_SIZE;
-    return launch_rows(sample_kernel, rows, vocab, stream, logits, stride, temperature, uniform, out);
+    if (part_value != nullptr && (part_index == nullptr || parts < 1 || rows > kPartStride)) return TB_ERR_BAD_SIZE;
+    return launch_rows(sample_kernel, rows, vocab, stream, logits, stride, temperature, uniform, out, part_value,
+                       part_index, parts);
 }

@@ -118,7 +118,9 @@ class _Graph:
         # sampler output, which never leaves the device
         kernels.select_tokens(self.d["tokens"], self.d["feed"], self.sampled, self.tokens, stepper.vocab_size)
         logits = stepper.model.forward(self.ctx, stepper.cache.bindings, self.want_rows, want_every_row=True)
-        kernels.sample(logits, self.d["temps"], self.d["uniform"], self.sampled[:self.batch])
+        # the head may have left each of its CTAs' best token per row: the sampler's second stage of the argmax
+        partials = getattr(stepper.model.head, "argmax_partials", lambda: None)()
+        kernels.sample(logits, self.d["temps"], self.d["uniform"], self.sampled[:self.batch], partials=partials)
         return logits
 
     def _capture(self, stepper: Stepper) -> None:

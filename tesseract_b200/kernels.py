@@ -83,6 +83,8 @@ def _cuda(*tensors: torch.Tensor) -> None:
             raise KernelError("kernel arguments must live on a CUDA device")
 
 
+SS_STRIDE = 16      # rows per tile / per CTA in the small side arrays that one kernel leaves for the next
+
 _i32 = ctypes.c_int
 _i64 = ctypes.c_int64
 _f32 = ctypes.c_float
@@ -242,17 +244,31 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """Per row: argmax if ``temperature <= 0`` else inverse-CDF sampling with the given uniform draw."""
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor,
+           partials: Optional[tuple] = None) -> torch.Tensor:
+    """Per row: argmax if ``temperature <= 0`` else inverse-CDF sampling with the given uniform draw.
+    ``partials=(values, indices)``: float32 / int32 ``[parts, 16]``, the best value and token of every row that each
+    CTA of the product that wrote ``logits`` left (``decode_linear(..., best=...)``): a greedy row is then decided
+    from those alone and a sampled row skips the pass over its logits that finds the maximum."""
     _cuda(logits, temperature, uniform, out)
     rows = logits.shape[0]
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 with contiguous rows")
     _need(temperature.dtype == torch.float32 and temperature.numel() >= rows, "temperature must be float32 [S]")
     _need(uniform.dtype == torch.float64 and uniform.numel() >= rows, "uniform must be float64 [S]")
     _need(out.dtype == torch.int32 and out.numel() >= rows and out.is_contiguous(), "sample out")
+    values = indices = None
+    parts = 0
+    if partials is not None:
+        values, indices = partials
+        _cuda(values, indices)
+        _need(values.dtype == torch.float32 and indices.dtype == torch.int32 and values.shape == indices.shape
+              and values.dim() == 2 and values.shape[1] == SS_STRIDE and values.is_contiguous()
+              and indices.is_contiguous() and rows <= SS_STRIDE, "sample partial results")
+        parts = values.shape[0]
     lib = load_library("sampling")
     _check(lib.tb_sample(_ptr(logits), _i64(logits.stride(0)), _ptr(temperature), _ptr(uniform), _ptr(out),
-                         _i32(rows), _i32(logits.shape[1]), _stream()), "sample")
+                         _i32(rows), _i32(logits.shape[1]), _ptr(values), _ptr(indices), _i32(parts), _stream()),
+           "sample")
     return out
 
 
@@ -412,7 +428,6 @@ def decode_linear_supported(rows: int, out_features: int, in_features: int, prol
 
 EPI_ADD_NORM = 3
 PRO_SCALED = 3
-SS_STRIDE = 16      # floats per tile in the sums-of-squares array that one product leaves for the next
 
 
 def decode_linear_tile_features(out_features: int) -> int:
@@ -420,11 +435,17 @@ def decode_linear_tile_features(out_features: int) -> int:
     return int(load_library("decode_linear").tb_decode_linear_tile_features(_i32(out_features)))
 
 
+def decode_linear_ctas(out_features: int) -> int:
+    """CTAs that the skinny decode product of this output width is launched with."""
+    return int(load_library("decode_linear").tb_decode_linear_ctas(_i32(out_features)))
+
+
 def decode_linear(weight: torch.Tensor, out: Optional[torch.Tensor], *, x: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, update: Optional[torch.Tensor] = None,
                   norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                   residual_out: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
-                  scaled_by: Optional[torch.Tensor] = None, prepare: Optional[tuple] = None) -> Optional[torch.Tensor]:
+                  scaled_by: Optional[torch.Tensor] = None, prepare: Optional[tuple] = None,
+                  best: Optional[tuple] = None) -> Optional[torch.Tensor]:
     """``out = X @ weight^T`` for at most 16 rows (bfloat16 weights, 32-bit accumulation).
 
     ``X`` is ``x``, or ``rms_norm(residual)`` (``norm_weight`` given), or ``rms_norm(residual + update)``
@@ -439,6 +460,9 @@ def decode_linear(weight: torch.Tensor, out: Optional[torch.Tensor], *, x: Optio
     ``sums`` (float32 ``[N / decode_linear_tile_features(N), 16]``).  ``scaled_by=sums`` (with ``x`` = such
     ``scaled_rows`` and ``eps``): ``out = rsqrt(sum(sums) / K + eps) * (x @ weight^T)``, row by row: together the
     norm's scale meets the 32-bit sums of the product behind it.
+
+    ``best=(values, indices)`` (with ``EPI_F32``; float32 / int32 ``[decode_linear_ctas(N), 16]``): every CTA also
+    leaves its best output value of each row and that value's lowest column: the first stage of a two-stage argmax.
     """
     _cuda(weight, out, x, residual, update, norm_weight, residual_out, scaled_by)
     n, k = weight.shape
@@ -483,12 +507,22 @@ def decode_linear(weight: torch.Tensor, out: Optional[torch.Tensor], *, x: Optio
         width = n // 2 if epilogue == EPI_SWIGLU else n
         _need(out is not None and out.shape == (m, width) and out.stride(1) == 1, "decode_linear out shape")
         _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "decode_linear out dtype")
+    best_values = best_indices = None
+    if best is not None:
+        best_values, best_indices = best
+        _cuda(best_values, best_indices)
+        shape = (decode_linear_ctas(n), SS_STRIDE)
+        _need(epilogue == EPI_F32 and best_values.dtype == torch.float32 and best_indices.dtype == torch.int32
+              and tuple(best_values.shape) == shape and tuple(best_indices.shape) == shape
+              and best_values.is_contiguous() and best_indices.is_contiguous(),
+              f"decode_linear best values and indices must be float32 / int32 {list(shape)} (32-bit output only)")
     lib = load_library("decode_linear")
     _check(lib.tb_decode_linear_ex(_ptr(x), _i64(x.stride(0) if x is not None else 0), _ptr(residual), _ptr(update),
                                    _ptr(norm_weight), _f32(eps), _ptr(residual_out), _ptr(weight), _ptr(out),
                                    _i64(out.stride(0) if out is not None else 0), _i32(m), _i32(n), _i32(k),
                                    _i32(prologue), _i32(epilogue), _ptr(ss_in), _i32(ss_tiles), _ptr(epi[0]),
-                                   _ptr(epi[1]), _ptr(epi[2]), _ptr(epi[3]), _ptr(epi[4]), _stream()), "decode_linear")
+                                   _ptr(epi[1]), _ptr(epi[2]), _ptr(epi[3]), _ptr(epi[4]), _ptr(best_values),
+                                   _ptr(best_indices), _stream()), "decode_linear")
     return out
 
 

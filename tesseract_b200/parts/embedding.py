@@ -15,7 +15,7 @@ from .. import kernels
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
 from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime
-from .linear import Linear
+from .linear import BestOfRows, Linear
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -52,6 +52,9 @@ class LMHead(Head):
         self.vocab_size = int(spec.params["vocab_size"])
         self.hidden_size = int(spec.params["hidden_size"])
         self.proj = Linear(tensors["weight"], runtime)     # the embedding's device copy if both name one tensor
+        # per-CTA best logit of each row, left by the product when it is the weight-streaming kernel (at most 16
+        # rows): the sampler then need not read the logits again to find a row's best token
+        self.best = BestOfRows(runtime.device) if not runtime.is_float32 else None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -63,9 +66,15 @@ class LMHead(Head):
     def forward(self, x, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         from .base import DeferredNorm
 
+        if self.best is not None:
+            self.best.valid = False
         if isinstance(x, DeferredNorm):
-            logits = self.proj.forward_normed(x, float32_out=True)
+            logits = self.proj.forward_normed(x, float32_out=True, best=self.best)
             if logits is not None:
                 return logits
             x = x.materialize()
-        return self.proj.forward(x, out=out, float32_out=True)
+        return self.proj.forward(x, out=out, float32_out=True, best=self.best)
+
+    def argmax_partials(self):
+        """``(values, indices)`` that the last ``forward`` left for the sampler, or None if it left none."""
+        return self.best.buffers if self.best is not None and self.best.valid else None

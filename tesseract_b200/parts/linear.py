@@ -17,6 +17,24 @@ from .. import kernels, plan
 from .base import Runtime
 
 
+class BestOfRows:
+    """Where a 32-bit product leaves, per CTA, its best output value of each row and that value's lowest column (the
+    first stage of a two-stage argmax; the sampler is the second).  The buffers are made once and kept (a captured
+    graph holds their addresses); ``valid`` says whether the product that ran last filled them."""
+
+    def __init__(self, device):
+        self.device = device
+        self.buffers = None
+        self.valid = False
+
+    def take(self, out_features: int) -> None:
+        shape = (kernels.decode_linear_ctas(out_features), kernels.SS_STRIDE)
+        if self.buffers is None or tuple(self.buffers[0].shape) != shape:
+            self.buffers = (torch.empty(shape, dtype=torch.float32, device=self.device),
+                            torch.empty(shape, dtype=torch.int32, device=self.device))
+        self.valid = True
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, runtime: Runtime):
         self.runtime = runtime
@@ -34,7 +52,7 @@ class Linear:
         return torch.empty((rows, width), dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, float32_out: bool = False,
-                epilogue: Optional[str] = None, follow=None):
+                epilogue: Optional[str] = None, follow=None, best=None):
         """``x @ W^T``; with ``epilogue="swiglu"`` the activated product ``[rows, out / 2]`` if the plan has a kernel
         that folds the activation in, else ``None`` (the caller then activates the plain product itself).  With
         ``follow`` (a :class:`FollowNorm`) the product may do the work of the norm behind it and return a
@@ -62,7 +80,10 @@ class Linear:
         if choice.kernel == "gemm_f32":
             return kernels.gemm_f32_nt(x, self.weight, out)
         if choice.kernel == "decode_linear":
-            return kernels.decode_linear(self.weight, out, x=x, epilogue=choice.epilogue_code)
+            if best is not None and choice.epilogue == plan.F32:
+                best.take(self.out_features)
+            return kernels.decode_linear(self.weight, out, x=x, epilogue=choice.epilogue_code,
+                                         best=best.buffers if best is not None and best.valid else None)
         return kernels.gemm_tcgen05(x, self.weight, out, epilogue=choice.epilogue_code)
 
     def _prepare(self, x: torch.Tensor, follow):
@@ -87,7 +108,8 @@ class Linear:
         kernels.decode_linear(self.weight, None, x=x, prepare=(residual, weight, new_residual, scaled_rows, sums))
         return PreparedNorm(follow.norm, new_residual, scaled_rows, sums)
 
-    def forward_normed(self, deferred, float32_out: bool = False, epilogue: Optional[str] = None) -> torch.Tensor:
+    def forward_normed(self, deferred, float32_out: bool = False, epilogue: Optional[str] = None,
+                       best=None) -> torch.Tensor:
         """``norm(residual [+ update]) @ W^T`` with the norm folded into the product's kernel, or ``None`` when the
         plan has no such kernel for these sizes or the norm does not offer its parameters for folding
         (``rms_parameters()``): the caller then lets the norm run on its own."""
@@ -105,8 +127,11 @@ class Linear:
                 return None
             _, eps = parameters()
             out = self._out(deferred.rows, choice, deferred.residual.device)
+            if best is not None and choice.epilogue == plan.F32:
+                best.take(self.out_features)
             kernels.decode_linear(self.weight, out, x=deferred.scaled_rows, scaled_by=deferred.sums, eps=eps,
-                                  epilogue=choice.epilogue_code)
+                                  epilogue=choice.epilogue_code,
+                                  best=best.buffers if best is not None and best.valid else None)
             deferred.fused(None)
             return out
         choice = self.plan(deferred.rows, wanted, norm="norm" if deferred.update is None else "add_norm")
@@ -115,7 +140,10 @@ class Linear:
         weight, eps = parameters()
         out = self._out(deferred.rows, choice, deferred.residual.device)
         new_residual = torch.empty_like(deferred.residual) if deferred.update is not None else None
+        if best is not None and choice.epilogue == plan.F32:
+            best.take(self.out_features)
         kernels.decode_linear(self.weight, out, residual=deferred.residual, update=deferred.update,
-                              norm_weight=weight, eps=eps, residual_out=new_residual, epilogue=choice.epilogue_code)
+                              norm_weight=weight, eps=eps, residual_out=new_residual, epilogue=choice.epilogue_code,
+                              best=best.buffers if best is not None and best.valid else None)
         deferred.fused(new_residual)
         return out

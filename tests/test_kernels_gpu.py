@@ -607,6 +607,40 @@ def test_decode_linear_prepares_the_following_norm(m, inner, hidden, wide, eps):
         kernels.decode_linear(dev(w_first), None, x=dev(x), prepare=(res_dev, dev(nw), res_dev, rows, sums))
 
 
+@pytest.mark.parametrize("m, n, k", [(8, 128256, 256), (3, 5024, 96), (16, 331 * 16, 64), (1, 48, 32)])
+def test_two_stage_argmax_through_the_product_and_the_sampler(m, n, k):
+    """The product that writes 32-bit logits leaves each CTA's best value per row and its lowest column; the
+    sampler takes a greedy row's token from those alone and a sampled row's maximum (so the same token as without
+    them); ties go to the lowest token wherever in the vocabulary they lie."""
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(n + m)
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
+    # two identical weight rows far apart (in different tiles and CTAs) that row 0 scores highest: a tie
+    tie_lo, tie_hi = 5, n - 3
+    w[tie_lo] = w[tie_hi] = (x[0].float() * 4 / x[0].float().norm()).to(torch.bfloat16)
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    shape = (kernels.decode_linear_ctas(n), kernels.SS_STRIDE)
+    values = torch.full(shape, float("nan"), device="cuda")
+    indices = torch.full(shape, -7, dtype=torch.int32, device="cuda")
+    kernels.decode_linear(dev(w), out, x=dev(x), epilogue=kernels.EPI_F32, best=(values, indices))
+    logits = out.cpu()
+    got_best = values.cpu()[:, :m].max(0).values
+    assert torch.equal(got_best, logits.max(1).values)
+    temperature = torch.tensor([0.0 if r % 2 == 0 else 0.7 for r in range(m)], device="cuda")
+    uniform = torch.tensor([0.1 + 0.8 * r / max(1, m - 1) for r in range(m)], dtype=torch.float64, device="cuda")
+    with_parts = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+    without = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+    kernels.sample(out, temperature, uniform, with_parts, partials=(values, indices))
+    kernels.sample(out, temperature, uniform, without)
+    assert torch.equal(with_parts, without)
+    assert int(with_parts[0]) == tie_lo and logits[0, tie_lo] == logits[0, tie_hi]
+    for r in range(0, m, 2):
+        row = logits[r]
+        assert int(with_parts[r]) == int((row == row.max()).nonzero()[0])
+
+
 def test_decode_linear_refuses_other_sizes():
     from tesseract_b200 import kernels
 
