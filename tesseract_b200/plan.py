@@ -59,14 +59,15 @@ class ProductPlan:
     residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
     ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product.
     ``prepares_norm``: the product also does the work of the norm BEHIND it (new residual, rows times the norm's
-    weights, sums of squares); the product behind that then runs with ``norm="prepared"``: it takes those rows as
-    they are and applies the scale to its 32-bit sums."""
+    weights, sums of squares); the product behind that then runs with ``norm="prepared"`` (``takes_prepared``): it
+    takes those rows as they are and applies the scale to its 32-bit sums."""
 
     kernel: str
     norm_folded: bool = False
     epilogue: str = BF16
     activation_apart: bool = False
     prepares_norm: bool = False
+    takes_prepared: bool = False
 
     @property
     def epilogue_code(self) -> int:
@@ -74,7 +75,9 @@ class ProductPlan:
 
     def __str__(self) -> str:
         extras = [f"{self.epilogue} store"]
-        if self.norm_folded:
+        if self.takes_prepared:
+            extras.insert(0, "rows prepared by the product in front, the norm's scale on the sums")
+        elif self.norm_folded:
             extras.insert(0, "add+norm folded in front")
         if self.activation_apart:
             extras.append("SwiGLU as a kernel of its own")
@@ -94,7 +97,7 @@ def product(dtype: torch.dtype, rows: int, out_features: int, in_features: int, 
     if rows <= DECODE_LINEAR_MAX_ROWS and contiguous_rows:
         if norm == "prepared":
             if _decode_linear_takes(rows, out_features, in_features, kernels.PRO_NONE):
-                return ProductPlan("decode_linear", True, epilogue)
+                return ProductPlan("decode_linear", True, epilogue, takes_prepared=True)
             return ProductPlan("library", False, BF16 if epilogue == SWIGLU else epilogue, activation_apart=epilogue == SWIGLU)
         if follow and norm is None and epilogue == BF16 and _decode_linear_takes(rows, out_features, in_features,
                                                                                 kernels.PRO_NONE):
@@ -252,5 +255,9 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
     if proj is not None:
         lines.append("head (wanted rows only)")
         for rows in row_counts:
-            lines.append(f"  {rows} rows  {product(dtype, rows, proj.out_features, proj.in_features, epilogue=F32, norm='add_norm')}")
+            text = f"  {rows} rows  {product(dtype, rows, proj.out_features, proj.in_features, epilogue=F32, norm='add_norm')}"
+            behind = product(dtype, rows, proj.out_features, proj.in_features, epilogue=F32, norm='prepared')
+            if behind.takes_prepared:
+                text += f"; on every row of a step: {behind}"
+            lines.append(text)
     return "\n".join(lines)

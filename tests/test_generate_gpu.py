@@ -142,6 +142,22 @@ def test_command_line_generates(model_folders):
     check_greedy(config, tensors, [5, 6, 7, 8], records[0]["token_ids"], GREEDY_MARGIN["float32"])
 
 
+def test_command_line_prints_the_kernel_plan(model_folders):
+    """``--print-plan`` says, for every distinct layer and the head, which kernel each operation takes at each row
+    count: the one answer every part then follows (the reference prints its plan too,
+    src/cuda/kernel_plan.rs:140-161)."""
+    folder = model_folders("b")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "tesseract"), "--model-path", folder, "--print-plan",
+           "--kv-capacity-tokens", "256", "--max-running", "2"]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr
+    text = done.stdout
+    assert "kernel plan for LlamaForCausalLM in bfloat16" in text and "layers 0..2 (3)" in text
+    for word in ("qkv", "attend", "gate/up", "down", "head", "decode_linear", "attention_decode", "library"):
+        assert word in text, word
+    assert "does the following add+norm's work" in text          # the small-batch products prepare the next norm
+
+
 @pytest.mark.parametrize("dtype, margin", sorted(GREEDY_MARGIN.items()))
 def test_graph_replay_decodes_like_the_eager_path(model_folders, dtype, margin):
     """Pure decode steps replayed as CUDA graphs (batch padded to a bucket) give the eager path's tokens."""

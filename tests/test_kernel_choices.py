@@ -54,9 +54,9 @@ def test_products_of_the_1b_sizes():
             plan.ProductPlan("decode_linear", False, "bf16", prepares_norm=True)
         assert plan.product(BF, rows, hidden, inter, follow=True).prepares_norm
         assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu", norm="prepared") == \
-            plan.ProductPlan("decode_linear", True, "swiglu")
+            plan.ProductPlan("decode_linear", True, "swiglu", takes_prepared=True)
         assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="prepared") == \
-            plan.ProductPlan("decode_linear", True, "f32")
+            plan.ProductPlan("decode_linear", True, "f32", takes_prepared=True)
     assert not plan.product(BF, 17, hidden, hidden, follow=True).prepares_norm
     assert not plan.product(F32, 8, hidden, hidden, follow=True).prepares_norm
     for rows in (17, 64, 2048):
