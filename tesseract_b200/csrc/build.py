@@ -32,7 +32,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 INCLUDES: Dict[str, List[str]] = {
     "attention_noalloc": ["attention_mma.cu", "attention_noalloc.h"],
     "attention_tcgen05": ["tma.cuh"],
-    "gemm_tcgen05": ["tma.cuh"],
+    "gemm_tcgen05": ["tma.cuh", "umma.cuh"],
 }
 
 # Every source file, with the extra flags it needs.
