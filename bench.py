@@ -568,6 +568,34 @@ def run_kernels(args):
         out_lines[f"decode_linear_m{m}_{name}"] = entry
         del ws
 
+    # 17 to 128 rows: the swapped-operand tcgen05 product against the library GEMM, plain, with SwiGLU (against the
+    # tcgen05 GEMM that carried it before) and as the product that does a norm's work (against product + norm kernel)
+    for rows in (32, 64, 128):
+        for name, n, k in (("qkv", 3072, 2048), ("o", 2048, 2048), ("gate_up", 16384, 2048), ("down", 2048, 8192)):
+            ws = [(torch.randn(n, k, device=dev) / math.sqrt(k)).to(torch.bfloat16) for _ in range(16)]
+            x = torch.randn(rows, k, device=dev).to(torch.bfloat16)
+            out = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+            mb = n * k * 2 / 1e6
+            entry = {"weight_mb": mb, "hbm_floor_us": mb / pk["hbm_gbs"] * 1e3,
+                     "library_us": timed([lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]),
+                     "skinny_us": timed([lambda w=w: kernels.skinny_tcgen05(x, w, out) for w in ws])}
+            if name == "gate_up":
+                act = torch.empty(rows, n // 2, device=dev, dtype=torch.bfloat16)
+                entry["gemm_tcgen05_swiglu_us"] = timed(
+                    [lambda w=w: kernels.gemm_tcgen05(x, w, act, epilogue=kernels.EPI_SWIGLU) for w in ws])
+                entry["skinny_swiglu_us"] = timed(
+                    [lambda w=w: kernels.skinny_tcgen05(x, w, act, epilogue=kernels.EPI_SWIGLU) for w in ws])
+            if name in ("o", "down"):
+                res, nw = torch.randn(rows, n, device=dev).to(torch.bfloat16), torch.ones(n, device=dev)
+                res_out, xw = torch.empty_like(res), torch.empty_like(res)
+                sums = torch.empty(kernels.skinny_tcgen05_sums_shape(n), device=dev)
+                entry["skinny_prepare_us"] = timed([lambda w=w: kernels.skinny_tcgen05(
+                    x, w, None, prepare=(res, nw, res_out, xw, sums)) for w in ws])
+                entry["library_then_add_norm_us"] = timed([lambda w=w: (
+                    torch.mm(x, w.t(), out=out), kernels.add_rms_norm(res, out, nw, 1e-5, xw, res_out)) for w in ws])
+            out_lines[f"skinny_m{rows}_{name}"] = entry
+            del ws
+
     nh, nkv, d, ps, ctx = 32, 8, 64, PAGE_SIZE, 2100
     for batch in (1, 8, 64):
         pages = -(-ctx // ps)

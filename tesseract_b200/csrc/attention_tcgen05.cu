@@ -96,6 +96,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
 }
+__device__ __forceinline__ void umma_add(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {   // D += A . B
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -317,38 +324,58 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0);
             constexpr uint32_t idesc_pv = idesc_bf16(BM, D, 1);
-            auto issue_qk = [&](int j) {
-                const int s = j % STAGES;
-                if (!mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag)) return false;
+            // One thread issues every product, and what it executes between two of them is time the tensor core
+            // idles (a 128 x 64 x 16 product takes 46 cycles; building two descriptors from addresses takes 100):
+            // the descriptors of stage 0 are built once and moved by adding to the start-address field (bytes >> 4;
+            // the field holds addresses below 256 KiB, so the sum never carries out of it).
+            const uint64_t q_desc = desc_sw128(q_tile, 1), p_desc = desc_sw128(p_tile, 1);
+            const uint64_t k_desc0 = desc_sw128(kv_tiles, 1);
+            const uint64_t v_desc0 = desc_sw128(kv_tiles + kKVTileBytes, kKVHalfBytes >> 4);
+            constexpr uint32_t kStageStep = (2 * kKVTileBytes) >> 4;          // a ring stage further, in the field's units
+            auto issue_qk = [&](int s, uint32_t parity) {
+                if (!mbar_wait(k_full + 8 * s, parity, &abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t k_tile = kv_tiles + s * 2 * kKVTileBytes;
+                const uint64_t k_desc = k_desc0 + (uint32_t)s * kStageStep;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    umma(tmem_s, desc_sw128(q_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
-                         desc_sw128(k_tile + (kk >> 2) * kKVHalfBytes + (kk & 3) * 32, 1), idesc_qk, kk != 0);
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t a = q_desc + (((kk >> 2) * kTileBytes + (kk & 3) * 32) >> 4);
+                    const uint64_t b = k_desc + (((kk >> 2) * kKVHalfBytes + (kk & 3) * 32) >> 4);
+                    if (kk == 0) umma(tmem_s, a, b, idesc_qk, 0);
+                    else umma_add(tmem_s, a, b, idesc_qk);
+                }
                 umma_commit(s_full);
                 umma_commit(k_empty + 8 * s);     // the key stage may be refilled once these products are done
                 return true;
             };
-            bool ok = issue_qk(0);
+            // ring cursors of the block whose scores are issued (qs, q_parity) and of the one whose P.V is (s, parity)
+            int qs = 0, s = 0;
+            uint32_t q_parity = 0, parity = 0;
+            auto next_q = [&]() { if (++qs == STAGES) { qs = 0; q_parity ^= 1; } };
+            bool ok = issue_qk(qs, q_parity);
+            next_q();
             for (int j = 0; j < n_blocks && ok; ++j) {
                 // as soon as the softmax warps hold S_j in registers the next block's scores may overwrite it
                 if (j + 1 < n_blocks) {
                     if (!mbar_wait(s_free, j & 1, &abort_flag)) { ok = false; break; }
-                    ok = issue_qk(j + 1);
+                    ok = issue_qk(qs, q_parity);
+                    next_q();
                     if (!ok) break;
                 }
                 // P_j is in shared memory (and O has been rescaled if the maximum jumped): O += P_j V_j
                 if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
-                if (!mbar_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(v_full + 8 * s, parity, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t v_tile = kv_tiles + (j % STAGES) * 2 * kKVTileBytes + kKVTileBytes;
+                const uint64_t v_desc = v_desc0 + (uint32_t)s * kStageStep;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    umma(tmem_o, desc_sw128(p_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32, 1),
-                         desc_sw128(v_tile + kk * 2048, kKVHalfBytes >> 4), idesc_pv, (j | kk) != 0);
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t a = p_desc + (((kk >> 2) * kTileBytes + (kk & 3) * 32) >> 4);
+                    const uint64_t b = v_desc + ((kk * 2048) >> 4);
+                    if (kk == 0) umma(tmem_o, a, b, idesc_pv, j != 0);
+                    else umma_add(tmem_o, a, b, idesc_pv);
+                }
                 umma_commit(o_full);
-                umma_commit(v_empty + 8 * (j % STAGES));
+                umma_commit(v_empty + 8 * s);
+                if (++s == STAGES) { s = 0; parity ^= 1; }
             }
             if (!ok) {
                 abort_flag = 1;

@@ -33,6 +33,7 @@ INCLUDES: Dict[str, List[str]] = {
     "attention_noalloc": ["attention_mma.cu", "attention_noalloc.h"],
     "attention_tcgen05": ["tma.cuh"],
     "gemm_tcgen05": ["tma.cuh", "umma.cuh"],
+    "skinny_tcgen05": ["tma.cuh", "umma.cuh"],
 }
 
 # Every source file, with the extra flags it needs.
@@ -47,6 +48,7 @@ SOURCES: Dict[str, List[str]] = {
     "gemm_f32": [],
     "decode_linear": [],
     "gemm_tcgen05": [],
+    "skinny_tcgen05": [],
     "sampling": [],
 }
 

@@ -139,12 +139,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
-        int g = 0;                                               // k blocks issued so far, over all tiles
+        int s = 0;
+        uint32_t parity = 1;                                     // fresh barriers pass a wait for parity 1
         for (int t = blockIdx.x; t < total_tiles && !abort_flag; t += gridDim.x) {
             const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-            for (int kb = 0; kb < k_blocks; ++kb, ++g) {
-                const int s = g % STAGES;
-                if (!mbar_wait(empty0 + 8 * s, ((g / STAGES) & 1) ^ 1, &abort_flag)) {   // fresh barriers pass parity 1
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(empty0 + 8 * s, parity, &abort_flag)) {
                     abort_flag = 1;
                     atomicExch(p.error, 1);
                     break;
@@ -153,12 +153,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const uint32_t a_dst = tiles + s * kStageBytes;
                 tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
                 tma_load_2d(a_dst + kATileBytes, &map_b, full0 + 8 * s, kb * BK, n0);
+                if (++s == STAGES) {
+                    s = 0;
+                    parity ^= 1;
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-        int g = 0, i = 0;
+        // the descriptors of stage 0; those of the other stages and K steps are sums (see umma_desc_advance)
+        const uint64_t desc_a0 = umma_desc_k_sw128(tiles), desc_b0 = umma_desc_k_sw128(tiles + kATileBytes);
+        int s = 0, i = 0;
+        uint32_t parity = 0;                                      // of the wait for a stage: flips with every turn of the ring
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
             const int buf = i & 1;
@@ -171,23 +178,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + buf * BN;
-            for (int kb = 0; kb < k_blocks; ++kb, ++g) {
-                const int s = g % STAGES;
-                if (!mbar_wait(full0 + 8 * s, (g / STAGES) & 1, &abort_flag)) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(full0 + 8 * s, parity, &abort_flag)) {
                     abort_flag = 1;
                     atomicExch(p.error, 2);
                     ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = tiles + s * kStageBytes, b_addr = a_addr + kATileBytes;
+                const uint64_t desc_a = umma_desc_advance(desc_a0, s * kStageBytes);
+                const uint64_t desc_b = umma_desc_advance(desc_b0, s * kStageBytes);
+                // inside the 128-byte swizzle atom a step of 16 elements along K is 32 bytes of start address
+                umma_bf16(acc, desc_a, desc_b, idesc, kb != 0);
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk) {
-                    // inside the 128-byte swizzle atom a step of 16 elements along K is 32 bytes of start address
-                    umma_bf16(acc, umma_desc_k_sw128(a_addr + kk * 32), umma_desc_k_sw128(b_addr + kk * 32), idesc,
-                              (kb | kk) != 0);
-                }
+                for (int kk = 1; kk < BK / 16; ++kk)
+                    umma_bf16_add(acc, umma_desc_advance(desc_a, kk * 32), umma_desc_advance(desc_b, kk * 32), idesc);
                 umma_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+                if (++s == STAGES) {
+                    s = 0;
+                    parity ^= 1;
+                }
             }
             if (ok) umma_commit(acc_full0 + 8 * buf); // the accumulator is complete once all products are done
         }

@@ -45,7 +45,7 @@ def _check(status: int, what: str) -> None:
 _LIBRARIES = {
     torch.float32: ("elementwise", "norm", "rope_cache", "attention_rows", "gemm_f32", "sampling"),
     torch.bfloat16: ("elementwise", "norm", "rope_cache", "attention_mma", "attention_tcgen05", "decode_linear",
-                     "gemm_tcgen05", "sampling"),
+                     "gemm_tcgen05", "skinny_tcgen05", "sampling"),
 }
 
 
@@ -560,6 +560,69 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     _check(lib.tb_gemm_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
                                _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
                                _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    return out
+
+
+SKINNY_MAX_ROWS = 128          # rows of the widest product that skinny_tcgen05 takes
+
+
+def skinny_tcgen05_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    return bool(load_library("skinny_tcgen05").tb_skinny_tcgen05_supported(_i32(rows), _i32(out_features),
+                                                                          _i32(in_features), _i32(epilogue)))
+
+
+def skinny_tcgen05_sums_shape(out_features: int):
+    """Shape of the sums-of-squares array that a product of this width leaves with ``prepare``."""
+    lib = load_library("skinny_tcgen05")
+    return (int(lib.tb_skinny_tcgen05_sums_tiles(_i32(out_features))), int(lib.tb_skinny_tcgen05_sums_stride()))
+
+
+def skinny_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor], epilogue: int = EPI_BF16,
+                   scaled_by: Optional[torch.Tensor] = None, eps: float = 0.0, prepare=None) -> Optional[torch.Tensor]:
+    """``out = x @ weight^T`` for 1 to 128 rows on the tcgen05 tensor cores, the weights streamed once.
+
+    ``epilogue`` as for :func:`gemm_tcgen05`.  ``scaled_by``: sums of squares ``[tiles, 128]`` that a product with
+    ``prepare`` left; every row of the result is then scaled by ``rsqrt(sum / in_features + eps)`` (the product
+    behind a prepared norm).  ``prepare = (residual, norm_weight, new_residual, scaled_rows, sums)``: instead of
+    storing ``out`` the product adds its (rounded) result to ``residual`` and leaves the new residual, that sum
+    times the following norm's weights, and the rows' sums of squares per tile of 128 features.
+    """
+    _cuda(x, weight)
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(x.dtype == weight.dtype == torch.bfloat16, "skinny_tcgen05 takes bfloat16 operands")
+    _need(weight.shape[1] == k and x.stride(1) == 1 and weight.stride(1) == 1, "skinny_tcgen05 layout")
+    null = ctypes.c_void_p(0)
+    ss_in, ss_tiles = null, 0
+    if scaled_by is not None:
+        _need(scaled_by.dtype == torch.float32 and scaled_by.is_contiguous() and scaled_by.dim() == 2
+              and scaled_by.shape[1] == 128, "skinny_tcgen05 sums of squares")
+        ss_in, ss_tiles = _ptr(scaled_by), scaled_by.shape[0]
+    epi = [null] * 5
+    out_ptr, out_stride = null, 0
+    if prepare is not None:
+        residual, norm_weight, new_residual, scaled_rows, sums = prepare
+        _cuda(residual, norm_weight, new_residual, scaled_rows, sums)
+        _need(scaled_by is None and epilogue == EPI_BF16, "a preparing product is a plain bfloat16 product")
+        _need(residual.shape == (m, n) and new_residual.shape == (m, n) and scaled_rows.shape == (m, n)
+              and residual.is_contiguous() and new_residual.is_contiguous() and scaled_rows.is_contiguous()
+              and residual.dtype == new_residual.dtype == scaled_rows.dtype == torch.bfloat16, "prepare rows")
+        _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == n and norm_weight.is_contiguous(),
+              "prepare norm weights")
+        _need(tuple(sums.shape) == skinny_tcgen05_sums_shape(n) and sums.dtype == torch.float32
+              and sums.is_contiguous(), "prepare sums")
+        epi = [_ptr(residual), _ptr(norm_weight), _ptr(new_residual), _ptr(scaled_rows), _ptr(sums)]
+        epilogue = EPI_ADD_NORM
+    else:
+        width = n // 2 if epilogue == EPI_SWIGLU else n
+        _cuda(out)
+        _need(out.shape == (m, width) and out.stride(1) == 1, "skinny_tcgen05 out shape")
+        _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "skinny_tcgen05 out dtype")
+        out_ptr, out_stride = _ptr(out), out.stride(0)
+    lib = load_library("skinny_tcgen05")
+    _check(lib.tb_skinny_tcgen05(_ptr(x), _i64(x.stride(0)), _ptr(weight), _i64(weight.stride(0)), out_ptr,
+                                 _i64(out_stride), _i32(m), _i32(n), _i32(k), _i32(epilogue), ss_in, _i32(ss_tiles),
+                                 _f32(eps), *epi, _ptr(_error_word(x.device)), _stream()), "skinny_tcgen05")
     return out
 
 

@@ -269,10 +269,12 @@ class PreparedNorm(DeferredNorm):
     and ``sums`` (``Linear.forward_normed``); any other consumer calls :meth:`materialize`, which runs the norm's
     own kernel on the new residual."""
 
-    def __init__(self, norm: "Norm", residual: torch.Tensor, rows: torch.Tensor, sums: torch.Tensor):
+    def __init__(self, norm: "Norm", residual: torch.Tensor, rows: torch.Tensor, sums: torch.Tensor,
+                 made_by: str = "decode_linear"):
         super().__init__(norm, residual, None)
         self.scaled_rows = rows
         self.sums = sums
+        self.made_by = made_by      # the kernel that left ``sums`` (their layout is that kernel's own)
 
 
 # ----------------------------------------------------------------------------- part bases

@@ -2,8 +2,9 @@
 
 Which kernel runs a product is the kernel plan's decision (``tesseract_b200.plan.product``); this class carries
 the decision out.  In float32: the package's own 32-bit kernel (a fixed K-ordered chain per output element).  In
-bfloat16: the weight-streaming kernel up to 16 rows (optionally with the norm in front and SwiGLU behind folded
-in), the tcgen05 GEMM where the plan says so, else the library GEMM with 32-bit accumulation, where the reference
+bfloat16: the weight-streaming kernels up to 16 rows (``decode_linear``, optionally with the norm in front and
+SwiGLU behind folded in) and up to 128 rows (``skinny_tcgen05``), the tcgen05 GEMM where the plan says so, else
+the library GEMM with 32-bit accumulation, where the reference
 also calls a library (src/cuda/cublas.rs:49-92: bfloat16 in and out, 32-bit compute, the weight transposed).
 """
 
@@ -33,6 +34,13 @@ class BestOfRows:
             self.buffers = (torch.empty(shape, dtype=torch.float32, device=self.device),
                             torch.empty(shape, dtype=torch.int32, device=self.device))
         self.valid = True
+
+
+def _tma_rows(x: torch.Tensor) -> torch.Tensor:
+    """Rows as a bulk tensor copy can fetch them: a 16-byte aligned base, a row stride of a multiple of 8 elements."""
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        return x.contiguous()
+    return x
 
 
 class Linear:
@@ -84,6 +92,8 @@ class Linear:
                 best.take(self.out_features)
             return kernels.decode_linear(self.weight, out, x=x, epilogue=choice.epilogue_code,
                                          best=best.buffers if best is not None and best.valid else None)
+        if choice.kernel == "skinny_tcgen05":
+            return kernels.skinny_tcgen05(_tma_rows(x), self.weight, out, epilogue=choice.epilogue_code)
         return kernels.gemm_tcgen05(x, self.weight, out, epilogue=choice.epilogue_code)
 
     def _prepare(self, x: torch.Tensor, follow):
@@ -96,17 +106,24 @@ class Linear:
         if (parameters is None or not follow.before.done or residual.shape != (rows, self.out_features)
                 or residual.dtype != self.runtime.dtype or not residual.is_contiguous() or x.stride(1) != 1):
             return None
-        if not self.plan(rows, plan.BF16, follow=True).prepares_norm:
+        choice = self.plan(rows, plan.BF16, follow=True)
+        if not choice.prepares_norm:
             return None
         weight, _ = parameters()
         if weight.numel() != self.out_features:
             return None
         new_residual = torch.empty_like(residual)
         scaled_rows = torch.empty_like(residual)
-        tiles = self.out_features // kernels.decode_linear_tile_features(self.out_features)
-        sums = torch.empty((tiles, kernels.SS_STRIDE), dtype=torch.float32, device=residual.device)
-        kernels.decode_linear(self.weight, None, x=x, prepare=(residual, weight, new_residual, scaled_rows, sums))
-        return PreparedNorm(follow.norm, new_residual, scaled_rows, sums)
+        if choice.kernel == "skinny_tcgen05":
+            sums = torch.empty(kernels.skinny_tcgen05_sums_shape(self.out_features), dtype=torch.float32,
+                               device=residual.device)
+            kernels.skinny_tcgen05(_tma_rows(x), self.weight, None,
+                                   prepare=(residual, weight, new_residual, scaled_rows, sums))
+        else:
+            tiles = self.out_features // kernels.decode_linear_tile_features(self.out_features)
+            sums = torch.empty((tiles, kernels.SS_STRIDE), dtype=torch.float32, device=residual.device)
+            kernels.decode_linear(self.weight, None, x=x, prepare=(residual, weight, new_residual, scaled_rows, sums))
+        return PreparedNorm(follow.norm, new_residual, scaled_rows, sums, made_by=choice.kernel)
 
     def forward_normed(self, deferred, float32_out: bool = False, epilogue: Optional[str] = None,
                        best=None) -> torch.Tensor:
@@ -123,10 +140,15 @@ class Linear:
             # the product in front left the rows times the norm's weights and their sums of squares: this product
             # takes them as they are and applies the scale to its 32-bit sums
             choice = self.plan(deferred.rows, wanted, norm="prepared")
-            if not choice.norm_folded:
+            if not choice.norm_folded or choice.kernel != deferred.made_by:     # the sums' layout is the kernel's own
                 return None
             _, eps = parameters()
             out = self._out(deferred.rows, choice, deferred.residual.device)
+            if choice.kernel == "skinny_tcgen05":
+                kernels.skinny_tcgen05(deferred.scaled_rows, self.weight, out, epilogue=choice.epilogue_code,
+                                       scaled_by=deferred.sums, eps=eps)
+                deferred.fused(None)
+                return out
             if best is not None and choice.epilogue == plan.F32:
                 best.take(self.out_features)
             kernels.decode_linear(self.weight, out, x=deferred.scaled_rows, scaled_by=deferred.sums, eps=eps,

@@ -12,9 +12,13 @@ Thresholds, with the measurement behind each:
   ``decode_linear`` kernel (mma.sync, 16 warps splitting K), with the residual addition and the RMSNorm in front
   and SwiGLU or a 32-bit store behind folded in.  Against the library product with norm and activation kernels
   of their own a decode step of 16 rows of the 1B sizes takes 0.94 instead of 1.33 ms.
-* ``FUSED_GATE_UP_MIN_ROWS`` (17): from here on gate/up + SwiGLU is one tcgen05 GEMM (100 against 114 us per
-  product at 2,048 rows; a decode step of 32 rows 1.48 -> 1.42 ms).
-* Plain bfloat16 products over more than 16 rows (QKV, O, down, the head) call the library GEMM, where the
+* ``SKINNY_MAX_ROWS`` (128): from 17 rows up to here a product streams its weights through ``skinny_tcgen05``
+  (tcgen05 with the weights as the 128-row operand, K splits as a thread-block cluster), with SwiGLU or a 32-bit
+  store behind it, and with the same division of a norm's work between the product in front of it and the product
+  behind it as ``decode_linear`` has.
+* ``FUSED_GATE_UP_MIN_ROWS`` (17): above ``SKINNY_MAX_ROWS`` gate/up + SwiGLU is one tcgen05 GEMM (100 against
+  114 us per product at 2,048 rows).
+* Plain bfloat16 products over more than 128 rows (QKV, O, down, the head) call the library GEMM, where the
   reference calls one (src/cuda/cublas.rs:49-92).
 """
 
@@ -29,6 +33,7 @@ import torch
 from . import kernels
 
 DECODE_LINEAR_MAX_ROWS = 16
+SKINNY_MAX_ROWS = kernels.SKINNY_MAX_ROWS
 FUSED_GATE_UP_MIN_ROWS = 17
 MAX_ATTENTION_SPLITS = kernels.MAX_ATTENTION_SPLITS
 CLUSTER_SPLITS = 8            # up to this many splits merge inside a thread-block cluster; more go through scratch
@@ -40,6 +45,11 @@ _EPILOGUE_CODE = {BF16: kernels.EPI_BF16, F32: kernels.EPI_F32, SWIGLU: kernels.
 @lru_cache(maxsize=None)
 def _decode_linear_takes(rows: int, out_features: int, in_features: int, prologue: int) -> bool:
     return kernels.decode_linear_supported(rows, out_features, in_features, prologue)
+
+
+@lru_cache(maxsize=None)
+def _skinny_takes(rows: int, out_features: int, in_features: int, epilogue: int) -> bool:
+    return kernels.skinny_tcgen05_supported(rows, out_features, in_features, epilogue)
 
 
 @lru_cache(maxsize=None)
@@ -55,7 +65,8 @@ def _attention_tcgen05_takes(num_heads: int, num_kv_heads: int, head_dim: int, p
 @dataclass(frozen=True)
 class ProductPlan:
     """``kernel``: ``gemm_f32`` (true 32-bit FFMA), ``decode_linear`` (weight streaming, at most 16 rows),
-    ``gemm_tcgen05`` (this package's tensor-memory GEMM) or ``library``.  ``norm_folded``: the RMSNorm (and the
+    ``skinny_tcgen05`` (weight streaming on the tensor-memory cores, at most 128 rows), ``gemm_tcgen05`` (this
+    package's tensor-memory GEMM) or ``library``.  ``norm_folded``: the RMSNorm (and the
     residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
     ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product.
     ``prepares_norm``: the product also does the work of the norm BEHIND it (new residual, rows times the norm's
@@ -108,6 +119,15 @@ def product(dtype: torch.dtype, rows: int, out_features: int, in_features: int, 
                 return ProductPlan("decode_linear", True, epilogue)
         if _decode_linear_takes(rows, out_features, in_features, kernels.PRO_NONE):
             return ProductPlan("decode_linear", False, epilogue)
+    if DECODE_LINEAR_MAX_ROWS < rows <= SKINNY_MAX_ROWS and in_features % 8 == 0:
+        # (rows whose stride is no multiple of 8 elements are refused by the kernel's caller, which then copies)
+        if norm == "prepared" and _skinny_takes(rows, out_features, in_features, _EPILOGUE_CODE[epilogue]):
+            return ProductPlan("skinny_tcgen05", True, epilogue, takes_prepared=True)
+        if (follow and norm is None and epilogue == BF16
+                and _skinny_takes(rows, out_features, in_features, kernels.EPI_ADD_NORM)):
+            return ProductPlan("skinny_tcgen05", False, BF16, prepares_norm=True)
+        if norm != "prepared" and _skinny_takes(rows, out_features, in_features, _EPILOGUE_CODE[epilogue]):
+            return ProductPlan("skinny_tcgen05", False, epilogue)
     if (epilogue == SWIGLU and rows >= FUSED_GATE_UP_MIN_ROWS
             and _gemm_tcgen05_takes(rows, out_features, in_features, kernels.EPI_SWIGLU)):
         return ProductPlan("gemm_tcgen05", False, SWIGLU)

@@ -57,13 +57,28 @@ def test_products_of_the_1b_sizes():
             plan.ProductPlan("decode_linear", True, "swiglu", takes_prepared=True)
         assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="prepared") == \
             plan.ProductPlan("decode_linear", True, "f32", takes_prepared=True)
-    assert not plan.product(BF, 17, hidden, hidden, follow=True).prepares_norm
     assert not plan.product(F32, 8, hidden, hidden, follow=True).prepares_norm
-    for rows in (17, 64, 2048):
+    for rows in (17, 64, 128):
+        # 17 to 128 rows stream their weights through the tensor-memory kernel, with the same division of a norm's
+        # work; a norm that no product prepared runs as a kernel of its own in front
+        assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan("skinny_tcgen05", False, "bf16")
+        assert plan.product(BF, rows, qkv, hidden, norm="prepared") == \
+            plan.ProductPlan("skinny_tcgen05", True, "bf16", takes_prepared=True)
+        assert plan.product(BF, rows, hidden, hidden, follow=True) == \
+            plan.ProductPlan("skinny_tcgen05", False, "bf16", prepares_norm=True)
+        assert plan.product(BF, rows, hidden, inter, follow=True).prepares_norm
+        assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu", norm="prepared") == \
+            plan.ProductPlan("skinny_tcgen05", True, "swiglu", takes_prepared=True)
+        assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu") == plan.ProductPlan("skinny_tcgen05", False, "swiglu")
+        assert plan.product(BF, rows, vocab, hidden, epilogue="f32", norm="prepared") == \
+            plan.ProductPlan("skinny_tcgen05", True, "f32", takes_prepared=True)
+    for rows in (129, 2048):
+        assert not plan.product(BF, rows, hidden, hidden, follow=True).prepares_norm
         assert plan.product(BF, rows, qkv, hidden, norm="add_norm") == plan.ProductPlan("library", False, "bf16")
         assert plan.product(BF, rows, 2 * inter, hidden, epilogue="swiglu") == plan.ProductPlan("gemm_tcgen05", False, "swiglu")
         assert plan.product(BF, rows, vocab, hidden, epilogue="f32") == plan.ProductPlan("library", False, "f32")
-    assert plan.DECODE_LINEAR_MAX_ROWS == 16 and plan.FUSED_GATE_UP_MIN_ROWS == plan.DECODE_LINEAR_MAX_ROWS + 1
+    assert plan.DECODE_LINEAR_MAX_ROWS == 16 and plan.SKINNY_MAX_ROWS == 128
+    assert plan.FUSED_GATE_UP_MIN_ROWS == plan.DECODE_LINEAR_MAX_ROWS + 1
 
 
 def test_products_of_sizes_a_kernel_does_not_take_fall_to_the_next():

@@ -717,3 +717,84 @@ def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
         else:
             assert torch.isnan(got.float()).all()           # short sequences are not this kernel's
         at += n
+
+
+@pytest.mark.parametrize("m, n, k", [(64, 2048, 2048), (17, 3072, 2048), (128, 2048, 8192), (100, 200, 136),
+                                     (33, 16384, 2048), (48, 20000, 64), (1, 128, 8), (96, 1152, 5120)])
+def test_skinny_tcgen05_against_a_plain_product(m, n, k):
+    """The swapped-operand tcgen05 product for up to 128 rows against a 64-bit product: every split count (one tile
+    per SM and fewer, K splits meeting in a cluster), several tiles per CTA, sizes that are no multiple of a tile,
+    bfloat16 and 32-bit stores, and SwiGLU on interleaved rows."""
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m + n + k)
+    bf = torch.bfloat16
+    x = torch.randn(m, k).to(bf)
+    w = (torch.randn(n, k) / math.sqrt(k)).to(bf)
+    exact = x.double() @ w.double().T
+    out32 = torch.full((m, n), float("nan"), device="cuda")
+    kernels.skinny_tcgen05(dev(x), dev(w), out32, epilogue=kernels.EPI_F32)
+    torch.testing.assert_close(out32.cpu().double(), exact, rtol=1e-4, atol=1e-4)
+    out16 = torch.zeros(m, n, dtype=bf, device="cuda")
+    kernels.skinny_tcgen05(dev(x), dev(w), out16)
+    assert torch.equal(out16.cpu(), out32.cpu().to(bf))
+    # rows with a stride of their own (a slice of a wider buffer)
+    wide = torch.zeros(m, k + 64, dtype=bf, device="cuda")
+    wide[:, 8:k + 8] = dev(x)
+    again = torch.zeros(m, n, dtype=bf, device="cuda")
+    kernels.skinny_tcgen05(wide[:, 8:k + 8], dev(w), again)
+    assert torch.equal(again, out16)
+    if n % 16 == 0:
+        act = torch.zeros(m, n // 2, dtype=bf, device="cuda")
+        kernels.skinny_tcgen05(dev(x), dev(w), act, epilogue=kernels.EPI_SWIGLU)
+        y = out32.cpu().double().view(m, n // 16, 2, 8)
+        g, u = y[:, :, 0].reshape(m, n // 2), y[:, :, 1].reshape(m, n // 2)
+        torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+    assert kernels.tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("m, inner, hidden, wide, eps", [(64, 2048, 2048, 3072, 1e-5), (19, 96, 160, 64, 1e-6),
+                                                         (128, 8192, 2048, 16384, 1e-5), (40, 64, 5024, 48, 1e-3),
+                                                         (77, 320, 3072, 1024, 1e-5)])
+def test_skinny_tcgen05_prepares_the_following_norm(m, inner, hidden, wide, eps):
+    """The same two halves as decode_linear's, for up to 128 rows: a product that leaves the new residual, the rows
+    times the following norm's weights and their sums of squares per tile of 128 features, and the product behind,
+    which applies the norm's scale to its 32-bit sums."""
+    from tesseract_b200 import kernels
+
+    torch.manual_seed(m + inner + hidden)
+    bf = torch.bfloat16
+    x = torch.randn(m, inner).to(bf)
+    w_first = (torch.randn(hidden, inner) / math.sqrt(inner)).to(bf)
+    res = (torch.randn(m, hidden) * 2).to(bf)
+    nw = 1 + 0.1 * torch.randn(hidden)
+    w_second = (torch.randn(wide, hidden) / math.sqrt(hidden)).to(bf)
+    res_out = torch.zeros(m, hidden, dtype=bf, device="cuda")
+    rows = torch.zeros(m, hidden, dtype=bf, device="cuda")
+    sums = torch.full(kernels.skinny_tcgen05_sums_shape(hidden), float("nan"), device="cuda")
+    res_dev = dev(res)
+    kernels.skinny_tcgen05(dev(x), dev(w_first), None, prepare=(res_dev, dev(nw), res_out, rows, sums))
+    o = (x.double() @ w_first.double().T).to(bf)                       # the product as it would be stored alone
+    c = res.double() + o.double()
+    close = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(res_out.cpu().double(), c, **close)
+    torch.testing.assert_close(rows.cpu().double(), c * nw.double(), **close)
+    assert torch.equal(res_dev.cpu(), res)                                  # the old residual is left alone
+    got_sums = sums.cpu().double()[:, :m]
+    assert torch.isfinite(got_sums).all()
+    torch.testing.assert_close(got_sums.sum(0), (c * c).sum(1), rtol=2e-2, atol=1e-3)
+    out = torch.empty(m, wide, dtype=torch.float32, device="cuda")
+    kernels.skinny_tcgen05(rows, dev(w_second), out, epilogue=kernels.EPI_F32, scaled_by=sums, eps=eps)
+    s = torch.rsqrt(got_sums.sum(0) / hidden + eps)[:, None]
+    torch.testing.assert_close(out.cpu().double(), (rows.cpu().double() @ w_second.double().T) * s, rtol=1e-4, atol=1e-4)
+    reference = llama.rms_norm(c, nw.double(), eps).to(bf).double() @ w_second.double().T
+    torch.testing.assert_close(out.cpu().double(), reference, **close)
+    if wide % 16 == 0:
+        act = torch.empty(m, wide // 2, dtype=bf, device="cuda")
+        kernels.skinny_tcgen05(rows, dev(w_second), act, epilogue=kernels.EPI_SWIGLU, scaled_by=sums, eps=eps)
+        y = out.cpu().double().view(m, wide // 16, 2, 8)
+        g, u = y[:, :, 0].reshape(m, wide // 2), y[:, :, 1].reshape(m, wide // 2)
+        torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, **close)
+    with pytest.raises(kernels.KernelError):       # the new residual needs a buffer of its own
+        kernels.skinny_tcgen05(dev(x), dev(w_first), None, prepare=(res_dev, dev(nw), res_dev, rows, sums))
+    assert kernels.tcgen05_error() == 0
