@@ -160,17 +160,22 @@ def run_ours(args):
     scratch = tempfile.TemporaryDirectory(prefix="tesseract_bench_")
     write_random_model(scratch.name, cfg, seed=0)
     max_batch = max(args.batch, 64)
-    decode_capacity = args.repeats * max_batch * (PROMPT_TOKENS + 320)     # every window's requests at once
+    # `--only decode --decode-context N`: the decode windows start behind prompts of N tokens instead of 2,048
+    decode_prompt = args.decode_context if args.only == "decode" and args.decode_context else PROMPT_TOKENS
+    context_limit = max(CONTEXT, decode_prompt + 512)
+    if decode_prompt != PROMPT_TOKENS:
+        max_batch = args.batch
+    decode_capacity = args.repeats * max_batch * (decode_prompt + 320)     # every window's requests at once
     llm = LLM(scratch.name, dtype="bfloat16", max_running=args.repeats * max_batch, max_batch_tokens=4096,
               prefill_chunk_tokens=PROMPT_TOKENS, kv_capacity_tokens=max(decode_capacity, max_batch * CONTEXT),
               page_size=PAGE_SIZE,
-              max_sequence_length=CONTEXT, cuda_graphs=not args.no_graphs)
+              max_sequence_length=context_limit, cuda_graphs=not args.no_graphs)
     stepper, cache = llm.stepper, llm.stepper.cache
     numbers = model_numbers(cfg, layers)
     sampler.start()
 
-    def prompt():
-        return rng.integers(0, cfg["vocab_size"], PROMPT_TOKENS).tolist()
+    def prompt(tokens=PROMPT_TOKENS):
+        return rng.integers(0, cfg["vocab_size"], tokens).tolist()
 
     # ---------------------------------------------------------------- prefill: one 2,048-token prompt, one step
     def prefill_once(rid):
@@ -248,7 +253,9 @@ def run_ours(args):
         for window_ids in sets:
             for rid in window_ids:
                 assert cache.admit(rid)
-                stepper.step([StepEntry(rid, prompt(), [])])
+                ids_of_prompt = prompt(decode_prompt)
+                for at in range(0, decode_prompt, PROMPT_TOKENS):
+                    stepper.step([StepEntry(rid, ids_of_prompt[at:at + PROMPT_TOKENS], [])])
         ids = list(sets[0])
 
         entries = [StepEntry(rid, [0], [0]) for rid in ids]
@@ -305,8 +312,11 @@ def run_ours(args):
 
     ms_step, launches, context, step_times = decode_device(args.batch, args.steps, args.warmup)
     if args.only == "decode":
+        step_bytes = numbers["weight_bytes"] + args.batch * context * numbers["kv_bytes_per_token"]
         print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms_step,
-                          "tokens_per_s": args.batch / (ms_step / 1e3), "context": context}))
+                          "tokens_per_s": args.batch / (ms_step / 1e3), "context": context,
+                          "gb_per_step": step_bytes / 1e9,
+                          "frac_of_hbm_peak": step_bytes / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"]}))
         return 0
     point_steps = max(8, min(args.steps, 64))
     ms_b1, _, context_b1, _ = decode_device(1, point_steps, args.warmup)
@@ -659,6 +669,8 @@ def main():
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     parser.add_argument("--no-graphs", action="store_true", help="decode without CUDA-graph replay")
+    parser.add_argument("--decode-context", type=int, default=0,
+                        help="with --only decode: decode behind prompts of this many tokens instead of 2,048")
     parser.add_argument("--repeats", type=int, default=REPEATS_DECODE,
                         help="how often the window of --steps decode steps is timed (the median counts); 1 keeps a "
                              "profiling run short")

@@ -454,8 +454,10 @@ void fit(Shape& s, int my_tiles, int my_pairs) {
 // How many clusters of `splits` CTAs with this much shared memory the GPU runs at once (a cluster needs its SMs
 // inside one GPC, so this is less than SMs / splits: 15 clusters of 8 and 22 of 6 on a B200 with a CTA per SM).
 int clusters_at_once(int splits, size_t smem) {
+    static std::mutex lock;
     static int known[kMaxSplits + 1] = {0};       // by cluster size, for the largest shared memory asked so far
     static size_t known_smem[kMaxSplits + 1] = {0};
+    std::lock_guard<std::mutex> guard(lock);
     if (known[splits] != 0 && smem <= known_smem[splits]) return known[splits];
     auto kernel = skinny_tcgen05_kernel<EPI_BF16, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
