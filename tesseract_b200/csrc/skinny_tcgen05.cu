@@ -19,11 +19,12 @@
 //     quarter of the tensor-memory lanes and take every other chunk of columns); then a warp takes a batch row
 //     at a time, a lane four neighbouring features of it, so that what goes to memory is contiguous.
 // A product with fewer feature tiles than SMs is also split along K, the splits of a tile being one thread-block
-// cluster (up to 8): after a cluster barrier split r takes the batch rows r, r + S, ... and adds the splits'
-// partial sums in ascending order of the splits, whichever finished first, through distributed shared memory
-// (all of a row's loads are in flight at once: a load from a peer's shared memory has a latency of hundreds of
-// cycles).  A CTA with several tiles (the head) alternates between two accumulators, so that one tile's epilogue
-// runs under the next tile's products.
+// cluster: as many splits (up to 8) as let all clusters run at once (a cluster lies inside one GPC, so fewer fit
+// than SMs / splits: 15 of 8 and 22 of 6 on a B200).  After a cluster barrier split r takes the batch rows r,
+// r + S, ... and adds the splits' partial sums in ascending order of the splits, whichever finished first, through
+// distributed shared memory (all of a row pair's loads are in flight at once: a load from a peer's shared memory
+// takes about a microsecond).  A CTA with several tiles (the head) alternates between two accumulators, so that
+// one tile's epilogue runs under the next tile's products.
 //
 // Epilogues: bfloat16 or 32-bit store; SwiGLU (src/cuda/kernels.rs:191-208) for a weight whose rows interleave
 // eight gate rows and their eight up rows; and EPI_ADD_NORM, the work of the addition and RMSNorm that FOLLOW the
