@@ -720,7 +720,8 @@ def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
 
 
 @pytest.mark.parametrize("m, n, k", [(64, 2048, 2048), (17, 3072, 2048), (128, 2048, 8192), (100, 200, 136),
-                                     (33, 16384, 2048), (48, 20000, 64), (1, 128, 8), (96, 1152, 5120)])
+                                     (33, 16384, 2048), (48, 20000, 64), (1, 128, 8), (96, 1152, 5120),
+                                     (21, 201, 72)])
 def test_skinny_tcgen05_against_a_plain_product(m, n, k):
     """The swapped-operand tcgen05 product for up to 128 rows against a 64-bit product: every split count (one tile
     per SM and fewer, K splits meeting in a cluster), several tiles per CTA, sizes that are no multiple of a tile,
@@ -744,6 +745,10 @@ def test_skinny_tcgen05_against_a_plain_product(m, n, k):
     again = torch.zeros(m, n, dtype=bf, device="cuda")
     kernels.skinny_tcgen05(wide[:, 8:k + 8], dev(w), again)
     assert torch.equal(again, out16)
+    # and an output that is a column slice of a wider buffer (rows that do not start on 8-byte boundaries)
+    framed = torch.full((m, n + 3), 7.0, dtype=bf, device="cuda")
+    kernels.skinny_tcgen05(dev(x), dev(w), framed[:, 1:n + 1])
+    assert torch.equal(framed[:, 1:n + 1], out16) and (framed[:, 0] == 7).all() and (framed[:, n + 1:] == 7).all()
     if n % 16 == 0:
         act = torch.zeros(m, n // 2, dtype=bf, device="cuda")
         kernels.skinny_tcgen05(dev(x), dev(w), act, epilogue=kernels.EPI_SWIGLU)
