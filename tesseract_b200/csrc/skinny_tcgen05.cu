@@ -201,6 +201,10 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __shared__ float scale_s[BF];            // SCALED: the batch rows' reciprocal root mean squares
 
     pdl_trigger();
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = p.splits, stages = p.stages;
     const int rank = S > 1 ? (int)cluster_rank() : 0;
