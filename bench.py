@@ -222,8 +222,10 @@ def run_ours(args):
             prefill_once(f"warm{k}")
             prefill_in_portions(f"warmp{k}", 512)
         t0 = time.time()
-        prefill_times = sorted(prefill_once(f"pre{k}")[0] for k in range(REPEATS_PREFILL))
-        portions_times = sorted(prefill_in_portions(f"prp{k}", 512) for k in range(REPEATS_PREFILL))
+        # (`--repeats N` below the default also shortens the prefill: a run under a profiler wants few launches)
+        prefill_repeats = REPEATS_PREFILL if args.repeats >= REPEATS_DECODE else max(1, args.repeats)
+        prefill_times = sorted(prefill_once(f"pre{k}")[0] for k in range(prefill_repeats))
+        portions_times = sorted(prefill_in_portions(f"prp{k}", 512) for k in range(prefill_repeats))
         windows.append((t0, time.time()))
     prefill_ms = statistics.median(prefill_times)
     if args.only == "prefill":
@@ -239,7 +241,7 @@ def run_ours(args):
                # beside it the fastest step against the burst peak and the median against the sustained peak
                "frac_fastest": flops / (prefill_times[0] / 1e3) / (pk["bf16_tflops"] * 1e12),
                "frac_of_sustained": flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12),
-               "repeats": REPEATS_PREFILL, "ms_min": prefill_times[0], "ms_max": prefill_times[-1],
+               "repeats": len(prefill_times), "ms_min": prefill_times[0], "ms_max": prefill_times[-1],
                "ms_4x512": portions_ms, "value_4x512": PROMPT_TOKENS / (portions_ms / 1e3)}
 
     # ---------------------------------------------------------------- decode on the device clock
