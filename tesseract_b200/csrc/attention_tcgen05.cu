@@ -56,6 +56,10 @@ struct TcAttnParams {
     const int* seq_begin;
     const int* block_table;
     int* error;
+    // key splits (gridDim.y > 1): every split's unnormalised output rows, their maxima and sums, arrival counters
+    float* part_o;                 // [tile CTA][split][128 rows][D]
+    float* part_ml;                // [tile CTA][split][128 rows][2]
+    int* counters;                 // [tile CTA], zero before and after every launch
     int64_t q_stride, out_stride;
     int bt_stride;
     int num_heads, num_kv_heads, group, page_shift, page_size, window;
@@ -196,6 +200,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     __shared__ __align__(8) uint64_t bars[4 * STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ int last_to_arrive;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // blockIdx.x runs over (tile rank, kv head) with the kv head fastest: CTAs start in the order of their index,
@@ -230,8 +235,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     const int last_row = min(n_rows, r0 + BM) - 1;
     const int key_hi = begin + last_row / p.group;
     const int key_lo = p.window > 0 ? max(0, begin + r0 / p.group - p.window + 1) : 0;
-    const int kb_first = key_lo / BN, kb_last = key_hi / BN;
-    const int n_blocks = kb_last - kb_first + 1;
+    // The tile's key blocks, cut into gridDim.y contiguous runs: a step whose tiles are too few to fill the GPU (a
+    // 512-token portion late in a long prompt) gives each tile to several CTAs, which leave unnormalised partial
+    // rows; the one that finishes last adds them in the order of the runs.  A run may be empty (early tiles).
+    const int key_splits = gridDim.y, key_split = blockIdx.y;
+    const int tile_blocks = key_hi / BN - key_lo / BN + 1;
+    const int first_of_run = key_split * tile_blocks / key_splits;
+    const int kb_first = key_lo / BN + first_of_run;
+    const int n_blocks = (key_split + 1) * tile_blocks / key_splits - first_of_run;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -351,7 +362,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             int qs = 0, s = 0;
             uint32_t q_parity = 0, parity = 0;
             auto next_q = [&]() { if (++qs == STAGES) { qs = 0; q_parity ^= 1; } };
-            bool ok = issue_qk(qs, q_parity);
+            bool ok = n_blocks == 0 || issue_qk(qs, q_parity);
             next_q();
             for (int j = 0; j < n_blocks && ok; ++j) {
                 // as soon as the softmax warps hold S_j in registers the next block's scores may overwrite it
@@ -525,27 +536,110 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             tc_fence_before();
             mbar_arrive(p_ready);
         }
-        if (ok && !mbar_wait(o_full, (n_blocks - 1) & 1, &abort_flag)) ok = false;
-        if (ok) {
-            tc_fence_after();
-            const float inv = 1.0f / fmaxf(l, 1.0e-8f);
-            const int qpos = pos >= 0 ? fr / p.group : 0, g = pos >= 0 ? fr - qpos * p.group : 0;
-            __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
+        if (ok && n_blocks > 0 && !mbar_wait(o_full, (n_blocks - 1) & 1, &abort_flag)) ok = false;
+        const int qpos = pos >= 0 ? fr / p.group : 0, g = pos >= 0 ? fr - qpos * p.group : 0;
+        __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
+        if (key_splits == 1) {
+            if (ok) {
+                tc_fence_after();
+                const float inv = 1.0f / fmaxf(l, 1.0e-8f);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                float v[32];
-                tmem_load_32(tmem_o + lane_base + c * 32, v);
-                if (pos >= 0) {
+                for (int c = 0; c < D / 32; ++c) {
+                    float v[32];
+                    tmem_load_32(tmem_o + lane_base + c * 32, v);
+                    if (pos >= 0) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
+                        for (int i = 0; i < 32; i += 8) {
+                            float w8[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) w8[e] = v[i + e] * inv;
+                            Packet<__nv_bfloat16>::store(dst + c * 32 + i, w8);
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+        } else {
+            // this run's rows as they stand (scaled by 2^-m, not yet divided by the sum), its maxima and sums
+            const int64_t tile_cta = (int64_t)seq * gridDim.x + blockIdx.x;
+            float* my_o = p.part_o + ((tile_cta * key_splits + key_split) * BM + r) * D;
+            float* my_ml = p.part_ml + ((tile_cta * key_splits + key_split) * BM + r) * 2;
+            if (ok && n_blocks > 0) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    float v[32];
+                    tmem_load_32(tmem_o + lane_base + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        __stcg(reinterpret_cast<float4*>(my_o + c * 32 + i), make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+                }
+                tc_fence_before();
+            }
+            __stcg(reinterpret_cast<float2*>(my_ml), make_float2(n_blocks > 0 ? m : kMasked, n_blocks > 0 ? l : 0.0f));
+            __threadfence();
+            asm volatile("bar.sync 2, 128;" ::: "memory");            // the four softmax warps
+            if (r == 0) {
+                const int arrived = atomicAdd(p.counters + tile_cta, 1);
+                last_to_arrive = arrived == key_splits - 1;
+                if (last_to_arrive) p.counters[tile_cta] = 0;         // every run of the tile has arrived: as found
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (last_to_arrive && ok && pos >= 0) {
+                // the runs in ascending order, whichever arrived when: o = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
+                __threadfence();
+                const float* runs_o = p.part_o + (tile_cta * key_splits * BM + r) * D;
+                const float* runs_ml = p.part_ml + (tile_cta * key_splits * BM + r) * 2;
+                float weight[8];
+                float big = kMasked, total = 0.0f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    weight[s] = kMasked;
+                    if (s < key_splits) weight[s] = __ldcg(runs_ml + (int64_t)s * BM * 2);
+                    big = fmaxf(big, weight[s]);
+                }
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const float sum = s < key_splits ? __ldcg(runs_ml + (int64_t)s * BM * 2 + 1) : 0.0f;
+                    weight[s] = sum > 0.0f ? fast_exp2(weight[s] - big) : 0.0f;
+                    total = fmaf(sum, weight[s], total);
+                }
+                const float inv = 1.0f / fmaxf(total, 1.0e-8f);
+                // 64 columns at a time, run by run: all of a run's sixteen loads are in flight before the first is
+                // used (a loop over the columns with the runs inside waits for L2 once per eight columns)
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 64) {
+                    float acc[64];
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) acc[e] = 0.0f;
+#pragma unroll 1
+                    for (int s = 0; s < key_splits; ++s) {
+                        float w = 0.0f;
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) w = t == s ? weight[t] : w;
+                        if (w > 0.0f) {
+                            float4 part[16];
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                part[e] = __ldcg(reinterpret_cast<const float4*>(runs_o + (int64_t)s * BM * D + c0 + 4 * e));
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                acc[4 * e] = fmaf(part[e].x, w, acc[4 * e]);
+                                acc[4 * e + 1] = fmaf(part[e].y, w, acc[4 * e + 1]);
+                                acc[4 * e + 2] = fmaf(part[e].z, w, acc[4 * e + 2]);
+                                acc[4 * e + 3] = fmaf(part[e].w, w, acc[4 * e + 3]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 64; e += 8) {
                         float w8[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) w8[e] = v[i + e] * inv;
-                        Packet<__nv_bfloat16>::store(dst + c * 32 + i, w8);
+                        for (int i = 0; i < 8; ++i) w8[i] = acc[e + i] * inv;
+                        Packet<__nv_bfloat16>::store(dst + c0 + e, w8);
                     }
                 }
             }
-            tc_fence_before();
         }
         if (!ok) {
             abort_flag = 1;
@@ -573,7 +667,8 @@ TB_EXPORT int tb_attention_tcgen05_supported(int num_heads, int num_kv_heads, in
 namespace {
 
 template <int D, int BN>
-int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_rows_per_seq, const TcAttnParams& p,
+int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_rows_per_seq, int key_splits,
+                     int64_t part_o_floats, int64_t part_ml_floats, int64_t counters_len, const TcAttnParams& p,
                      cudaStream_t stream) {
     const CUtensorMap* map = cache_map_for(cache, cache_pages, p.num_kv_heads, p.page_size, BN, D);
     if (map == nullptr) return TB_ERR_BAD_SIZE;
@@ -582,7 +677,14 @@ int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_r
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     const int max_folded = max_rows_per_seq * p.group;
-    dim3 grid(((max_folded + BM - 1) / BM) * p.num_kv_heads, 1, num_seqs);
+    dim3 grid(((max_folded + BM - 1) / BM) * p.num_kv_heads, key_splits, num_seqs);
+    if (key_splits > 1) {
+        const int64_t tile_ctas = (int64_t)grid.x * num_seqs;
+        if (p.part_o == nullptr || p.part_ml == nullptr || p.counters == nullptr ||
+            part_o_floats < tile_ctas * key_splits * BM * D || part_ml_floats < tile_ctas * key_splits * BM * 2 ||
+            counters_len < tile_ctas || ((uintptr_t)p.part_o | (uintptr_t)p.part_ml) % 16 != 0)
+            return TB_ERR_BAD_SIZE;
+    }
     if (cudaError_t launch = tb_launch_pdl(kernel, grid, dim3(kThreads), smem, stream, *map, p)) return (int)launch;
     return tb_launch_status();
 }
@@ -591,16 +693,22 @@ int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_r
 
 // Attention of the sequences with more than 16 folded rows of a packed batch (the others are left to the split
 // decode kernel).  Arguments as tb_attention_mma; error: device int, set non-zero if a bounded wait ran out.
+// key_splits (1 to 8): CTAs per tile, each over a contiguous run of the tile's key blocks; more than one needs
+// part_o (tile CTAs x key_splits x 128 x head_dim floats, 16-byte aligned; tile CTAs = ceil(max_rows_per_seq *
+// group / 128) * num_kv_heads * num_seqs), part_ml (tile CTAs x key_splits x 128 x 2 floats) and counters (tile
+// CTAs ints, zero before the first launch; every launch leaves them zero).  Launches that share them must be
+// ordered on one stream.
 TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
                                    const int* row_start, const int* seq_begin, const int* block_table, int bt_stride,
                                    int num_seqs, int max_rows_per_seq, int num_heads, int num_kv_heads, int head_dim,
-                                   int page_size, int cache_pages, int window, float scale, int* error,
-                                   cudaStream_t stream) {
+                                   int page_size, int cache_pages, int window, float scale, int key_splits,
+                                   float* part_o, int64_t part_o_floats, float* part_ml, int64_t part_ml_floats,
+                                   int* counters, int64_t counters_len, int* error, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     if (!tb_attention_tcgen05_supported(num_heads, num_kv_heads, head_dim, page_size)) return TB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
         return TB_ERR_BAD_ALIGN;
-    if (num_seqs > 65535 || num_kv_heads > 65535) return TB_ERR_BAD_SIZE;
+    if (num_seqs > 65535 || num_kv_heads > 65535 || key_splits < 1 || key_splits > 8) return TB_ERR_BAD_SIZE;
     TcAttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.out = (__nv_bfloat16*)out;
@@ -609,6 +717,9 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     p.seq_begin = seq_begin;
     p.block_table = block_table;
     p.error = error;
+    p.part_o = part_o;
+    p.part_ml = part_ml;
+    p.counters = counters;
     p.q_stride = q_stride;
     p.out_stride = out_stride;
     p.bt_stride = bt_stride;
@@ -620,6 +731,9 @@ TB_EXPORT int tb_attention_tcgen05(const void* q, int64_t q_stride, void* out, i
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.scale_log2 = scale * kLog2e;
-    if (head_dim == 128) return launch_attention<128, 64>(cache, cache_pages, num_seqs, max_rows_per_seq, p, stream);
-    return launch_attention<64, kBlockKeys64>(cache, cache_pages, num_seqs, max_rows_per_seq, p, stream);
+    if (head_dim == 128)
+        return launch_attention<128, 64>(cache, cache_pages, num_seqs, max_rows_per_seq, key_splits, part_o_floats,
+                                         part_ml_floats, counters_len, p, stream);
+    return launch_attention<64, kBlockKeys64>(cache, cache_pages, num_seqs, max_rows_per_seq, key_splits, part_o_floats,
+                                              part_ml_floats, counters_len, p, stream);
 }

@@ -308,6 +308,11 @@ class _AttentionWorkspace:
         self.max_ctas = self.part_o.numel() // (16 * 32)
         self.part_ml = torch.empty(self.max_ctas * 16 * 2, dtype=torch.float32, device=device)
         self.counters = torch.zeros(max(4096, self.max_ctas), dtype=torch.int32, device=device)   # left zero by every launch
+        # the prompt kernel's key splits (attention_tcgen05): one CTA's 128 rows of up to 128 floats, their maxima
+        # and sums, for as many CTAs as are resident at once; a counter per tile
+        self.prompt_o = torch.empty(ctas * 128 * 128, dtype=torch.float32, device=device)
+        self.prompt_ml = torch.empty(ctas * 128 * 2, dtype=torch.float32, device=device)
+        self.prompt_counters = torch.zeros(ctas, dtype=torch.int32, device=device)                # left zero as well
 
 
 _attention_workspaces = {}
@@ -337,6 +342,9 @@ def attention_workspace(device) -> None:
     """Create the device's permanent attention workspace now (before any graph capture)."""
     device = torch.device(device)
     if device not in _attention_workspaces:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention workspace must exist before a graph is captured "
+                              "(call kernels.attention_workspace(device) first)")
         _attention_workspaces[device] = _AttentionWorkspace(device)
 
 
@@ -641,11 +649,22 @@ def attention_tcgen05_supported(num_heads: int, num_kv_heads: int, head_dim: int
         _i32(num_heads), _i32(num_kv_heads), _i32(head_dim), _i32(page_size)))
 
 
+def attention_tcgen05_tile_ctas(num_seqs: int, max_new: int, num_heads: int, num_kv_heads: int) -> int:
+    """CTAs that :func:`attention_tcgen05` launches per key split: tiles of 128 folded rows per kv head and
+    sequence (the grid is laid out for the longest sequence)."""
+    fold = num_heads // num_kv_heads
+    return -(-(max_new * fold) // 128) * num_kv_heads * num_seqs
+
+
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, row_start: torch.Tensor,
                       seq_begin: torch.Tensor, block_table: torch.Tensor, num_seqs: int, max_new: int, num_heads: int,
-                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                      key_splits: int = 1) -> torch.Tensor:
     """Prompt-portion attention on the tcgen05 tensor cores: the sequences of the batch with more than 16 folded
-    rows (``new tokens * num_heads / num_kv_heads``); rows of shorter sequences are left untouched."""
+    rows (``new tokens * num_heads / num_kv_heads``); rows of shorter sequences are left untouched.  With
+    ``key_splits`` > 1 every tile of 128 folded rows is shared by that many CTAs, each over a contiguous run of the
+    tile's keys, and the last to finish adds the runs in order (for steps with too few tiles to fill the GPU); the
+    partial rows go through the device's permanent workspace, which holds ``2 * SMs`` CTAs."""
     _cuda(q, out, cache, row_start, seq_begin, block_table)
     _need(q.dtype == out.dtype == cache.dtype == torch.bfloat16, "attention_tcgen05 takes bfloat16")
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim and out.shape == q.shape,
@@ -656,9 +675,20 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, r
     _need(block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[0] >= num_seqs, "block table")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "cache layout")
     lib = load_library("attention_tcgen05")
+    part_o = part_ml = counters = None
+    if key_splits > 1:
+        attention_workspace(q.device)
+        work = _attention_workspaces[q.device]
+        ctas = attention_tcgen05_tile_ctas(num_seqs, max_new, num_heads, num_kv_heads) * key_splits
+        _need(1 < key_splits <= 8 and ctas * 128 * head_dim <= work.prompt_o.numel(),
+              "attention_tcgen05: more key splits than the workspace holds")
+        part_o, part_ml, counters = work.prompt_o, work.prompt_ml, work.prompt_counters
     _check(lib.tb_attention_tcgen05(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
                                     _ptr(row_start), _ptr(seq_begin), _ptr(block_table), _i32(block_table.stride(0)),
                                     _i32(num_seqs), _i32(max_new), _i32(num_heads), _i32(num_kv_heads),
                                     _i32(head_dim), _i32(page_size), _i32(cache.shape[0]), _i32(window), _f32(scale),
+                                    _i32(key_splits), _ptr(part_o), _i64(part_o.numel() if part_o is not None else 0),
+                                    _ptr(part_ml), _i64(part_ml.numel() if part_ml is not None else 0),
+                                    _ptr(counters), _i64(counters.numel() if counters is not None else 0),
                                     _ptr(_error_word(q.device)), _stream()), "attention_tcgen05")
     return out

@@ -124,7 +124,7 @@ class Attention(Mixer):
             # prompt portions on the fifth-generation tensor cores; decode rows (if any) by the split kernel
             kernels.attention_tcgen05(q, attended, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
                                       ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,
-                                      cache.page_size, self.window, self.scale)
+                                      cache.page_size, self.window, self.scale, key_splits=choice.key_splits)
         if tiles or choice.split:
             kernels.attention_mma(q, attended, cache.storage, ctx.row_start, ctx.seq_begin, group.block_table,
                                   ctx.num_seqs, ctx.max_new, self.num_heads, self.num_kv_heads, self.head_dim,

@@ -162,19 +162,36 @@ def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_di
     return best
 
 
+def prompt_key_splits(tile_ctas: int, max_context: int, head_dim: int = 64, sms: Optional[int] = None) -> int:
+    """CTAs per tile of the tcgen05 prompt kernel.  A tile of 128 folded rows walks over its key blocks (128 keys
+    up to head size 64, else 64) one after the other, about 1.7 microseconds a block, and two CTAs fit an SM: a
+    step with fewer tiles than that (a 512-token portion of one prompt is 128 tiles of the 1B sizes) leaves SMs
+    idle while every tile walks its whole context.  Such a step gives each tile to several CTAs, each over a run of
+    at least sixteen blocks, as many as are resident at once (at most 8); the last one to finish adds the runs.
+    Leaving and adding the partial rows costs about 10 microseconds (a round of stores, a fence, a counter, three
+    rounds of loads from L2), and two CTAs on an SM share its exponential unit, so short contexts lose: a 512-token
+    portion at context 2,048 takes 34.9 us alone and 36.6 shared by two, at 4,096 61.7 and 52.4, at 16,384 232 and
+    146."""
+    resident = 2 * (sms or kernels.sm_count())
+    blocks = -(-max_context // (128 if head_dim <= 64 else 64))
+    return max(1, min(8, resident // max(1, tile_ctas), blocks // 16))
+
+
 @dataclass(frozen=True)
 class AttentionPlan:
     """``fused_decode``: one kernel rotates q and the new key, writes the cache page and attends (a pure decode
     step).  Otherwise a rotation + cache-write kernel runs first and ``prompt`` (``tcgen05``, ``mma_tiles`` or
     None) takes the sequences with more than 16 folded rows (new tokens x query heads per kv head), ``split``
     (True/False) the others through the split decode kernel.  ``rows``: the 32-bit path's one kernel.
-    ``splits``/``merge``: key splits of the split kernel and how they meet (``none``, ``cluster``, ``scratch``)."""
+    ``splits``/``merge``: key splits of the split kernel and how they meet (``none``, ``cluster``, ``scratch``).
+    ``key_splits``: CTAs per tile of the tcgen05 prompt kernel (``prompt_key_splits``)."""
 
     fused_decode: bool = False
     prompt: Optional[str] = None
     split: bool = False
     rows: bool = False
     splits: int = 1
+    key_splits: int = 1
 
     @property
     def merge(self) -> str:
@@ -187,7 +204,8 @@ class AttentionPlan:
             return f"attention_decode (rotation and cache write folded in; {self.splits} split(s), merge: {self.merge})"
         parts = ["rope_kv_write"]
         if self.prompt:
-            parts.append(f"attention_{self.prompt} for prompt portions")
+            shared = f", {self.key_splits} CTAs a tile" if self.key_splits > 1 else ""
+            parts.append(f"attention_{self.prompt} for prompt portions{shared}")
         if self.split:
             parts.append(f"attention_decode for short sequences ({self.splits} split(s), merge: {self.merge})")
         return " + ".join(parts)
@@ -211,7 +229,11 @@ def attention(dtype: torch.dtype, *, num_heads: int, num_kv_heads: int, head_dim
         if prompt_kernel == "tcgen05" and _attention_tcgen05_takes(num_heads, num_kv_heads, head_dim, page_size):
             prompt = "tcgen05"
     splits = attention_splits(seqs, num_kv_heads, max_context, head_dim, sms) if short_seqs else 1
-    return AttentionPlan(prompt=prompt, split=short_seqs, splits=splits)
+    key_splits = 1
+    if prompt == "tcgen05":
+        tile_ctas = -(-(max(new_tokens) * fold) // 128) * num_kv_heads * seqs      # the kernel's grid, per key split
+        key_splits = prompt_key_splits(tile_ctas, max_context, head_dim, sms)
+    return AttentionPlan(prompt=prompt, split=short_seqs, splits=splits, key_splits=key_splits)
 
 
 def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), context: int = 4096,

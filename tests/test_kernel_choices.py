@@ -103,7 +103,12 @@ def test_attention_plans():
     lonely = plan.attention(BF, new_tokens=[1], max_context=131072, **sizes)
     assert lonely.fused_decode and lonely.splits == 32 and lonely.merge == "scratch"
     portion = plan.attention(BF, new_tokens=[2048], max_context=2048, **sizes)
-    assert portion.prompt == "tcgen05" and not portion.split and not portion.fused_decode
+    assert portion.prompt == "tcgen05" and not portion.split and not portion.fused_decode and portion.key_splits == 1
+    # a 512-token portion is 128 tiles: late in a long prompt every tile is shared by two CTAs, early it is not
+    assert plan.attention(BF, new_tokens=[512], max_context=2048, **sizes).key_splits == 1
+    assert plan.attention(BF, new_tokens=[512], max_context=16384, **sizes).key_splits == 2
+    assert plan.attention(BF, new_tokens=[512, 512, 512], max_context=16384, **sizes).key_splits == 1
+    assert plan.attention(BF, new_tokens=[64], max_context=32768, **sizes).key_splits == 8
     mixed = plan.attention(BF, new_tokens=[512, 1, 1, 3], max_context=4096, **sizes)
     assert mixed.prompt == "tcgen05" and mixed.split and mixed.splits >= 1
     narrow = dict(sizes, head_dim=48, num_heads=6, num_kv_heads=3)

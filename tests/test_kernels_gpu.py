@@ -462,7 +462,8 @@ def test_attention_tcgen05_and_wide_decode_find_one_far_key_among_hundreds(d):
                 seq_begin = torch.tensor([n - new], dtype=torch.int32)
                 out = torch.full((new, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
                 kernels.attention_tcgen05(dev(case["q"]).view(new, nh * d), out, dev(case["cache"]), dev(row_start),
-                                          dev(seq_begin), dev(case["table"]), 1, new, nh, nkv, d, page_size, 0, 1.0)
+                                          dev(seq_begin), dev(case["table"]), 1, new, nh, nkv, d, page_size, 0, 1.0,
+                                          key_splits=1 + target % 4)      # alone, or shared by up to four CTAs
                 assert kernels.tcgen05_error() == 0
             else:
                 out = run_attention_mma(case, nh, nkv, d, page_size, 0, 1.0, splits)
@@ -717,6 +718,26 @@ def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
         else:
             assert torch.isnan(got.float()).all()           # short sequences are not this kernel's
         at += n
+    # the same with every tile shared by several CTAs, each over a run of the tile's key blocks (some runs are empty:
+    # early tiles have fewer blocks than CTAs), twice in a row (the arrival counters must be left as found)
+    tiles = kernels.attention_tcgen05_tile_ctas(len(lengths), max(new), nh, nkv)
+    for key_splits in (2, 3, 8):
+        if tiles * key_splits > 2 * kernels.sm_count():
+            continue
+        for _ in range(2):
+            shared = torch.full((rows, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+            kernels.attention_tcgen05(dev(case["q"]).view(rows, nh * d), shared, dev(case["cache"]), dev(row_start),
+                                      dev(seq_begin), dev(case["table"]), len(lengths), max(new), nh, nkv, d, page_size,
+                                      window, scale, key_splits=key_splits)
+            assert kernels.tcgen05_error() == 0
+            at = 0
+            for n in new:
+                if n * fold > 16:
+                    torch.testing.assert_close(shared[at:at + n].cpu().double(), want[at:at + n], rtol=2e-2, atol=2e-2)
+                    torch.testing.assert_close(shared[at:at + n].float(), out[at:at + n].float(), rtol=2e-2, atol=1e-2)
+                else:
+                    assert torch.isnan(shared[at:at + n].float()).all()
+                at += n
 
 
 @pytest.mark.parametrize("m, n, k", [(64, 2048, 2048), (17, 3072, 2048), (128, 2048, 8192), (100, 200, 136),
