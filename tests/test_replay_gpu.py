@@ -506,3 +506,41 @@ def test_graphs_that_use_split_scratch_survive_later_larger_steps(tmp_path):
     assert kernels.tcgen05_error() == 0
     for k, (a, b) in enumerate(zip(got, want)):
         assert torch.equal(a, b), f"step {k} of the replayed run differs from launch by launch"
+
+
+def test_portions_late_in_a_long_prompt_share_their_tiles_between_ctas(tmp_path):
+    """Beyond some 4,000 tokens of context a step with few attention tiles gives every tile to several CTAs, each
+    over a run of the tile's key blocks (``plan.prompt_key_splits``).  A prompt of 4,700 tokens fed as one large
+    portion and then portions of 300 down to 2 tokens: the rows of the late portions against the plain model.  (That
+    one far key among hundreds is found whichever run it lies in is the kernel test's part:
+    test_attention_tcgen05_and_wide_decode_find_one_far_key_among_hundreds.)"""
+    from tests.helpers import make_model_folder
+    from tests.plain import llama
+    from tesseract_b200 import kernels, plan
+    from tesseract_b200.engine import load_model, make_stepper
+
+    folder = make_model_folder(str(tmp_path / "long_prompt"), LONG_CONTEXT, "bfloat16", 5)
+    total = 4700
+    requests = {"long": random_tokens(LONG_CONTEXT["vocab_size"], total, seed=77)}
+    sizes = [4096, 300, 200, 64, 30, 8, 2]
+    assert sum(sizes) == total
+    for new in sizes[1:4]:
+        shared = plan.attention(torch.bfloat16, num_heads=4, num_kv_heads=2, head_dim=64, page_size=16,
+                                new_tokens=[new], max_context=4400)
+        assert shared.prompt == "tcgen05" and shared.key_splits >= 2
+    keep = {"long": sorted(set(range(4096, total, 7)) | set(range(total - 40, total)))}
+    config, tensors = llama.load_folder(folder)
+    plain = {"long": llama.forward(config, tensors, requests["long"], head_rows=keep["long"]).numpy()}
+    rows_of = {"long": {position: row for row, position in enumerate(keep["long"])}}
+    noise = bf16_noise(folder, requests, plain, head_rows=keep)
+    steps, at = [], 0
+    for size in sizes:
+        steps.append(([("long", requests["long"][at:at + size], list(range(size)))], ["long"] if at + size == total else []))
+        at += size
+    model = load_model(folder, dtype="bfloat16")
+    stepper = make_stepper(model, capacity_tokens=total + 64, max_requests=2)
+    got = replay(stepper, keep_wants(steps, {"long": set(keep["long"])}))
+    assert kernels.tcgen05_error() == 0
+    assert len(got) == len(keep["long"])
+    compare(got, plain, REL["bfloat16"], "long prompt, late portions", rows_of, noise)
+    stepper.cache.check()
