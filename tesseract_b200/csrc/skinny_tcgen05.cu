@@ -37,6 +37,8 @@
 // CTA still meets its cluster barriers and frees its tensor memory.
 #include "umma.cuh"
 
+#include <atomic>
+
 namespace {
 
 using namespace tbtma;
@@ -465,7 +467,8 @@ int clusters_at_once(int splits, size_t smem) {
     std::lock_guard<std::mutex> guard(lock);
     if (known[splits] != 0 && smem <= known_smem[splits]) return known[splits];
     auto kernel = skinny_tcgen05_kernel<EPI_BF16, false>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSmemBudget + 1024)) != cudaSuccess)
+        return 0;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(splits * sm_count());
     config.blockDim = dim3(kThreads);
@@ -516,8 +519,13 @@ template <int EPI, bool SCALED>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const SkinnyParams& p, const Shape& s,
            cudaStream_t stream) {
     auto kernel = skinny_tcgen05_kernel<EPI, SCALED>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem);
-    if (err != cudaSuccess) return (int)err;
+    static std::atomic<bool> allowed{false};      // this instantiation may use as much shared memory as any shape asks
+    cudaError_t err = cudaSuccess;
+    if (!allowed.load(std::memory_order_acquire)) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSmemBudget + 1024));
+        if (err != cudaSuccess) return (int)err;
+        allowed.store(true, std::memory_order_release);
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(s.clusters * s.splits);
     config.blockDim = dim3(kThreads);
@@ -579,9 +587,12 @@ TB_EXPORT int tb_skinny_tcgen05(const void* x, int64_t x_stride, const void* w, 
     }
     if (ss_in != nullptr && ss_tiles < 1) return TB_ERR_BAD_ALIGN;
     const Shape s = shape_for(M, N, K);
-    CUtensorMap map_w, map_x;
-    if (int status = make_map_2d(&map_w, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, BF)) return status;
-    if (int status = make_map_2d(&map_x, x, (uint64_t)M, (uint64_t)K, (uint64_t)x_stride, (uint32_t)s.mp)) return status;
+    const CUtensorMap* cached_w = cached_map_2d(w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, BF);
+    if (cached_w == nullptr) return TB_ERR_BAD_SIZE;
+    const CUtensorMap map_w = *cached_w;
+    const CUtensorMap* cached_x = cached_map_2d(x, (uint64_t)M, (uint64_t)K, (uint64_t)x_stride, (uint32_t)s.mp);
+    if (cached_x == nullptr) return TB_ERR_BAD_SIZE;
+    const CUtensorMap map_x = *cached_x;
     SkinnyParams p;
     p.out = out;
     p.out_stride = out_stride;

@@ -97,6 +97,28 @@ inline int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : TB_ERR_BAD_SIZE;
 }
 
+// The same, kept per (pointer, geometry): encoding a map costs the host a couple of microseconds, a step launched
+// kernel by kernel makes hundreds, and weights (and, through the caching allocator, most activations) come back
+// at the same addresses.  A map depends on nothing but the key, so an entry can never go stale; the table is
+// emptied when it has grown to 4,096 entries.  The pointer stays valid until the next call from the same thread.
+inline const CUtensorMap* cached_map_2d(const void* base, uint64_t rows, uint64_t cols, uint64_t stride,
+                                        uint32_t box_rows) {
+    static std::mutex lock;
+    static std::map<std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t>, CUtensorMap> maps;
+    thread_local CUtensorMap mine;
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_tuple(base, rows, cols, stride, box_rows);
+    auto found = maps.find(key);
+    if (found == maps.end()) {
+        CUtensorMap map;
+        if (make_map_2d(&map, base, rows, cols, stride, box_rows) != 0) return nullptr;
+        if (maps.size() >= 4096) maps.clear();
+        found = maps.emplace(key, map).first;
+    }
+    mine = found->second;
+    return &mine;
+}
+
 // Tensor map of one cache entry [pages][K|V][kv head][key][head_dim] (head_dim a multiple of 64), boxes of 64 dims
 // of min(page_size, max_rows) keys of one head.  Maps are kept per (pointer, geometry): a cache entry lives as long
 // as its model.

@@ -260,21 +260,36 @@ class DecodeGraphs:
 
 class _ChunkGraph:
     """Buffers and the captured graph for steps in which ``portions`` sequences bring ``rows`` prompt tokens each
-    (rows ``k * rows`` .. ``(k + 1) * rows - 1``) and up to ``decodes`` others one decoded token each (the rows
-    after them, all wanted).  With ``wants_last`` the last row of every portion goes through the head as well (the
-    caller picks the ones it asked for); without, no portion row does."""
+    (rows ``k * rows`` .. ``(k + 1) * rows - 1``), then (``tail`` > 0) one sequence brings the end of its prompt,
+    fewer than ``tail`` tokens, and up to ``decodes`` others one decoded token each (the rows after them, all
+    wanted).  With ``wants_last`` the last row of every portion goes through the head as well (the caller picks the
+    ones it asked for); without, no portion row does.
+
+    A tail has ``tail`` rows in the graph whatever its length: the rows behind its last token belong to a padding
+    sequence whose block table names the scratch page only and whose state slot is the scratch slot, so that they
+    compute on garbage and touch nothing.  Which rows are the tail's and which the padding's is data (the row
+    starts, the sequence of each row, the row that goes through the head), so one graph serves every tail length
+    below ``tail``.  The tail's last row always goes through the head."""
 
     def __init__(self, stepper: Stepper, rows: int, portions: int, decodes: int, wants_last: bool, columns: int,
-                 pool=None):
+                 pool=None, tail: int = 0):
         cache, device = stepper.cache, stepper.runtime.device
         self.rows, self.portions, self.decodes, self.columns = rows, portions, decodes, columns
-        self.wants_last = wants_last
-        prompt_rows = portions * rows
-        total, seqs = prompt_rows + decodes, portions + decodes
+        self.wants_last, self.tail = wants_last, tail
+        prompt_rows = portions * rows + tail
+        extra = 2 if tail else 0                       # the tail's sequence and the padding's
+        total, seqs = prompt_rows + decodes, portions + extra + decodes
+        self.total, self.seqs, self.prompt_rows = total, seqs, prompt_rows
         self.paged = [i for i, g in enumerate(cache.groups) if g.pool is not None]
-        # int32 block: tokens[total] positions[total] begin[seqs] slot[seqs]; block tables apart (only the columns
-        # in use are copied)
-        self.ints = 2 * total + 2 * seqs
+        wanted = ([(k + 1) * rows - 1 for k in range(portions)] if wants_last else [])
+        self.tail_want = len(wanted) if tail else None           # where among the wanted rows the tail's stands
+        if tail:
+            wanted.append(prompt_rows - 2)
+        wanted += list(range(prompt_rows, total))
+        self.wanted = len(wanted)
+        # int32 block: tokens[total] positions[total] begin[seqs] slot[seqs], and with a tail seq_of_row[total]
+        # row_start[seqs + 1] want[wanted]; block tables apart (only the columns in use are copied)
+        self.ints = 2 * total + 2 * seqs + ((total + seqs + 1 + len(wanted)) if tail else 0)
         self.hosts = [torch.zeros(self.ints, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
         self.host_tables = [[torch.zeros((seqs, columns), dtype=torch.int32, pin_memory=True) for _ in self.paged]
                             for _ in range(HOST_RING)]
@@ -286,22 +301,44 @@ class _ChunkGraph:
         tables = dict(zip(self.paged, self.dev_tables))
         groups = [GroupView(tables.get(index), cache.page_size if g.pool is not None else 0)
                   for index, g in enumerate(cache.groups)]
-        seq_of_row = torch.cat([torch.arange(portions, dtype=torch.int32).repeat_interleave(rows),
-                                torch.arange(portions, seqs, dtype=torch.int32)]).to(device)
-        row_start = torch.cat([torch.arange(0, prompt_rows, rows, dtype=torch.int32),
-                               torch.arange(prompt_rows, total + 1, dtype=torch.int32)]).to(device)
+        seq_of_row_host = torch.cat([torch.arange(portions, dtype=torch.int32).repeat_interleave(rows),
+                                     torch.full((max(0, tail - 1),), portions, dtype=torch.int32),
+                                     torch.full((1 if tail else 0,), portions + 1, dtype=torch.int32),
+                                     torch.arange(portions + extra, seqs, dtype=torch.int32)])
+        row_start_host = torch.cat([torch.arange(0, portions * rows, rows, dtype=torch.int32),
+                                    torch.tensor([portions * rows, prompt_rows - 1] if tail else [], dtype=torch.int32),
+                                    torch.arange(prompt_rows, total + 1, dtype=torch.int32)])
+        self.at_seq_of_row = 2 * total + 2 * seqs
+        self.at_row_start = self.at_seq_of_row + total
+        self.at_want = self.at_row_start + seqs + 1
+        if tail:
+            seq_of_row = d[self.at_seq_of_row:self.at_row_start]
+            row_start = d[self.at_row_start:self.at_want]
+            self.want_rows = d[self.at_want:self.at_want + len(wanted)]
+            # a portion as long as the graph's rows, then a row of one: the plan then launches both the prompt
+            # kernel and the kernel of the short sequences, whatever the tail's and the padding's lengths will be
+            host_new = [rows] * portions + [tail, 1] + [1] * decodes
+        else:
+            seq_of_row, row_start = seq_of_row_host.to(device), row_start_host.to(device)
+            self.want_rows = torch.tensor(wanted, dtype=torch.int32, device=device) if wanted else None
+            host_new = [rows] * portions + [1] * decodes
         self.ctx = StepContext(
             num_rows=total, num_seqs=seqs, token_ids=d[:total], positions=d[total:2 * total], seq_of_row=seq_of_row,
             row_start=row_start, seq_begin=d[2 * total:2 * total + seqs],
             state_slots=d[2 * total + seqs:2 * total + 2 * seqs], groups=groups,
-            host_new=[rows] * portions + [1] * decodes, host_begin=(), host_slots=(), max_new=rows,
+            host_new=host_new, host_begin=(), host_slots=(), max_new=max(rows if portions else 0, tail),
             max_context=columns * cache.page_size)
-        wanted = ([(k + 1) * rows - 1 for k in range(portions)] if wants_last else []) + list(range(prompt_rows, total))
-        self.want_rows = torch.tensor(wanted, dtype=torch.int32, device=device) if wanted else None
-        # capture on harmless metadata: positions 0.., the scratch slot, the scratch page
+        # capture on harmless metadata: positions 0.., the scratch slot, the scratch page; a tail of all rows but one
         host = self.hosts[0].numpy()
-        host[total:total + prompt_rows] = np.tile(np.arange(rows, dtype=np.int32), portions)
+        host[total:total + portions * rows] = np.tile(np.arange(rows, dtype=np.int32), portions)
+        if tail:
+            host[total + portions * rows:total + prompt_rows - 1] = np.arange(tail - 1, dtype=np.int32)
+            host[self.at_seq_of_row:self.at_row_start] = seq_of_row_host.numpy()
+            host[self.at_row_start:self.at_want] = row_start_host.numpy()
+            host[self.at_want:self.at_want + len(wanted)] = np.asarray(wanted, dtype=np.int32)
         host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
+        for other in self.hosts[1:]:                 # (the parts that no step rewrites must stand in every copy)
+            other.copy_(self.hosts[0])
         self.dev.copy_(self.hosts[0])
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
@@ -329,19 +366,21 @@ class _ChunkGraph:
 
 class ChunkGraphs:
     """CUDA-graph replay of steps with prompt portions: the first one to ``max_portions`` sequences bring exactly
-    ``rows`` tokens each (the configured portion size) and want nothing or their last place; every other sequence
-    brings one decoded token and wants it.  Between two such steps only device metadata differs (token ids,
-    positions, block tables), so the launches of the whole model are replayed instead of issued one by one; at
-    2,048 rows of the 1B sizes that takes the step from 4.6 to 3.9 ms.  One graph per (portions, decode rows
-    rounded up to a power of two, whether any portion wants its last place, block-table width rounded up to a
-    power of two): the width bounds the context, and with it the split count that the decode rows' attention is
-    captured with, as for the decode graphs.  Rows that pad the decode part point at the scratch page and the
-    scratch state slot.  If one portion wants its last place the last rows of all portions go through the head
-    and the caller gets the ones it asked for.  The graphs share one memory pool (they never run at the same
-    time), so the returned logits are valid until the next replayed step; at most ``MAX_GRAPHS`` are captured,
-    other shapes run launch by launch."""
+    ``rows`` tokens each (the configured portion size) and want nothing or their last place; then at most one
+    sequence brings the end of its prompt (2 to ``rows`` - 1 tokens, wanting nothing or its last place); every
+    other sequence brings one decoded token and wants it.  Between two such steps only device metadata differs
+    (token ids, positions, block tables, and where a tail ends), so the launches of the whole model are replayed
+    instead of issued one by one; at 2,048 rows of the 1B sizes that takes the step from 4.6 to 3.9 ms, and a step
+    of 100 rows, which the host needs 2.8 ms to issue, takes the 1.2 ms of its kernels.  One graph per (portions,
+    tail rows rounded up to 64, 128, ... ``rows``, decode rows rounded up to a power of two, whether any portion
+    wants its last place, block-table width rounded up to a power of two): the width bounds the context, and with
+    it the split count that the decode rows' attention is captured with, as for the decode graphs.  Rows that pad
+    the tail and the decode part point at the scratch page and the scratch state slot.  If one portion wants its
+    last place the last rows of all portions go through the head and the caller gets the ones it asked for.  The
+    graphs share one memory pool (they never run at the same time), so the returned logits are valid until the
+    next replayed step; at most ``MAX_GRAPHS`` are captured, other shapes run launch by launch."""
 
-    MAX_GRAPHS = 48
+    MAX_GRAPHS = 96
 
     def __init__(self, stepper: Stepper, rows: int, max_sequence_length: int, max_decodes: int, max_portions: int = 1):
         self.stepper = stepper
@@ -350,7 +389,7 @@ class ChunkGraphs:
         self.max_portions = max(1, max_portions)
         page = stepper.cache.page_size
         self.columns = max(1, -(-min(max_sequence_length, stepper.max_positions) // page))
-        self.graphs: Dict[Tuple[int, int, bool, int], _ChunkGraph] = {}
+        self.graphs: Dict[Tuple[int, int, int, bool, int], _ChunkGraph] = {}
         self.pool = None
         self.replays = 0
         self.kernels_replayed = 0
@@ -365,43 +404,69 @@ class ChunkGraphs:
             count += 1
         return count
 
-    def _key(self, entries: Sequence[StepEntry], portions: int) -> Tuple[int, int, bool, int]:
+    def _tail(self, entries: Sequence[StepEntry], portions: int) -> int:
+        """Tokens of the entry behind the full portions if it is the end of a prompt (0 if there is none)."""
+        if portions >= len(entries):
+            return 0
+        entry = entries[portions]
+        n = len(entry.tokens)
+        if 1 < n < self.rows and list(entry.want) in ([], [n - 1]):
+            return n
+        return 0
+
+    def _tail_rows(self, n: int) -> int:
+        """Rows that a tail of ``n`` tokens takes in its graph: more than ``n`` (a padding row at least)."""
+        if n == 0:
+            return 0
+        bucket = 64
+        while bucket <= n and bucket < self.rows:
+            bucket <<= 1
+        return min(bucket, self.rows)
+
+    def _key(self, entries: Sequence[StepEntry], portions: int, tail: int) -> Tuple[int, int, int, bool, int]:
         cache = self.stepper.cache
-        decodes = len(entries) - portions
+        decodes = len(entries) - portions - (1 if tail else 0)
         bucket = 0 if decodes == 0 else min(_next_pow2(decodes), max(self.max_decodes, decodes))
-        pages = -(-max(cache.length(e.request) + len(e.tokens) for e in entries) // cache.page_size)
+        tail_rows = self._tail_rows(tail)
+        pages = -(-max([cache.length(e.request) + len(e.tokens) for e in entries] + [tail_rows]) // cache.page_size)
         columns = min(self.columns, max(8, _next_pow2(pages)))
-        return portions, bucket, any(e.want for e in entries[:portions]), columns
+        return portions, tail_rows, bucket, any(e.want for e in entries[:portions]), columns
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not self.safe or not entries:
             return False
         portions = self._portions(entries)
-        if portions == 0 or portions > self.max_portions or len(entries) - portions > self.max_decodes:
+        tail = self._tail(entries, portions)
+        first_decode = portions + (1 if tail else 0)
+        if first_decode == 0 or portions > self.max_portions or len(entries) - first_decode > self.max_decodes:
             return False
-        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries[portions:]):
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries[first_decode:]):
             return False
         cache = self.stepper.cache
         limit = self.columns * cache.page_size
         if not all(cache.is_live(e.request) and cache.length(e.request) + len(e.tokens) <= limit for e in entries):
             return False
-        return len(self.graphs) < self.MAX_GRAPHS or self._key(entries, portions) in self.graphs
+        if self._tail_rows(tail) > limit:
+            return False
+        return len(self.graphs) < self.MAX_GRAPHS or self._key(entries, portions, tail) in self.graphs
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         stepper, cache = self.stepper, self.stepper.cache
         stepper._validate(entries)
         rows, portions = self.rows, self._portions(entries)
-        decodes = len(entries) - portions
-        key = self._key(entries, portions)
-        _, bucket, wants_last, columns = key
+        tail = self._tail(entries, portions)
+        first_decode = portions + (1 if tail else 0)
+        decodes = len(entries) - first_decode
+        key = self._key(entries, portions, tail)
+        _, tail_rows, bucket, wants_last, columns = key
         graph = self.graphs.get(key)
         if graph is None:
             if self.pool is None:
                 self.pool = torch.cuda.graph_pool_handle()
-            graph = _ChunkGraph(stepper, rows, portions, bucket, wants_last, columns, self.pool)
+            graph = _ChunkGraph(stepper, rows, portions, bucket, wants_last, columns, self.pool, tail=tail_rows)
             self.graphs[key] = graph
-        prompt_rows = portions * rows
-        total, seqs = prompt_rows + bucket, portions + bucket
+        total, seqs, prompt_rows = graph.total, graph.seqs, graph.prompt_rows
+        full_rows = portions * rows
         begins = [cache.length(e.request) for e in entries]
         for entry in entries:
             cache.extend(entry.request, len(entry.tokens))
@@ -411,24 +476,40 @@ class ChunkGraphs:
             graph.host_events[index].synchronize()
         host = graph.hosts[index].numpy()
         slots = [cache.slot(e.request) for e in entries]
-        host[prompt_rows:total] = 0
-        host[total + prompt_rows:2 * total] = 0
+        # sequence slots of the graph: the portions, (the tail, its padding,) the decode rows; entries skip the padding
+        seq_of_entry = list(range(first_decode)) + [first_decode + (1 if tail else 0) + j for j in range(decodes)]
+        host[full_rows:total] = 0
+        host[total + full_rows:2 * total] = 0
         host[2 * total:2 * total + seqs] = 0
         host[2 * total + seqs:2 * total + 2 * seqs] = cache.scratch_slot
         for k in range(portions):
             host[k * rows:(k + 1) * rows] = np.asarray(entries[k].tokens, dtype=np.int32)
             host[total + k * rows:total + (k + 1) * rows] = np.arange(begins[k], begins[k] + rows, dtype=np.int32)
+        if tail:
+            host[full_rows:full_rows + tail] = np.asarray(entries[portions].tokens, dtype=np.int32)
+            host[total + full_rows:total + full_rows + tail] = np.arange(begins[portions], begins[portions] + tail,
+                                                                         dtype=np.int32)
+            host[total + full_rows + tail:total + prompt_rows] = np.arange(tail_rows - tail, dtype=np.int32)   # padding
+            seq_of_row = host[graph.at_seq_of_row:graph.at_row_start]
+            seq_of_row[full_rows:full_rows + tail] = portions
+            seq_of_row[full_rows + tail:prompt_rows] = portions + 1
+            row_start = host[graph.at_row_start:graph.at_want]
+            row_start[portions] = full_rows
+            row_start[portions + 1] = full_rows + tail
+            host[graph.at_want + graph.tail_want] = full_rows + tail - 1
         if decodes:
-            host[prompt_rows:prompt_rows + decodes] = [int(e.tokens[0]) for e in entries[portions:]]
-            host[total + prompt_rows:total + prompt_rows + decodes] = begins[portions:]
-        host[2 * total:2 * total + portions + decodes] = begins
-        host[2 * total + seqs:2 * total + seqs + portions + decodes] = slots
-        used = min(graph.columns, -(-max(b + len(e.tokens) for b, e in zip(begins, entries)) // cache.page_size))
+            host[prompt_rows:prompt_rows + decodes] = [int(e.tokens[0]) for e in entries[first_decode:]]
+            host[total + prompt_rows:total + prompt_rows + decodes] = begins[first_decode:]
+        for k, seq in enumerate(seq_of_entry):
+            host[2 * total + seq] = begins[k]
+            host[2 * total + seqs + seq] = slots[k]
+        used = min(graph.columns, -(-max([b + len(e.tokens) for b, e in zip(begins, entries)] + [tail_rows])
+                                    // cache.page_size))
         graph.dev.copy_(graph.hosts[index], non_blocking=True)
         for k, group_index in enumerate(graph.paged):
             table = graph.host_tables[index][k].numpy()
-            table[:portions + decodes, :used] = cache.block_table_rows(group_index, slots, used)
-            table[portions + decodes:, :used] = 0
+            table[:, :used] = 0
+            table[seq_of_entry, :used] = cache.block_table_rows(group_index, slots, used)
             graph.dev_tables[k][:, :used].copy_(graph.host_tables[index][k][:, :used], non_blocking=True)
         copied = torch.cuda.Event()
         copied.record()
@@ -441,8 +522,13 @@ class ChunkGraphs:
         self.kernels_replayed += graph.kernels_per_replay
         if graph.logits is None:
             return None
+        # the head's rows: the portions' last places (if any portion wants one), the tail's, the decode rows'
         head_portions = portions if wants_last else 0
-        picked = [k for k in range(head_portions) if entries[k].want] + list(range(head_portions, head_portions + decodes))
+        picked = [k for k in range(head_portions) if entries[k].want]
+        if tail and entries[portions].want:
+            picked.append(head_portions)
+        behind = head_portions + (1 if tail else 0)
+        picked += list(range(behind, behind + decodes))
         if not picked:
             return None
         if picked == list(range(picked[0], picked[0] + len(picked))):

@@ -220,8 +220,11 @@ class Scheduler:
                 budget -= count
         if len(self.running) > 1:
             self.running.rotate(-1)
-        # prompt portions first, then decode rows (src/engine/batch.rs:355-428), order otherwise kept
-        batch.sort(key=lambda s: s.is_decode)
+        # prompt portions first, then decode rows (src/engine/batch.rs:355-428); among the portions the full ones
+        # first (a step of full portions, one shorter one and decode rows is a shape that replays as a graph); order
+        # otherwise kept
+        full = self.config.prefill_chunk_tokens
+        batch.sort(key=lambda s: (s.is_decode, len(s.tokens) != full))
         return batch
 
     def step(self) -> StepResult:

@@ -65,7 +65,9 @@ def _code(dtype: torch.dtype) -> int:
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream's handle.  (``torch.cuda.current_stream()`` builds a Python stream object through several
+    layers on every call: a step launched kernel by kernel spent a seventh of its host time there.)"""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
@@ -579,10 +581,17 @@ def skinny_tcgen05_supported(rows: int, out_features: int, in_features: int, epi
                                                                           _i32(in_features), _i32(epilogue)))
 
 
+_skinny_sums_shapes: Dict[int, tuple] = {}
+
+
 def skinny_tcgen05_sums_shape(out_features: int):
     """Shape of the sums-of-squares array that a product of this width leaves with ``prepare``."""
-    lib = load_library("skinny_tcgen05")
-    return (int(lib.tb_skinny_tcgen05_sums_tiles(_i32(out_features))), int(lib.tb_skinny_tcgen05_sums_stride()))
+    shape = _skinny_sums_shapes.get(out_features)
+    if shape is None:
+        lib = load_library("skinny_tcgen05")
+        shape = (int(lib.tb_skinny_tcgen05_sums_tiles(_i32(out_features))), int(lib.tb_skinny_tcgen05_sums_stride()))
+        _skinny_sums_shapes[out_features] = shape
+    return shape
 
 
 def skinny_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor], epilogue: int = EPI_BF16,
