@@ -186,7 +186,9 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 }
 
 
-template <int D, int BN>
+// SPLIT: tiles shared by gridDim.y CTAs (the code that leaves and adds partial rows costs the unsplit kernel 2-6 %
+// of its time through its registers alone, so it is an instantiation of its own).
+template <int D, int BN, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, (Shape<D, BN>::kCtasPerSm))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const TcAttnParams p) {
     using Tiles = Shape<D, BN>;
@@ -238,7 +240,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     // The tile's key blocks, cut into gridDim.y contiguous runs: a step whose tiles are too few to fill the GPU (a
     // 512-token portion late in a long prompt) gives each tile to several CTAs, which leave unnormalised partial
     // rows; the one that finishes last adds them in the order of the runs.  A run may be empty (early tiles).
-    const int key_splits = gridDim.y, key_split = blockIdx.y;
+    const int key_splits = SPLIT ? (int)gridDim.y : 1, key_split = SPLIT ? (int)blockIdx.y : 0;
     const int tile_blocks = key_hi / BN - key_lo / BN + 1;
     const int first_of_run = key_split * tile_blocks / key_splits;
     const int kb_first = key_lo / BN + first_of_run;
@@ -539,7 +541,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         if (ok && n_blocks > 0 && !mbar_wait(o_full, (n_blocks - 1) & 1, &abort_flag)) ok = false;
         const int qpos = pos >= 0 ? fr / p.group : 0, g = pos >= 0 ? fr - qpos * p.group : 0;
         __nv_bfloat16* dst = p.out + (int64_t)(first_row + qpos) * p.out_stride + (int64_t)(kv_head * p.group + g) * D;
-        if (key_splits == 1) {
+        if (!SPLIT) {
             if (ok) {
                 tc_fence_after();
                 const float inv = 1.0f / fmaxf(l, 1.0e-8f);
@@ -672,7 +674,7 @@ int launch_attention(const void* cache, int cache_pages, int num_seqs, int max_r
                      cudaStream_t stream) {
     const CUtensorMap* map = cache_map_for(cache, cache_pages, p.num_kv_heads, p.page_size, BN, D);
     if (map == nullptr) return TB_ERR_BAD_SIZE;
-    auto kernel = attention_tcgen05_kernel<D, BN>;
+    auto kernel = key_splits > 1 ? attention_tcgen05_kernel<D, BN, true> : attention_tcgen05_kernel<D, BN, false>;
     const size_t smem = Shape<D, BN>::kSmemBytes;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
