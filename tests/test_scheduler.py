@@ -105,6 +105,23 @@ def test_decode_rows_come_before_prompt_portions_in_the_budget():
     assert [len(t) for _, _, t, _ in batch][-1] == 1 and batch[-1][0] == 0
 
 
+def test_full_portions_stand_before_shorter_ones_in_the_lowered_batch():
+    """Under one budget a step may carry the end of one prompt, full portions of others and decode rows: the full
+    portions come first, then the shorter one, then the decode rows (the shape that replays as one graph)."""
+    config = EngineConfig(max_queue=8, max_running=4, max_batch_tokens=32, prefill_chunk_tokens=8,
+                          kv_capacity_tokens=512, max_sequence_length=512)
+    s, fake = make(config)
+    s.add_request([1, 2], SamplingParams(max_tokens=20, ignore_eos=True, **GREEDY))
+    s.step()                                    # request 0 is now decoding
+    s.add_request(list(range(13)), SamplingParams(max_tokens=2, ignore_eos=True, **GREEDY))     # 8 + 5
+    s.add_request(list(range(30)), SamplingParams(max_tokens=2, ignore_eos=True, **GREEDY))
+    s.step()
+    s.step()                                    # request 1 brings its last five tokens, request 2 a full portion
+    batch = fake.batches[-1]
+    assert [(rid, len(tokens)) for rid, _, tokens, _ in batch] == [(2, 8), (1, 5), (0, 1)]
+    assert [want for _, _, _, want in batch] == [[], [4], [0]]
+
+
 def test_rotation_shares_a_tight_budget():
     config = EngineConfig(max_queue=8, max_running=3, max_batch_tokens=8, prefill_chunk_tokens=8,
                           kv_capacity_tokens=512, max_sequence_length=512)
