@@ -330,7 +330,9 @@ def run_ours(args):
         return (numbers["weight_bytes"] + batch * ctx * numbers["kv_bytes_per_token"]) / (ms / 1e3) / 1e9 / pk["hbm_gbs"]
 
     # ---------------------------------------------------------------- end to end through the scheduler
-    params = SamplingParams(max_tokens=args.steps + args.warmup + 4, temperature=0.0, ignore_eos=True)
+    # (every request must still be decoding at the end of the timed steps: the first ones start decoding while the
+    # last prompts are still being prefilled, two to a step)
+    params = SamplingParams(max_tokens=args.steps + args.warmup + 4 + args.batch, temperature=0.0, ignore_eos=True)
     for _ in range(args.batch):
         llm.scheduler.add_request(prompt(), params)
     while any(r.computed_tokens < len(r.prompt) for r in llm.scheduler.requests.values()) or llm.scheduler.waiting:
