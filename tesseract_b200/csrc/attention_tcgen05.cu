@@ -416,6 +416,79 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             if (!mbar_wait(s_full, j & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
             const bool full = all_rows && p.window <= 0 && key0 + BN - 1 <= warp_lo_pos;   // uniform across the warp
+            if (full && j > 0) {
+                // One pass for a block that needs no mask: its probabilities are computed against the maximum that
+                // earlier blocks left, while the block's own maximum is followed on the side.  Only if that exceeds m
+                // by more than 2^8 in some row of the warp (rare after a row's first block) is the work thrown away
+                // and the block done again by the two passes below, from the scores that are still in tensor memory:
+                // either way the probabilities are those of the two passes, bit for bit.  The first chunks wait in
+                // registers until the product before this one has read the P tile.
+                uint32_t ca[32], cb[32], held[32];
+                float mx[4] = {kMasked, kMasked, kMasked, kMasked};
+                uint64_t ls[4] = {0, 0, 0, 0};
+                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m, -m);
+                auto maxima = [&](const uint32_t (&chunk)[32]) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1]));
+                };
+                auto exps = [&](const uint32_t (&chunk)[32], uint32_t* packed) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float t0, t1;
+                        unpack2(fma2(pack2(__uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1])), scale2, neg_m2),
+                                t0, t1);
+                        const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                        ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+                        packed[i >> 1] = pack_bf16(p0, p1);
+                    }
+                };
+                auto store = [&](const uint32_t* packed, int c) {
+                    unsigned char* dst = smem + Tiles::kQBytes + (c >> 1) * kTileBytes;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<uint4*>(dst + sw128(r, (c & 1) * 4 + q4)) =
+                            make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                };
+                constexpr int kLast = BN / 32 - 1;                 // the chunk whose maxima decide
+                tmem_load_32_nowait(tmem_s + lane_base, ca);
+                tmem_wait_ld();
+                tmem_load_32_nowait(tmem_s + lane_base + 32, cb);
+                maxima(ca);
+                exps(ca, held);
+                tmem_wait_ld();
+                if (BN == 128) {
+                    tmem_load_32_nowait(tmem_s + lane_base + 64, ca);
+                    maxima(cb);
+                    exps(cb, held + 16);
+                }
+                if (!mbar_wait(o_full, (j - 1) & 1, &abort_flag)) { ok = false; break; }
+                store(held, 0);
+                if (BN == 128) {
+                    store(held + 16, 1);
+                    tmem_wait_ld();
+                    tmem_load_32_nowait(tmem_s + lane_base + 96, cb);
+                    maxima(ca);
+                    exps(ca, held);
+                    store(held, 2);
+                    tmem_wait_ld();
+                }
+                maxima(cb);
+                const float seen = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+                if (!__any_sync(0xffffffffu, seen > m + 8.0f)) {
+                    tc_fence_before();
+                    mbar_arrive(s_free);               // S has been read: the issuer may start the next block's scores
+                    exps(cb, held);
+                    store(held, kLast);
+                    float lo_sum, hi_sum;
+                    unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), lo_sum, hi_sum);
+                    l += lo_sum + hi_sum;
+                    fence_async_smem();
+                    tc_fence_before();
+                    mbar_arrive(p_ready);
+                    continue;
+                }
+            }
             // Pass 1: the row's maximum over the block, 32 columns at a time (the next chunk is in flight while one
             // is reduced; four partial maxima keep the dependency chains short).
             uint32_t ca[32], cb[32];
