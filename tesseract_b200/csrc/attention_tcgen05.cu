@@ -8,6 +8,8 @@
 //                      accumulator in tensor memory (128 columns)
 //   softmax            four warps, one thread per row: tcgen05.ld of the row, scale, mask, running maximum,
 //                      2^x, 32-bit row sum, probabilities rounded to bfloat16 into a swizzled P tile in shared memory
+//                      (a block that needs no mask is read once, against the maximum that earlier blocks left; the
+//                      row is read twice, maximum first, only where that maximum is exceeded by more than 2^8)
 //   O += P . V         tcgen05.mma, M128 x N64 x K128, P K-major, V MN-major (the cache's [key][dim] rows as they
 //                      are), accumulating in 64 further columns of tensor memory; when a row's maximum jumps by
 //                      more than 2^8 its thread rescales that row of O in place (tcgen05.ld / tcgen05.st)
@@ -345,8 +347,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             const uint64_t k_desc0 = desc_sw128(kv_tiles, 1);
             const uint64_t v_desc0 = desc_sw128(kv_tiles + kKVTileBytes, kKVHalfBytes >> 4);
             constexpr uint32_t kStageStep = (2 * kKVTileBytes) >> 4;          // a ring stage further, in the field's units
-            auto issue_qk = [&](int s, uint32_t parity) {
-                if (!mbar_wait(k_full + 8 * s, parity, &abort_flag)) return false;
+            // (a wait costs this thread some 200 cycles even on a barrier that is long complete, so the keys and
+            // values, which arrive far ahead, are waited for BEFORE the barrier that the softmax warps are about
+            // to complete: their answer is then the only one on the path from the softmax to the product)
+            auto issue_qk = [&](int s) {
                 tc_fence_after();
                 const uint64_t k_desc = k_desc0 + (uint32_t)s * kStageStep;
 #pragma unroll
@@ -358,25 +362,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 }
                 umma_commit(s_full);
                 umma_commit(k_empty + 8 * s);     // the key stage may be refilled once these products are done
-                return true;
             };
             // ring cursors of the block whose scores are issued (qs, q_parity) and of the one whose P.V is (s, parity)
             int qs = 0, s = 0;
             uint32_t q_parity = 0, parity = 0;
             auto next_q = [&]() { if (++qs == STAGES) { qs = 0; q_parity ^= 1; } };
-            bool ok = n_blocks == 0 || issue_qk(qs, q_parity);
+            bool ok = n_blocks == 0 || mbar_wait(k_full + 8 * qs, q_parity, &abort_flag);
+            if (ok && n_blocks > 0) issue_qk(qs);
             next_q();
             for (int j = 0; j < n_blocks && ok; ++j) {
                 // as soon as the softmax warps hold S_j in registers the next block's scores may overwrite it
                 if (j + 1 < n_blocks) {
+                    if (!mbar_wait(k_full + 8 * qs, q_parity, &abort_flag)) { ok = false; break; }
                     if (!mbar_wait(s_free, j & 1, &abort_flag)) { ok = false; break; }
-                    ok = issue_qk(qs, q_parity);
+                    issue_qk(qs);
                     next_q();
-                    if (!ok) break;
                 }
                 // P_j is in shared memory (and O has been rescaled if the maximum jumped): O += P_j V_j
-                if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * s, parity, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(p_ready, j & 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t v_desc = v_desc0 + (uint32_t)s * kStageStep;
 #pragma unroll
