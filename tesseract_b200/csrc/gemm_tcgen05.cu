@@ -11,6 +11,8 @@
 //     a time, and stores bfloat16 (or 32-bit) rows, or applies SwiGLU to a weight whose rows interleave eight
 //     gate rows and their eight up rows: out[m, j] = round(silu(gate_j) * up_j) on the unrounded accumulators
 //     (the reference multiplies rounded projections, src/cuda/kernels.rs:191-208; here one rounding fewer).
+// Products of more than 128 rows take the pair form further down: two CTAs of a cluster on one 256 x 256 tile
+// (tcgen05.mma.cta_group::2), each bringing half of the operands.
 // Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by the TMA unit and never stored.
 // Every wait on an mbarrier is bounded: a wait that runs out sets *error, tells the other roles to stop, and the
 // CTA still frees its tensor memory before it returns.
@@ -238,6 +240,168 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The pair form for products of more than 128 rows: two CTAs on neighbouring SMs (a cluster of two) compute one
+// 256 x 256 tile with tcgen05.mma.cta_group::2.  Each CTA brings its own 128 rows of A and its own 128 of the
+// tile's 256 rows of W (32 KiB a stage instead of 48: a third less traffic from L2 per product, which is what
+// bounds the single-CTA form at this size) and holds its 128 rows of both accumulators in its own tensor memory;
+// one thread of the even CTA issues the products for both and its commits arrive in both CTAs.
+//   full[s]       in the even CTA only: its producer announces both CTAs' bytes, both CTAs' copies count on it
+//   empty[s]      in each CTA (commit to both): that CTA's producer may refill the stage
+//   acc_full[b]   in each CTA (commit to both): that CTA's epilogue warps may read accumulator b
+//   acc_empty[b]  in the even CTA only: eight arrivals, one per epilogue warp of either CTA
+// No CTA leaves before both are done (the even CTA's products read the odd CTA's shared memory, the odd CTA's
+// warps arrive on the even CTA's barriers).
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairStageBytes = 2 * kATileBytes;           // A rows and W rows of this CTA: 16 KiB each
+constexpr uint32_t kPairTmemColumns = 512;                      // two accumulators of 256 columns
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p) {
+    constexpr int STAGES = kPairStages, BN = 256, PM = 256;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // every CTA's dynamic shared memory starts at the same offset, so the rounded-up tiles do too in both CTAs
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();                     // 0: issues the products; 1: its partner
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int m_tiles = (p.M + PM - 1) / PM, n_tiles = (p.N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = acc_full0 + 16;
+    const uint32_t tiles = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 8);      // one arrival per epilogue warp of both CTAs
+        }
+        mbar_fence_init();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) tmem_pair_alloc(smem_u32(&tmem_base_slot), kPairTmemColumns);
+    tc_fence_before();
+    __syncthreads();
+    cluster_barrier_all();                          // the partner's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer (one in each CTA)
+        const uint32_t full_in_even = cluster_shared_address(full0, 0);
+        int s = 0;
+        uint32_t parity = 1;
+        for (int t = pair; t < total_tiles && !abort_flag; t += pairs) {
+            const int m0 = (t % m_tiles) * PM + (int)rank * BM, n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(empty0 + 8 * s, parity, &abort_flag)) {
+                    abort_flag = 1;
+                    atomicExch(p.error, 11);
+                    break;
+                }
+                if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
+                const uint32_t a_dst = tiles + s * kPairStageBytes;
+                tma_load_2d_pair(a_dst, &map_a, full_in_even + 8 * s, kb * BK, m0);
+                tma_load_2d_pair(a_dst + kATileBytes, &map_b, full_in_even + 8 * s, kb * BK, n0);
+                if (++s == STAGES) {
+                    s = 0;
+                    parity ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------------------------------------------------------- MMA issuer (the even CTA's, for both)
+        constexpr uint32_t idesc = umma_idesc_bf16(PM, BN);
+        const uint64_t desc_a0 = umma_desc_k_sw128(tiles), desc_b0 = umma_desc_k_sw128(tiles + kATileBytes);
+        int s = 0, i = 0;
+        uint32_t parity = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += pairs, ++i) {
+            const int buf = i & 1;
+            if (!mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_flag)) {
+                abort_flag = 1;
+                atomicExch(p.error, 14);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * BN;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(full0 + 8 * s, parity, &abort_flag)) {
+                    abort_flag = 1;
+                    atomicExch(p.error, 12);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t desc_a = umma_desc_advance(desc_a0, s * kPairStageBytes);
+                const uint64_t desc_b = umma_desc_advance(desc_b0, s * kPairStageBytes);
+                umma_pair_bf16(acc, desc_a, desc_b, idesc, kb != 0);
+#pragma unroll
+                for (int kk = 1; kk < BK / 16; ++kk)
+                    umma_pair_bf16_add(acc, umma_desc_advance(desc_a, kk * 32), umma_desc_advance(desc_b, kk * 32), idesc);
+                umma_pair_commit(empty0 + 8 * s, 3);      // both CTAs' stage s is free once these products have read it
+                if (++s == STAGES) {
+                    s = 0;
+                    parity ^= 1;
+                }
+            }
+            if (ok) umma_pair_commit(acc_full0 + 8 * buf, 3);
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- epilogue (this CTA's 128 rows)
+        const int quarter = warp & 3;
+        const uint32_t acc_empty_in_even = cluster_shared_address(acc_empty0, 0);
+        int i = 0;
+        for (int t = pair; t < total_tiles; t += pairs, ++i) {
+            const int buf = i & 1;
+            const int m0 = (t % m_tiles) * PM + (int)rank * BM, n0 = (t / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            if (!mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, &abort_flag)) {
+                abort_flag = 1;
+                atomicExch(p.error, 13);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t lanes = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                uint32_t acc0[32], acc1[32];
+                tmem_load_32(lanes + c * 32, acc0);
+                tmem_load_32(lanes + c * 32 + 32, acc1);
+                tmem_wait_ld();
+                store_chunk<EPI>(p, row, n0 + c * 32, acc0);
+                store_chunk<EPI>(p, row, n0 + c * 32 + 32, acc1);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_in_even + 8 * buf);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_barrier_all();                          // both CTAs are done with each other's memory and barriers
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_pair_dealloc(tmem_base, kPairTmemColumns);
+    }
+}
+
 }  // namespace
 
 // 1 if the kernel takes these sizes.  K and the row strides must be multiples of 8 (16-byte TMA strides), N of 8
@@ -295,5 +459,49 @@ TB_EXPORT int tb_gemm_tcgen05(const void* a, int64_t a_stride, const void* w, in
     else return TB_ERR_BAD_SIZE;
 #undef TB_LAUNCH
 #undef TB_LAUNCH_BN
+    return tb_launch_status();
+}
+
+// The pair form (see gemm_pair_tcgen05_kernel): the same contract, for M > 128.
+TB_EXPORT int tb_gemm_pair_tcgen05(const void* a, int64_t a_stride, const void* w, int64_t w_stride, void* out,
+                                   int64_t out_stride, int M, int N, int K, int epilogue, int* error,
+                                   cudaStream_t stream) {
+    if (!tb_gemm_tcgen05_supported(M, N, K, epilogue)) return TB_ERR_BAD_SIZE;
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16 != 0 || a_stride % 8 != 0 || w_stride % 8 != 0 ||
+        out_stride % 8 != 0)
+        return TB_ERR_BAD_ALIGN;
+    CUtensorMap map_a, map_b;
+    if (int status = make_map_2d(&map_a, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_stride, BM)) return status;
+    if (int status = make_map_2d(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_stride, 128)) return status;
+    GemmParams p;
+    p.out = out;
+    p.out_stride = out_stride;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.error = error;
+    const int total_tiles = ((N + 255) / 256) * ((M + 255) / 256);
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 1) sms = 2;
+    }
+    const int pairs = total_tiles < sms / 2 ? total_tiles : sms / 2;
+    dim3 grid(2 * pairs);
+    const size_t smem = (size_t)kPairStages * kPairStageBytes + 1024;
+#define TB_LAUNCH_PAIR(E)                                                                                     \
+    {                                                                                                         \
+        cudaError_t err = cudaFuncSetAttribute(gemm_pair_tcgen05_kernel<E>,                                   \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        if (err != cudaSuccess) return (int)err;                                                              \
+        err = tb_launch_pdl(gemm_pair_tcgen05_kernel<E>, grid, dim3(kThreads), smem, stream, map_a, map_b, p); \
+        if (err != cudaSuccess) return (int)err;                                                              \
+    }
+    if (epilogue == EPI_BF16) TB_LAUNCH_PAIR(EPI_BF16)
+    else if (epilogue == EPI_SWIGLU) TB_LAUNCH_PAIR(EPI_SWIGLU)
+    else if (epilogue == EPI_F32) TB_LAUNCH_PAIR(EPI_F32)
+    else return TB_ERR_BAD_SIZE;
+#undef TB_LAUNCH_PAIR
     return tb_launch_status();
 }

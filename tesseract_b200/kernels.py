@@ -552,11 +552,16 @@ def gemm_tcgen05_supported(rows: int, out_features: int, in_features: int, epilo
                                                                       _i32(in_features), _i32(epilogue)))
 
 
-def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16) -> torch.Tensor:
+GEMM_PAIR_MIN_ROWS = 129       # from here on two CTAs share a 256 x 256 tile (tcgen05.mma.cta_group::2)
+
+
+def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16,
+                 pair: Optional[bool] = None) -> torch.Tensor:
     """``out = a @ weight^T`` on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     ``EPI_BF16`` / ``EPI_F32`` store ``[M, N]``; ``EPI_SWIGLU`` takes a weight whose rows interleave eight gate rows
-    and their eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``.
+    and their eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``.  ``pair``: CTA pairs on 256 x 256
+    tiles instead of single CTAs on 128 x 256 (default: from ``GEMM_PAIR_MIN_ROWS`` rows on).
     """
     _cuda(a, weight, out)
     m, k = a.shape
@@ -567,9 +572,12 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     _need(out.shape == (m, width), "gemm_tcgen05 out shape")
     _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemm_tcgen05 out dtype")
     lib = load_library("gemm_tcgen05")
-    _check(lib.tb_gemm_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
-                               _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
-                               _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    if pair is None:
+        pair = m >= GEMM_PAIR_MIN_ROWS
+    entry = lib.tb_gemm_pair_tcgen05 if pair else lib.tb_gemm_tcgen05
+    _check(entry(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
+                 _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
+                 _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
     return out
 
 
