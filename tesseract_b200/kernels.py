@@ -556,12 +556,13 @@ GEMM_PAIR_MIN_ROWS = 129       # from here on two CTAs share a 256 x 256 tile (t
 
 
 def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16,
-                 pair: Optional[bool] = None) -> torch.Tensor:
+                 pair: Optional[bool] = None, tile_width: int = 0) -> torch.Tensor:
     """``out = a @ weight^T`` on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     ``EPI_BF16`` / ``EPI_F32`` store ``[M, N]``; ``EPI_SWIGLU`` takes a weight whose rows interleave eight gate rows
     and their eight up rows and stores ``silu(gate) * up`` as ``[M, N / 2]``.  ``pair``: CTA pairs on 256 x 256
-    tiles instead of single CTAs on 128 x 256 (default: from ``GEMM_PAIR_MIN_ROWS`` rows on).
+    tiles instead of single CTAs on 128 x 256 (default: from ``GEMM_PAIR_MIN_ROWS`` rows on); ``tile_width``: the
+    width of the pairs' tiles (256 or 448; 0: the one whose tiles fill the pairs in the cheaper rounds).
     """
     _cuda(a, weight, out)
     m, k = a.shape
@@ -574,10 +575,14 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     lib = load_library("gemm_tcgen05")
     if pair is None:
         pair = m >= GEMM_PAIR_MIN_ROWS
-    entry = lib.tb_gemm_pair_tcgen05 if pair else lib.tb_gemm_tcgen05
-    _check(entry(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
-                 _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
-                 _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    if pair:
+        _check(lib.tb_gemm_pair_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
+                                        _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
+                                        _i32(tile_width), _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+        return out
+    _check(lib.tb_gemm_tcgen05(_ptr(a), _i64(a.stride(0)), _ptr(weight), _i64(weight.stride(0)), _ptr(out),
+                               _i64(out.stride(0)), _i32(m), _i32(n), _i32(k), _i32(epilogue),
+                               _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
     return out
 
 

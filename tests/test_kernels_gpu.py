@@ -659,30 +659,32 @@ def test_decode_linear_refuses_other_sizes():
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (1, 256, 64), (130, 264, 72),
                                      (2048, 3072, 2048), (333, 1000, 520), (77, 16, 8), (64, 1000, 520),
                                      (96, 40000, 1024)])
-@pytest.mark.parametrize("pair", [False, True])
-def test_gemm_tcgen05(m, n, k, pair):
-    """Single CTAs on 128 x 256 tiles and CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2), each at every size:
-    fewer rows than a tile, edges in every dimension, more tiles than CTAs (both accumulators in turn), a ring that
-    turns many times."""
+@pytest.mark.parametrize("form", ["single", "pair", "pair448"])
+def test_gemm_tcgen05(m, n, k, form):
+    """Single CTAs on 128 x 256 tiles, CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2) and pairs on 256 x 448
+    tiles (two products a step into one accumulator), each at every size: fewer rows than a tile, edges in every
+    dimension, more tiles than CTAs (both accumulators in turn), a ring that turns many times."""
     from tesseract_b200 import kernels
+
+    pair = dict(pair=form != "single", tile_width={"single": 0, "pair": 256, "pair448": 448}[form])
 
     torch.manual_seed(m + n + k)
     a = torch.randn(m, k).to(torch.bfloat16)
     w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16)
     want = a.double() @ w.double().T
     out32 = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
-    kernels.gemm_tcgen05(dev(a), dev(w), out32, epilogue=kernels.EPI_F32, pair=pair)
+    kernels.gemm_tcgen05(dev(a), dev(w), out32, epilogue=kernels.EPI_F32, **pair)
     assert kernels.tcgen05_error() == 0, "a bounded wait inside the kernel ran out"
     torch.testing.assert_close(out32.cpu().double(), want, rtol=1e-4, atol=1e-4)
     out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    kernels.gemm_tcgen05(dev(a), dev(w), out, pair=pair)
+    kernels.gemm_tcgen05(dev(a), dev(w), out, **pair)
     assert kernels.tcgen05_error() == 0
     torch.testing.assert_close(out.cpu().double(), want, rtol=1e-2, atol=1e-2)
     if n % 16 == 0:
         gate, up = w[: n // 2], w[n // 2:]
         merged = torch.stack([gate.view(n // 16, 8, k), up.view(n // 16, 8, k)], dim=1).reshape(n, k).contiguous()
         act = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
-        kernels.gemm_tcgen05(dev(a), dev(merged), act, epilogue=kernels.EPI_SWIGLU, pair=pair)
+        kernels.gemm_tcgen05(dev(a), dev(merged), act, epilogue=kernels.EPI_SWIGLU, **pair)
         assert kernels.tcgen05_error() == 0
         g, u = a.double() @ gate.double().T, a.double() @ up.double().T
         torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
