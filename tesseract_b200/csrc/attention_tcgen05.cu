@@ -410,6 +410,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
         const int warp_first = r0 + warp * 32;
         const bool all_rows = warp_first + 32 <= n_rows;
         const int warp_lo_pos = begin + warp_first / p.group;
+        const int warp_hi_pos = begin + (warp_first + 31) / p.group;    // (of a warp whose rows are all there)
         // The running output lives in tensor memory (P.V accumulates there).  m is the maximum that the stored
         // probabilities and O are scaled by; it is only raised (and O rescaled) when a block's maximum exceeds it
         // by more than 2^8, which keeps every probability at or below 256 and makes the rescaling rare.
@@ -493,6 +494,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                     continue;
                 }
             }
+            // The two passes, chunk by chunk.  A warp's rows are a few neighbouring positions, so of the block on the
+            // diagonal most 32-key chunks lie wholly before them (no mask needed: the short path) or wholly behind
+            // them (no score counts: zeros, nothing computed), and only the chunk or two that the rows' last keys
+            // (and, with a window, their first) fall into are masked element by element, which costs four times
+            // the instructions: a whole block done that way took as long as three and a half unmasked ones.
+            enum { kOpen = 0, kMaskedChunk = 1, kDead = 2 };
+            auto chunk_mode = [&](int c) {                          // uniform across the warp
+                if (full) return (int)kOpen;
+                if (!all_rows) return (int)kMaskedChunk;
+                const int first_key = key0 + c * 32, last_key = first_key + 31;
+                if (first_key > warp_hi_pos) return (int)kDead;
+                if (p.window > 0) {
+                    if (last_key < max(0, warp_lo_pos - p.window + 1)) return (int)kDead;
+                    if (first_key < max(0, warp_hi_pos - p.window + 1)) return (int)kMaskedChunk;
+                }
+                return last_key <= warp_lo_pos ? (int)kOpen : (int)kMaskedChunk;
+            };
             // Pass 1: the row's maximum over the block, 32 columns at a time (the next chunk is in flight while one
             // is reduced; four partial maxima keep the dependency chains short).
             uint32_t ca[32], cb[32];
@@ -501,11 +519,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             // (the scale is positive, so the maximum of the raw scores is scaled once at the end; blocks that need
             // no mask take the short path: one instruction per element)
             auto reduce_max = [&](const uint32_t (&chunk)[32], int c) {
-                if (full) {
+                const int mode = chunk_mode(c);
+                if (mode == kOpen) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2)
                         mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1]));
-                } else {
+                } else if (mode == kMaskedChunk) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const bool valid = c * 32 + i >= lo_col && c * 32 + i <= hi_col;
@@ -556,7 +575,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
             auto emit = [&](const uint32_t (&chunk)[32], int c) {
                 uint32_t packed[16];
                 const float neg_m = -m;
-                if (full) {
+                const int mode = chunk_mode(c);
+                if (mode == kDead) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) packed[i] = 0u;
+                } else if (mode == kOpen) {
                     const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(neg_m, neg_m);
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
