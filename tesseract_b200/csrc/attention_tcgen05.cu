@@ -269,26 +269,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
     }
     // barriers and tensor memory are set up while the kernel before this one drains; its results (the rotated
     // queries, this step's keys and values) are read from here on
-    pdl_wait();
-    // the Q tile: every thread copies its share of the 128 rows x D / 8 chunks, swizzled like the K/V tiles
-    constexpr int kChunks = D / 8;
-    for (int idx = threadIdx.x; idx < BM * kChunks; idx += kThreads) {
-        const int r = idx / kChunks, c = idx % kChunks;
-        const int fr = r0 + r;
-        const bool ok = fr < n_rows;
-        const __nv_bfloat16* src = p.q;
-        if (ok) {
-            const int qpos = fr / p.group, g = fr - qpos * p.group;
-            src = p.q + (int64_t)(first_row + qpos) * p.q_stride + (int64_t)(kv_head * p.group + g) * D + c * 8;
-        }
-        cp_async16(q_tile + (c >> 3) * kTileBytes + sw128(r, c & 7), src, ok);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();
+    // The Q tile: the threads of warps 0..4 copy their share of the 128 rows x D / 8 chunks, swizzled like the K/V
+    // tiles, while warp 5 already brings the first key and value blocks (a tile's first scores used to wait for
+    // the two loads one after the other).
+    constexpr int kChunks = D / 8;
+    if (warp != 5) {
+        for (int idx = threadIdx.x; idx < BM * kChunks; idx += kThreads - 32) {
+            const int r = idx / kChunks, c = idx % kChunks;
+            const int fr = r0 + r;
+            const bool ok = fr < n_rows;
+            const __nv_bfloat16* src = p.q;
+            if (ok) {
+                const int qpos = fr / p.group, g = fr - qpos * p.group;
+                src = p.q + (int64_t)(first_row + qpos) * p.q_stride + (int64_t)(kv_head * p.group + g) * D + c * 8;
+            }
+            cp_async16(q_tile + (c >> 3) * kTileBytes + sw128(r, c & 7), src, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        asm volatile("bar.sync 1, 160;" ::: "memory");            // warps 0..4: the issuer reads Q after this
+    }
     const uint32_t tmem_base = tmem_base_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BN;
 
