@@ -187,6 +187,31 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// 2^x for a pair of lanes on the FMA pipe, for x <= 8 or so (the softmax's exponents): the special-function unit
+// gives 16 results a cycle and SM, which bounds the unmasked blocks' loop once two CTAs share an SM, so at head
+// size 64 every fourth pair of a row goes this way (2 to 5 % faster; every third or second pair is slower again,
+// and so is any share at head size 128, whose blocks have more products per exponential).  x = n + f with n the
+// nearest integer (the low mantissa bits of x + 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f by a cubic (largest
+// relative error 7.5e-5, far below the rounding of the probabilities to bfloat16); n is added into the exponent
+// field.  All of it in 32-bit arithmetic.
+template <int D>
+constexpr int kPolyEvery = D == 64 ? 4 : 0;
+__device__ __forceinline__ void exp2_pair_fma(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    const uint64_t x = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+    const uint64_t t = add2(x, pack2(12582912.0f, 12582912.0f));
+    const uint64_t n = add2(t, pack2(-12582912.0f, -12582912.0f));
+    const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), x);
+    uint64_t q = fma2(f, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
+    q = fma2(q, f, pack2(0.6932609677f, 0.6932609677f));
+    q = fma2(q, f, pack2(0.9999280572f, 0.9999280572f));
+    float q0, q1, t0, t1;
+    unpack2(q, q0, q1);
+    unpack2(t, t0, t1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
 
 // SPLIT: tiles shared by gridDim.y CTAs (the code that leaves and adds partial rows costs the unsplit kernel 2-6 %
 // of its time through its registers alone, so it is an instantiation of its own).
@@ -445,10 +470,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap cache_map, const Tc
                 auto exps = [&](const uint32_t (&chunk)[32], uint32_t* packed) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float t0, t1;
-                        unpack2(fma2(pack2(__uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1])), scale2, neg_m2),
-                                t0, t1);
-                        const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                        const uint64_t x2 = fma2(pack2(__uint_as_float(chunk[i]), __uint_as_float(chunk[i + 1])), scale2, neg_m2);
+                        float p0, p1;
+                        constexpr int kEvery = kPolyEvery<D> > 0 ? kPolyEvery<D> : 1;
+                        if (kPolyEvery<D> > 0 && (i >> 1) % kEvery == kEvery - 1) {
+                            exp2_pair_fma(x2, p0, p1);
+                        } else {
+                            float t0, t1;
+                            unpack2(x2, t0, t1);
+                            p0 = fast_exp2(t0);
+                            p1 = fast_exp2(t1);
+                        }
                         ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
                         packed[i >> 1] = pack_bf16(p0, p1);
                     }
