@@ -224,13 +224,15 @@ def run_ours(args):
         t0 = time.time()
         # (`--repeats N` below the default also shortens the prefill: a run under a profiler wants few launches)
         prefill_repeats = REPEATS_PREFILL if args.repeats >= REPEATS_DECODE else max(1, args.repeats)
-        prefill_times = sorted(prefill_once(f"pre{k}")[0] for k in range(prefill_repeats))
+        prefill_in_order = [prefill_once(f"pre{k}")[0] for k in range(prefill_repeats)]
+        prefill_times = sorted(prefill_in_order)
         portions_times = sorted(prefill_in_portions(f"prp{k}", 512) for k in range(prefill_repeats))
         windows.append((t0, time.time()))
     prefill_ms = statistics.median(prefill_times)
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens_per_s": PROMPT_TOKENS / (prefill_ms / 1e3),
                           "ms_min": prefill_times[0], "ms_max": prefill_times[-1],
+                          "ms_in_order": [round(t, 3) for t in prefill_in_order],
                           "ms_4x512": statistics.median(portions_times)}))
         return 0
     flops = prefill_flops(cfg, layers, PROMPT_TOKENS)
