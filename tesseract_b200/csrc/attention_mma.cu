@@ -642,8 +642,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
                 float c = 1.0f, s = 0.0f;
                 if (p.inv_freq != nullptr) {
                     const float angle = (float)begin * p.inv_freq[i];
-                    c = cosf(angle);
-                    s = sinf(angle);
+                    sincosf(angle, &s, &c);     // (the same call as in rope_cache.cu: a key is the same bits whichever wrote it)
                 }
                 trig[i] = c;
                 trig[half + i] = s;

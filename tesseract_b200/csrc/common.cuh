@@ -78,12 +78,24 @@ struct Packet<float> {
     static __device__ __forceinline__ void store(float* p, const float* v) {
         *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     }
+    // a packet kept as it was loaded (16 bytes) and taken apart later
+    static __device__ __forceinline__ void unpack(const uint4& t, float* v) {
+        v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y); v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+    }
 };
 template <>
 struct Packet<__nv_bfloat16> {
     static constexpr int N = 8;
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
         const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void unpack(const uint4& t, float* v) {
         const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {

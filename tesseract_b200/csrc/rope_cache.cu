@@ -30,8 +30,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int64_t qkv_stride, co
         float c = 1.0f, s = 0.0f;
         if (inv_freq != nullptr) {
             const float angle = (float)pos * inv_freq[i];
-            c = cosf(angle);
-            s = sinf(angle);
+            sincosf(angle, &s, &c);
         }
         trig[i] = c;
         trig[half + i] = s;
@@ -134,7 +133,7 @@ __global__ void rope_kv_write_preload_kernel(T* __restrict__ qkv, int64_t qkv_st
     const int v_per = head_dim / N;
     const int v_items = write_kv ? num_kv_heads * v_per : 0;
     const T* v = base + (int64_t)rot_heads * head_dim;
-    float lo[kItemsPerThread][N], hi[kItemsPerThread][N];
+    uint4 lo[kItemsPerThread], hi[kItemsPerThread];       // as loaded: converted when they are rotated
     uint4 v_packet[kItemsPerThread];
 #pragma unroll
     for (int k = 0; k < kItemsPerThread; ++k) {
@@ -142,8 +141,8 @@ __global__ void rope_kv_write_preload_kernel(T* __restrict__ qkv, int64_t qkv_st
         if (item < rot_items) {
             const int head = item / per_head;
             const int i = (item - head * per_head) * N;
-            Packet<T>::load(base + (int64_t)head * head_dim + i, lo[k]);
-            Packet<T>::load(base + (int64_t)head * head_dim + half + i, hi[k]);
+            lo[k] = *reinterpret_cast<const uint4*>(base + (int64_t)head * head_dim + i);
+            hi[k] = *reinterpret_cast<const uint4*>(base + (int64_t)head * head_dim + half + i);
         }
         if (item < v_items) {
             const int head = item / v_per;
@@ -155,8 +154,7 @@ __global__ void rope_kv_write_preload_kernel(T* __restrict__ qkv, int64_t qkv_st
         float c = 1.0f, s = 0.0f;
         if (inv_freq != nullptr) {
             const float angle = (float)pos * (i == (int)threadIdx.x ? freq : inv_freq[i]);
-            c = cosf(angle);
-            s = sinf(angle);
+            sincosf(angle, &s, &c);
         }
         trig[i] = c;
         trig[half + i] = s;
@@ -173,12 +171,14 @@ __global__ void rope_kv_write_preload_kernel(T* __restrict__ qkv, int64_t qkv_st
         if (item < rot_items) {
             const int head = item / per_head;
             const int i = (item - head * per_head) * N;
-            float out_lo[N], out_hi[N];
+            float in_lo[N], in_hi[N], out_lo[N], out_hi[N];
+            Packet<T>::unpack(lo[k], in_lo);
+            Packet<T>::unpack(hi[k], in_hi);
 #pragma unroll
             for (int e = 0; e < N; ++e) {
                 const float c = trig[i + e], s = trig[half + i + e];
-                out_lo[e] = lo[k][e] * c - hi[k][e] * s;
-                out_hi[e] = hi[k][e] * c + lo[k][e] * s;
+                out_lo[e] = in_lo[e] * c - in_hi[e] * s;
+                out_hi[e] = in_hi[e] * c + in_lo[e] * s;
             }
             T* dst = nullptr;
             if (head < num_heads) dst = base + (int64_t)head * head_dim;
