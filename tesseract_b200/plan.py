@@ -66,8 +66,8 @@ def _attention_tcgen05_takes(num_heads: int, num_kv_heads: int, head_dim: int, p
 class ProductPlan:
     """``kernel``: ``gemm_f32`` (true 32-bit FFMA), ``decode_linear`` (weight streaming, at most 16 rows),
     ``skinny_tcgen05`` (weight streaming on the tensor-memory cores, at most 128 rows), ``gemm_tcgen05`` (this
-    package's tensor-memory GEMM: CTA pairs on 256-row tiles above 128 rows) or ``library``.  ``norm_folded``: the RMSNorm (and the
-    residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
+    package's tensor-memory GEMM: CTA pairs on 256-row tiles above 128 rows) or ``library``.
+    ``norm_folded``: the RMSNorm (and the residual addition) in front runs inside the product's kernel.  ``epilogue``: what the kernel stores;
     ``activation_apart``: SwiGLU was asked for but runs as a kernel of its own behind the product.
     ``prepares_norm``: the product also does the work of the norm BEHIND it (new residual, rows times the norm's
     weights, sums of squares); the product behind that then runs with ``norm="prepared"`` (``takes_prepared``): it
