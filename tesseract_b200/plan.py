@@ -164,17 +164,17 @@ def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_di
 
 def prompt_key_splits(tile_ctas: int, max_context: int, head_dim: int = 64, sms: Optional[int] = None) -> int:
     """CTAs per tile of the tcgen05 prompt kernel.  A tile of 128 folded rows walks over its key blocks (128 keys
-    up to head size 64, else 64) one after the other, about 1.7 microseconds a block, and two CTAs fit an SM: a
-    step with fewer tiles than that (a 512-token portion of one prompt is 128 tiles of the 1B sizes) leaves SMs
-    idle while every tile walks its whole context.  Such a step gives each tile to several CTAs, each over a run of
-    at least sixteen blocks, as many as are resident at once (at most 8); the last one to finish adds the runs.
-    Leaving and adding the partial rows costs about 10 microseconds (a round of stores, a fence, a counter, three
-    rounds of loads from L2), and two CTAs on an SM share its exponential unit, so short contexts lose: a 512-token
-    portion at context 2,048 takes 34.9 us alone and 36.6 shared by two, at 4,096 61.7 and 52.4, at 16,384 232 and
-    146."""
+    up to head size 64, else 64) one after the other, and two CTAs fit an SM: a step with fewer tiles than that (a
+    512-token portion of one prompt is 128 tiles of the 1B sizes) leaves SMs idle while every tile walks its whole
+    context.  Such a step gives each tile to several CTAs, each over a run of at least 2,048 keys, as many as are
+    resident at once (at most 8); the last one to finish adds the runs.  Leaving and adding the partial rows costs
+    about 10 microseconds (a round of stores, a fence, a counter, three rounds of loads from L2), and two CTAs on an
+    SM share its exponential unit, so short contexts lose, at either head size: a 512-token portion at context
+    2,048 takes 27.3 us alone and 32.6 shared by two (head size 128: 42.9 and 53.5), at 3,072 38.6 and 39.0 (61.0
+    and 62.8), at 4,096 50.3 and 45.0 (78.6 and 72.3), at 8,192 94.4 and 68.5 (150 and 110); ``head_dim`` is taken for
+    the callers' sake and does not enter."""
     resident = 2 * (sms or kernels.sm_count())
-    blocks = -(-max_context // (128 if head_dim <= 64 else 64))
-    return max(1, min(8, resident // max(1, tile_ctas), blocks // 16))
+    return max(1, min(8, resident // max(1, tile_ctas), max_context // 2048))
 
 
 @dataclass(frozen=True)

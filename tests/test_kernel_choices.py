@@ -109,6 +109,11 @@ def test_attention_plans():
     assert plan.attention(BF, new_tokens=[512], max_context=16384, **sizes).key_splits == 2
     assert plan.attention(BF, new_tokens=[512, 512, 512], max_context=16384, **sizes).key_splits == 1
     assert plan.attention(BF, new_tokens=[64], max_context=32768, **sizes).key_splits == 8
+    # (the rule counts keys, not blocks: at head size 128, whose blocks are 64 keys, sharing starts at 4,096 too)
+    wide = dict(sizes, head_dim=128)
+    assert plan.attention(BF, new_tokens=[512], max_context=2048, **wide).key_splits == 1
+    assert plan.attention(BF, new_tokens=[512], max_context=3072, **wide).key_splits == 1
+    assert plan.attention(BF, new_tokens=[512], max_context=4096, **wide).key_splits == 2
     mixed = plan.attention(BF, new_tokens=[512, 1, 1, 3], max_context=4096, **sizes)
     assert mixed.prompt == "tcgen05" and mixed.split and mixed.splits >= 1
     narrow = dict(sizes, head_dim=48, num_heads=6, num_kv_heads=3)
