@@ -700,6 +700,8 @@ def test_gemm_tcgen05(m, n, k, form):
     ([300], [17], 16, 1, 16, 0),                                # a group of 16: two tokens fill a tile row block
     ([333, 90], [200, 90], 4, 2, 8, 0),                         # the smallest pages: sixteen or eight copies a block
     ([500], [300], 6, 3, 32, 64),                               # pages of 32 keys, a window
+    ([700], [300], 24, 8, 16, 0),                               # a group of three: tiles begin inside a position
+    ([900, 40], [420, 40], 12, 4, 16, 200),                     # the same with a window over several blocks
 ])
 @pytest.mark.parametrize("d", [64, 128])
 def test_attention_tcgen05(lengths, new, nh, nkv, page_size, window, d):
