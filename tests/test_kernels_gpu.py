@@ -690,6 +690,55 @@ def test_gemm_tcgen05(m, n, k, form):
         torch.testing.assert_close(act.cpu().double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("n, new, window", [(700, 300, 0), (700, 300, 130), (1100, 420, 300), (520, 130, 1)])
+def test_attention_tcgen05_at_the_edges_of_what_a_row_sees(n, new, window, d):
+    """Scores that grow by 8 with every key (the position written into two dimensions as 16 * hi + lo, exact in
+    bfloat16) make the LAST key a row sees take all the weight; scores that fall by 8 make the FIRST one take it.  A
+    mask off by one key at either edge (the row's own position; the window's first key) returns the wrong key's
+    value, whichever block, chunk or CTA the edge falls into."""
+    from tesseract_b200 import kernels
+
+    nh, nkv, page_size = 8, 2, 16
+    for direction in (1.0, -1.0):
+        case = paged_case(torch.bfloat16, [n], [new], nh, nkv, d, page_size, seed=n + new + window + d)
+        k = torch.zeros(n, nkv, d)
+        where = torch.arange(n)
+        k[:, :, 3] = (where // 16).float()[:, None]
+        k[:, :, 7] = (where % 16).float()[:, None]
+        q = torch.zeros(new, nh, d)
+        q[:, :, 3] = direction * 128.0
+        q[:, :, 7] = direction * 8.0
+        case["q"], case["ks"][0] = q.to(torch.bfloat16), k.to(torch.bfloat16)
+        cache = case["cache"].float()
+        for logical in range(-(-n // page_size)):
+            pg = int(case["table"][0, logical])
+            span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+            cache[pg, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+        case["cache"] = cache.to(torch.bfloat16)
+        row_start = torch.tensor([0, new], dtype=torch.int32)
+        seq_begin = torch.tensor([n - new], dtype=torch.int32)
+        tiles = kernels.attention_tcgen05_tile_ctas(1, new, nh, nkv)
+        for key_splits in (1, 2):
+            if tiles * key_splits > 2 * kernels.sm_count():
+                continue
+            out = torch.full((new, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+            kernels.attention_tcgen05(dev(case["q"]).view(new, nh * d), out, dev(case["cache"]), dev(row_start),
+                                      dev(seq_begin), dev(case["table"]), 1, new, nh, nkv, d, page_size, window, 1.0,
+                                      key_splits=key_splits)
+            assert kernels.tcgen05_error() == 0
+            values = case["vs"][0].float()
+            for r in range(new):
+                position = n - new + r
+                first = max(0, position - window + 1) if window else 0
+                target = position if direction > 0 else first
+                want = values[target].repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+                torch.testing.assert_close(out[r].cpu().float(), want, rtol=1e-2, atol=1e-2,
+                                           msg=lambda m: f"row at position {position} (window {window}, scores "
+                                                         f"{'rising' if direction > 0 else 'falling'}, "
+                                                         f"{key_splits} CTAs a tile): {m}")
+
+
 @pytest.mark.parametrize("lengths, new, nh, nkv, page_size, window", [
     ([40], [40], 4, 4, 16, 0),                                  # a single block, rows beyond the sequence masked
     ([100, 70], [30, 1], 8, 8, 16, 0),                          # no grouping; the decode row is left to the other kernel
