@@ -691,6 +691,43 @@ def test_gemm_tcgen05(m, n, k, form):
 
 
 @pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window", [0, 1, 100, 333])
+@pytest.mark.parametrize("splits", [1, 3, 12])
+def test_decode_attention_at_the_edges_of_what_a_row_sees(window, splits, d):
+    """The same construction for single decode rows on the split kernel (the prompt kernel's test below explains it):
+    sequences whose last key, and whose window's first key, fall at a page's first and last place, at a tile's and
+    at a split's."""
+    nh, nkv, page_size = 8, 2, 16
+    lengths = [1, 16, 17, 130, 257, 300, 511, 640, 1025]
+    for direction in (1.0, -1.0):
+        case = paged_case(torch.bfloat16, lengths, [1] * len(lengths), nh, nkv, d, page_size, seed=window + splits + d)
+        q = torch.zeros(len(lengths), nh, d)
+        q[:, :, 3] = direction * 128.0
+        q[:, :, 7] = direction * 8.0
+        case["q"] = q.to(torch.bfloat16)
+        cache = case["cache"].float()
+        for s, n in enumerate(lengths):
+            k = torch.zeros(n, nkv, d)
+            where = torch.arange(n)
+            k[:, :, 3] = (where // 16).float()[:, None]
+            k[:, :, 7] = (where % 16).float()[:, None]
+            case["ks"][s] = k.to(torch.bfloat16)
+            for logical in range(-(-n // page_size)):
+                pg = int(case["table"][s, logical])
+                span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+                cache[pg, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+        case["cache"] = cache.to(torch.bfloat16)
+        out = run_attention_mma(case, nh, nkv, d, page_size, window, 1.0, splits)
+        for s, n in enumerate(lengths):
+            first = max(0, n - window) if window else 0
+            target = n - 1 if direction > 0 else first
+            want = case["vs"][s][target].float().repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+            torch.testing.assert_close(out[s].cpu().float(), want, rtol=1e-2, atol=1e-2,
+                                       msg=lambda m: f"sequence of {n} keys (window {window}, scores "
+                                                     f"{'rising' if direction > 0 else 'falling'}): {m}")
+
+
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("n, new, window", [(700, 300, 0), (700, 300, 130), (1100, 420, 300), (520, 130, 1)])
 def test_attention_tcgen05_at_the_edges_of_what_a_row_sees(n, new, window, d):
     """Scores that grow by 8 with every key (the position written into two dimensions as 16 * hi + lo, exact in
