@@ -177,6 +177,43 @@ def test_attention_rows(dtype, lengths, new, nh, nkv, d, page_size, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 1, 24, 100])
+def test_attention_rows_at_the_edges_of_what_a_row_sees(dtype, window):
+    """Scores that rise by 8 with every key (the position as 16 * hi + lo in two dimensions, exact in bfloat16 too) give
+    all the weight to the LAST key a row sees, falling ones to the FIRST: a mask off by one key at the row's own
+    position or at the window's first key returns another key's value."""
+    from tesseract_b200 import kernels
+
+    nh, nkv, d, page_size = 4, 2, 32, 16
+    lengths, new = [1, 17, 130, 300, 511], [1, 17, 40, 1, 64]
+    for direction in (1.0, -1.0):
+        case = paged_case(dtype, lengths, new, nh, nkv, d, page_size, seed=window)
+        rows = case["q"].shape[0]
+        q = torch.zeros(rows, nh, d)
+        q[:, :, 3] = direction * 128.0
+        q[:, :, 7] = direction * 8.0
+        cache = case["cache"].float()
+        for s, n in enumerate(lengths):
+            k = torch.zeros(n, nkv, d)
+            where = torch.arange(n)
+            k[:, :, 3] = (where // 16).float()[:, None]
+            k[:, :, 7] = (where % 16).float()[:, None]
+            for logical in range(-(-n // page_size)):
+                pg = int(case["table"][s, logical])
+                span = slice(logical * page_size, min(n, (logical + 1) * page_size))
+                cache[pg, 0, :, :span.stop - span.start] = k[span].transpose(0, 1)
+        out = torch.empty(rows, nh * d, dtype=dtype, device="cuda")
+        kernels.attention_rows(dev(q.to(dtype)).view(rows, nh * d), out, dev(cache.to(dtype)), dev(case["positions"]),
+                               dev(case["seq_of_row"]), dev(case["table"]), nh, nkv, d, page_size, window, 1.0)
+        for r in range(rows):
+            s, position = int(case["seq_of_row"][r]), int(case["positions"][r])
+            first = max(0, position - window + 1) if window else 0
+            target = position if direction > 0 else first
+            want = case["vs"][s][target].float().repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+            torch.testing.assert_close(out[r].cpu().float(), want, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key_among_hundreds(dtype):
     """One query and one far key are scaled so that a single score stands out: the row must return that key's value,
     wherever in the pages it lies (first key, a page's last slot, a page's first slot, the row's own position)."""
